@@ -1,0 +1,388 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] (+)= A · B^T      A: M x K,  B: N x K,  fp32 accumulation in tensor memory.
+//
+// Either operand may be stored "K-major" (rows = M/N index, K contiguous; the layout of an
+// nn.Linear input or weight) or "MN-major" (rows = K index, M/N contiguous). That covers all three
+// products of a linear layer without any transposition pass:
+//   fprop  Y = X · W^T        A = X  (K-major),  B = W  (K-major)
+//   dgrad  dX = dY · W        A = dY (K-major),  B = W  (MN-major: rows are the contracted N)
+//   wgrad  dW = dY^T · X      A = dY (MN-major), B = X  (MN-major), contraction over tokens
+//
+// Structure (one CTA per SM, 192 threads):
+//   warp 0    TMA producer: cp.async.bulk.tensor tiles of A and B into a 128B-swizzled smem ring
+//   warp 1    one thread issues tcgen05.mma (128 x BN x 16) into one of two TMEM accumulators
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator, add bias / convert / store / reduce,
+//             while warp 1 already fills the other accumulator with the next tile.
+// Tiles are walked with a static stride over a persistent grid; an optional split along K makes
+// enough tiles for the long-K weight-gradient products and reduces with red.global.add.f32.
+//
+// Replaces cuBLAS behind nn.Linear in the reference (lset/models/decoder/qwen3/attention.py:102-104,
+// lset/models/decoder/qwen3/mlp.py:28).
+#include <cuda_bf16.h>
+
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+
+namespace lb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;  // nullable, length N
+  int accumulate;             // fp32 output only: C += result (red.global.add)
+  int splits;                 // >= 1, split of the K range
+  int kb_per_split;
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) {
+  uint4 q;
+  q.x = pack_bf16x2(v[0], v[1]);
+  q.y = pack_bf16x2(v[2], v[3]);
+  q.z = pack_bf16x2(v[4], v[5]);
+  q.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = q;
+}
+
+__device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+template <int A_MN, int B_MN, int BN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     GemmArgs g) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tfull = empty + C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (g.M + BM - 1) / BM;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  const int kb_total = (g.K + BK - 1) / BK;
+  const int total = tiles_m * tiles_n * g.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int split = tile / (tiles_m * tiles_n);
+        const int mn = tile - split * (tiles_m * tiles_n);
+        const int m0 = (mn / tiles_n) * BM;
+        const int n0 = (mn % tiles_n) * BN;
+        const int kb0 = split * g.kb_per_split;
+        const int kb1 = min(kb0 + g.kb_per_split, kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u)) {
+            report_status(g.status, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          uint8_t* sb = sa + C::A_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (BK * 128), &tmA, &full[stage], m0 + 64 * c, kb * BK);
+          } else {
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tmB, &full[stage], n0 + 64 * c, kb * BK);
+          } else {
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, n0);
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Let copies that were already issued land before the CTA gives its shared memory back.
+        for (int s = 0; s < C::STAGES; ++s) mbar_wait(&full[s], 0, 2000000ull);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+        const int split = tile / (tiles_m * tiles_n);
+        const int kb0 = split * g.kb_per_split;
+        const int kb1 = min(kb0 + g.kb_per_split, kb_total);
+        const int acc = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aphase ^ 1u)) {
+          report_status(g.status, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) {
+            report_status(g.status, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                        : umma_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                        : umma_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    OutT* Cout = reinterpret_cast<OutT*>(g.C);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+      const int split = tile / (tiles_m * tiles_n);
+      const int mn = tile - split * (tiles_m * tiles_n);
+      const int m0 = (mn / tiles_n) * BM;
+      const int n0 = (mn % tiles_n) * BN;
+      const int acc = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], aphase)) {
+        report_status(g.status, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool add_bias = (g.bias != nullptr) && (split == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < g.M && col0 < g.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (add_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
+          }
+          OutT* dst = Cout + static_cast<long long>(row) * g.ldc + col0;
+          if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (col0 + 8 * j < g.N)
+                store8_bf16(reinterpret_cast<__nv_bfloat16*>(dst) + 8 * j, v + 8 * j);
+          } else {
+            float* fd = reinterpret_cast<float*>(dst);
+            if (g.accumulate) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col0 + 4 * j < g.N)
+                  red_add4(fd + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col0 + 4 * j < g.N)
+                  *reinterpret_cast<float4*>(fd + 4 * j) =
+                      make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+int g_num_sms = 0;
+
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int A_MN, int B_MN, int BN, typename OutT>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
+           cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
+        cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <int A_MN, int B_MN, int BN>
+int launch_out(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
+               bool out_fp32, cudaStream_t stream) {
+  return out_fp32 ? launch<A_MN, B_MN, BN, float>(tmA, tmB, g, grid, stream)
+                  : launch<A_MN, B_MN, BN, __nv_bfloat16>(tmA, tmB, g, grid, stream);
+}
+
+}  // namespace
+}  // namespace lb
+
+// C = A · B^T with bf16 operands.
+//   a_mn = 0: A is [M, K] row-major with row stride lda; a_mn = 1: A is stored [K, M], stride lda.
+//   b_mn = 0: B is [N, K] row-major with row stride ldb; b_mn = 1: B is stored [K, N], stride ldb.
+//   out_fp32: C is float (else bf16), row stride ldc. accumulate (fp32 only): C += product.
+//   splits: split of K (fp32 accumulate only; >1 forces accumulate). bn: 0 = auto, 128 or 256.
+// All leading dimensions and N must be multiples of 8 elements; base pointers 16-byte aligned.
+// Returns 0 or a negative code; device-side timeouts are reported through *status (device int).
+extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                            int out_fp32, int accumulate, const void* bias, int splits, int bn,
+                            int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -4;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -3;
+  if (!out_fp32 && (ldc & 7)) return -3;
+  if (!out_fp32 && (accumulate || splits > 1)) return -5;
+
+  const int tiles_m = (M + BM - 1) / BM;
+  const int sms = num_sms();
+  if (bn != 128 && bn != 256) {
+    auto eff = [&](int b) {
+      const long long t = 1LL * tiles_m * ((N + b - 1) / b);
+      const long long waves = (t + sms - 1) / sms;
+      return double(t) * b / double(waves * sms);  // useful columns per SM-slot
+    };
+    bn = (N > 128 && eff(256) >= eff(128)) ? 256 : 128;
+  }
+  const int tiles_n = (N + bn - 1) / bn;
+  const int kb_total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  int kb_per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per - 1) / kb_per;
+  if (splits > 1) accumulate = 1;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (a_mn)
+    rc = make_tmap_2d(&tmA, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, true);
+  else
+    rc = make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true);
+  else
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, bn, true);
+  if (rc) return rc;
+
+  GemmArgs g;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.C = C;
+  g.ldc = ldc;
+  g.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  g.accumulate = accumulate;
+  g.splits = splits;
+  g.kb_per_split = kb_per;
+  g.status = status;
+  const long long total = 1LL * tiles_m * tiles_n * splits;
+  const int grid = (int)(total < sms ? total : sms);
+  const bool f32 = out_fp32 != 0;
+
+#define LB_DISPATCH(AM, BMJ)                                                        \
+  (bn == 256 ? launch_out<AM, BMJ, 256>(tmA, tmB, g, grid, f32, stream)             \
+             : launch_out<AM, BMJ, 128>(tmA, tmB, g, grid, f32, stream))
+  if (!a_mn && !b_mn) return LB_DISPATCH(0, 0);
+  if (!a_mn && b_mn) return LB_DISPATCH(0, 1);
+  if (a_mn && b_mn) return LB_DISPATCH(1, 1);
+  return LB_DISPATCH(1, 0);
+#undef LB_DISPATCH
+}

@@ -1,0 +1,141 @@
+"""bf16 GEMM on the tcgen05 kernel, and the ``linear`` autograd op built from its three forms.
+
+``matmul_abt`` computes ``C = A · Bᵀ`` where each operand is either K-major (``[rows, K]``, the
+layout of activations and ``nn.Linear`` weights) or MN-major (``[K, rows]``). The backward of a
+linear layer uses the MN-major forms so no tensor is ever transposed in memory.
+
+Replaces the cuBLAS calls behind ``nn.Linear`` in the reference
+(lset/models/decoder/qwen3/attention.py:102-104, lset/models/decoder/qwen3/mlp.py:28).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native as nv
+
+
+def _oracle(a, b, a_mn, b_mn, bias, out_dtype):
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float().t() if b_mn else b.float()
+    c = af @ bf.t()
+    if bias is not None:
+        c = c + bias.float()
+    return c.to(out_dtype)
+
+
+def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16,
+               accumulate=False, bias=None, splits=1, bn=0):
+    """``C[M,N] = A · Bᵀ`` with fp32 accumulation.
+
+    a: ``[M, K]`` (``[K, M]`` when ``a_mn``), b: ``[N, K]`` (``[K, N]`` when ``b_mn``); 2-D bf16
+    with unit inner stride. ``out`` may be given (fp32 with ``accumulate=True`` adds into it).
+    ``splits > 1`` splits the contraction and reduces with fp32 atomics (fp32 output only).
+    """
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("matmul_abt takes 2-D operands")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {K} vs {Kb}")
+    if out is not None:
+        out_dtype = out.dtype
+    if not nv.use_native(a, b):
+        c = _oracle(a, b, a_mn, b_mn, bias, torch.float32 if accumulate else out_dtype)
+        if out is not None:
+            if accumulate:
+                out.add_(c.to(out.dtype))
+            else:
+                out.copy_(c)
+            return out
+        return c
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("matmul_abt runs bf16 operands on the GPU")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("output must be bf16 or fp32")
+    if splits > 1 and out_dtype != torch.float32:
+        splits = 1
+    if out is None:
+        if accumulate or splits > 1:
+            out = torch.zeros(M, N, dtype=out_dtype, device=a.device)
+        else:
+            out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    elif splits > 1 and not accumulate:
+        out.zero_()
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        if not accumulate:
+            out.zero_()
+        return out
+    if bias is not None and bias.dtype != torch.bfloat16:
+        bias = bias.to(torch.bfloat16)
+    lib = nv.load()
+    rc = lib.lb_gemm_bf16(
+        nv.c_void_p(a.data_ptr()), nv.c_void_p(b.data_ptr()), nv.c_void_p(out.data_ptr()),
+        nv.c_int(M), nv.c_int(N), nv.c_int(K),
+        nv.c_ll(a.stride(0)), nv.c_ll(b.stride(0)), nv.c_ll(out.stride(0)),
+        nv.c_int(int(a_mn)), nv.c_int(int(b_mn)), nv.c_int(int(out_dtype == torch.float32)),
+        nv.c_int(int(accumulate or splits > 1)), nv.c_void_p(nv.ptr(bias)), nv.c_int(splits),
+        nv.c_int(bn), nv.c_void_p(nv.status_word(a.device).data_ptr()),
+        nv.c_void_p(nv.stream_ptr()),
+    )
+    nv.check_rc(rc, f"lb_gemm_bf16(M={M},N={N},K={K})")
+    nv.count_launch()
+    return out
+
+
+def wgrad_splits(n_out: int, k_in: int, tokens: int) -> int:
+    """Split of the token contraction that fills the 148 SMs for a ``[n_out, k_in]`` weight grad."""
+    tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
+    kb = max(1, (tokens + 63) // 64)
+    if tiles >= 148:
+        return 1
+    return max(1, min(kb // 8 if kb >= 8 else 1, (2 * 148 + tiles - 1) // tiles))
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        y = matmul_abt(x2, w, bias=bias)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16 and dy2.is_cuda:
+            dy2 = dy2.to(torch.bfloat16)
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_abt(dy2, w, b_mn=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            main = getattr(w, "main_grad", None)
+            if main is not None and dy2.is_cuda:
+                # fp32 gradient accumulator owned by the sharding runtime: add straight into it.
+                matmul_abt(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True,
+                           splits=wgrad_splits(w.shape[0], w.shape[1], x2.shape[0]))
+                dw = None
+            else:
+                dw = matmul_abt(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32,
+                                splits=wgrad_splits(w.shape[0], w.shape[1], x2.shape[0])
+                                if dy2.is_cuda else 1).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    """``y = x · wᵀ (+ bias)`` — drop-in for ``F.linear`` on bf16 CUDA tensors; eager on CPU/fp32."""
+    if not nv.use_native(x, w) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return torch.nn.functional.linear(x, w, bias)
+    return _Linear.apply(x, w, bias)
