@@ -1,0 +1,393 @@
+// Varlen (packed) flash attention forward on tcgen05: causal or bidirectional, grouped-query heads.
+//
+// One 128-thread CTA per (sequence, query tile, KV head); two CTAs share an SM. Per KV block of 64:
+//   S = Q·Kᵀ          tcgen05.mma, A = Q tile (128 x hd), B = K block (64 x hd), S in TMEM
+//   online softmax     thread r owns row r: tcgen05.ld, mask, running max / sum in registers;
+//                      the O accumulator in TMEM is rescaled only when the max moved by > 2^8
+//   O += P·V          P (bf16) is written into the shared-memory slot of the K block it came from,
+//                      V is consumed in place as an MN-major operand (no transpose)
+// Q/K/V are read with TMA straight out of the (possibly fused) projection output through explicit
+// row strides. Writes O and the natural-log LSE per (head, token) for the backward.
+//
+// Replaces flash_attn_varlen_func / varlen_attn / SDPA in the reference
+// (lset/models/decoder/qwen3/attention.py:169-272, lset/models/encoder/bert/model.py:264-319).
+#include "../common/ptx.cuh"
+#include "../common/tma_desc.h"
+#include "attn_common.cuh"
+
+namespace lb {
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+struct AttnFwdArgs {
+  const int* cu_seqlens;
+  const int* plan;
+  bf16* O;
+  long long ldo;   // elements between consecutive tokens of O
+  float* lse;      // [Hq, T]
+  int T, Hq, Hk;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  int* status;
+};
+
+template <int HD>
+struct FwdCfg {
+  static constexpr int PANELS = HD / 64;
+  static constexpr int Q_BYTES = 128 * HD * 2;
+  static constexpr int KV_BYTES = kAttnKvBlock * HD * 2;
+  static constexpr int P_BYTES = 128 * kAttnKvBlock * 2;
+  static constexpr bool P_IN_K = KV_BYTES >= P_BYTES;
+  static constexpr int SMEM_BYTES =
+      Q_BYTES + 4 * KV_BYTES + (P_IN_K ? 0 : P_BYTES) + 1024 + 128;
+  static constexpr int TMEM_COLS = (64 + HD) <= 128 ? 128 : ((64 + HD) <= 256 ? 256 : 512);
+  static constexpr int O_COL = 64;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+    attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, AttnFwdArgs a) {
+  using C = FwdCfg<HD>;
+  AttnPlanView plan{a.plan};
+  if (int(blockIdx.x) >= plan.count()) return;
+  const int b = plan.seq(blockIdx.x);
+  const int qt = plan.tile(blockIdx.x);
+  const int hk = blockIdx.y;
+  const int G = a.Hq / a.Hk;
+  const int QT = 128 / G;
+  const int seq0 = a.cu_seqlens[b];
+  const int len = a.cu_seqlens[b + 1] - seq0;
+  const int q0 = qt * QT;
+  const int kv_end = a.causal ? min(len, q0 + QT) : len;
+  const int nblk = (kv_end + kAttnKvBlock - 1) / kAttnKvBlock;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::Q_BYTES;          // two buffers
+  uint8_t* sV = sK + 2 * C::KV_BYTES;     // two buffers
+  uint8_t* sPx = sV + 2 * C::KV_BYTES;    // separate P buffer (only when !P_IN_K)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sPx + (C::P_IN_K ? 0 : C::P_BYTES));
+  uint64_t* bar_q = bars;
+  uint64_t* bar_kv = bars + 1;  // [2]
+  uint64_t* bar_s = bars + 3;
+  uint64_t* bar_o = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(&bar_kv[0], 1);
+    mbar_init(&bar_kv[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+
+  auto load_kv = [&](int j) {
+    const int buf = j & 1;
+    mbar_expect_tx(&bar_kv[buf], 2 * C::KV_BYTES);
+#pragma unroll
+    for (int p = 0; p < C::PANELS; ++p) {
+      tma_load_2d(sK + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmK, &bar_kv[buf],
+                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
+      tma_load_2d(sV + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmV, &bar_kv[buf],
+                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
+    }
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(bar_q, C::Q_BYTES);
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int p = 0; p < C::PANELS; ++p)
+        tma_load_2d(sQ + p * (128 * 128) + g * QT * 128, &tmQ, bar_q, (hk * G + g) * HD + p * 64,
+                    seq0 + q0);
+    load_kv(0);
+  }
+
+  const int r = tid;
+  const int g = r / QT;
+  const int qpos = q0 + r % QT;
+  const bool row_valid = qpos < len;
+  float m_ref = -INFINITY;
+  float l_sum = 0.f;
+  constexpr uint32_t idesc_s = umma_idesc_bf16(128, kAttnKvBlock, 0, 0);
+  constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+  bool failed = false;
+
+  {
+    const bool ok = mbar_wait(bar_q, 0);
+    if (__syncthreads_or(!ok)) {
+      report_status(a.status, kStatusTimeoutProducer);
+      failed = true;
+    }
+  }
+
+  for (int j = 0; j < nblk && !failed; ++j) {
+    const int buf = j & 1;
+    // 1. K/V block landed -> S = Q K^T
+    {
+      const bool ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1);
+      if (__syncthreads_or(!ok)) {
+        report_status(a.status, kStatusTimeoutProducer);
+        failed = true;
+        break;
+      }
+    }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sQ);
+      const uint32_t ka = smem_u32(sK + buf * C::KV_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint64_t ad = umma_smem_desc(qa + (ks / 4) * (128 * 128) + (ks % 4) * 32, 16, 1024);
+        const uint64_t bd =
+            umma_smem_desc(ka + (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32, 16, 1024);
+        umma_bf16(tmem_base, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_s);
+    }
+    // 2. softmax statistics of this block
+    {
+      const bool ok = mbar_wait(bar_s, j & 1);
+      if (__syncthreads_or(!ok)) {
+        report_status(a.status, kStatusTimeoutMma);
+        failed = true;
+        break;
+      }
+    }
+    tc_fence_after();
+    float s[kAttnKvBlock];
+    {
+      uint32_t t0[32], t1[32];
+      tmem_ld_32x32b_x32(tmem_row, t0);
+      tmem_ld_32x32b_x32(tmem_row + 32, t1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        s[c] = __uint_as_float(t0[c]);
+        s[32 + c] = __uint_as_float(t1[c]);
+      }
+    }
+    float mx = -INFINITY;
+    const int kv0 = j * kAttnKvBlock;
+#pragma unroll
+    for (int c = 0; c < kAttnKvBlock; ++c) {
+      const int kvpos = kv0 + c;
+      const bool valid = row_valid && kvpos < len && (!a.causal || kvpos <= qpos);
+      s[c] = valid ? s[c] * a.scale_log2 : -INFINITY;
+      mx = fmaxf(mx, s[c]);
+    }
+    // 3. previous P·V finished: its K/V/P slots are free and O may be touched
+    if (j > 0) {
+      const bool ok = mbar_wait(bar_o, (j - 1) & 1);
+      if (__syncthreads_or(!ok)) {
+        report_status(a.status, kStatusTimeoutMma);
+        failed = true;
+        break;
+      }
+      tc_fence_after();
+    }
+    if (tid == 0 && j + 1 < nblk) load_kv(j + 1);
+    // 4. lazy rescale, P -> shared memory
+    const float m_new = fmaxf(m_ref, mx);
+    const bool need = m_new > m_ref + 8.f;
+    if (__any_sync(0xffffffffu, need)) {
+      const float alpha = (m_new == -INFINITY) ? 1.f
+                          : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new));
+      l_sum *= alpha;
+      m_ref = m_new;
+      if (j > 0) {
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+    }
+    const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+    uint8_t* sP = C::P_IN_K ? (sK + buf * C::KV_BYTES) : sPx;
+#pragma unroll
+    for (int c8 = 0; c8 < kAttnKvBlock / 8; ++c8) {
+      float p[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        p[i] = exp2f(s[c8 * 8 + i] - m_use);
+        l_sum += p[i];
+      }
+      uint4 q;
+      q.x = pack_bf16x2(p[0], p[1]);
+      q.y = pack_bf16x2(p[2], p[3]);
+      q.z = pack_bf16x2(p[4], p[5]);
+      q.w = pack_bf16x2(p[6], p[7]);
+      *reinterpret_cast<uint4*>(sP + swz128_offset(r, c8)) = q;
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // 5. O += P V
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sP);
+      const uint32_t va = smem_u32(sV + buf * C::KV_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < kAttnKvBlock / 16; ++ks) {
+        const uint64_t ad = umma_smem_desc(pa + ks * 32, 16, 1024);
+        const uint64_t bd = umma_smem_desc(va + ks * 2048, kAttnKvBlock * 128, 1024);
+        umma_bf16(tmem_base + C::O_COL, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+      }
+      umma_commit(bar_o);
+    }
+  }
+
+  if (!failed) {
+    const bool ok = mbar_wait(bar_o, (nblk - 1) & 1);
+    if (__syncthreads_or(!ok)) {
+      report_status(a.status, kStatusTimeoutMma);
+      failed = true;
+    }
+  }
+  if (!failed) {
+    tc_fence_after();
+    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+    const long long tok = 1LL * seq0 + qpos;
+    bf16* orow = a.O + tok * a.ldo + (hk * G + g) * HD;
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
+      tmem_ld_wait();
+      if (row_valid) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+          q.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+          q.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+          q.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = q;
+        }
+      }
+    }
+    if (row_valid && a.lse != nullptr)
+      a.lse[1LL * (hk * G + g) * a.T + tok] =
+          (l_sum > 0.f) ? (m_ref * kLn2F + logf(l_sum)) : -INFINITY;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// One block: prefix over sequences -> (sequence, tile) list. plan[0] = tile count.
+__global__ void attn_plan_kernel(const int* __restrict__ cu, int B, int tile_tokens,
+                                 int* __restrict__ plan, int capacity) {
+  __shared__ int s_base;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < B; b0 += blockDim.x) {
+    const int b = b0 + threadIdx.x;
+    int nt = 0;
+    if (b < B) nt = (cu[b + 1] - cu[b] + tile_tokens - 1) / tile_tokens;
+    // inclusive scan over the block (simple Hillis-Steele in shared memory)
+    __shared__ int scan[256];
+    scan[threadIdx.x] = nt;
+    __syncthreads();
+    for (int o = 1; o < blockDim.x; o <<= 1) {
+      int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
+      __syncthreads();
+      scan[threadIdx.x] += v;
+      __syncthreads();
+    }
+    const int start = s_base + scan[threadIdx.x] - nt;
+    for (int t = 0; t < nt; ++t) {
+      if (start + t < capacity) {
+        plan[1 + 2 * (start + t)] = b;
+        plan[2 + 2 * (start + t)] = t;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) s_base += scan[threadIdx.x];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) plan[0] = s_base < capacity ? s_base : capacity;
+}
+
+template <int HD>
+int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+               const AttnFwdArgs& a, int max_tiles, cudaStream_t st) {
+  using C = FwdCfg<HD>;
+  auto kern = attn_fwd_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
+        cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  dim3 grid(max_tiles, a.Hk);
+  kern<<<grid, 128, C::SMEM_BYTES, st>>>(tmQ, tmK, tmV, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace
+}  // namespace lb
+
+using namespace lb;
+
+// plan: int32 [1 + 2 * capacity]; capacity >= ceil(T / tile_tokens) + B always suffices.
+extern "C" int lb_attn_plan(const int* cu_seqlens, int B, int tile_tokens, int* plan, int capacity,
+                            void* stream) {
+  if (B <= 0) return -3;
+  attn_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(cu_seqlens, B, tile_tokens,
+                                                                         plan, capacity);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// q: [T, Hq, hd] with token stride ldq (elements); k, v: [T, Hk, hd] with strides ldk, ldv.
+// plan was built with tile_tokens = 128 / (Hq / Hk). o: [T, Hq, hd] stride ldo; lse: [Hq, T] fp32.
+extern "C" int lb_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                           long long ldv, const int* cu_seqlens, const int* plan, int max_tiles,
+                           void* o, long long ldo, float* lse, int T, int Hq, int Hk, int hd,
+                           float softmax_scale, int causal, int* status, void* stream) {
+  if (T <= 0 || max_tiles <= 0) return 0;
+  if (Hk <= 0 || Hq % Hk != 0) return -3;
+  const int G = Hq / Hk;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
+  if ((ldq | ldk | ldv | ldo) & 7) return -3;
+  const int QT = 128 / G;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tmap_2d(&tmQ, q, 2, (uint64_t)Hq * hd, (uint64_t)T, (uint64_t)ldq * 2, 64, QT, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmK, k, 2, (uint64_t)Hk * hd, (uint64_t)T, (uint64_t)ldk * 2, 64, kAttnKvBlock,
+                    true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * hd, (uint64_t)T, (uint64_t)ldv * 2, 64, kAttnKvBlock,
+                    true);
+  if (rc) return rc;
+  AttnFwdArgs a{cu_seqlens, plan, (bf16*)o, ldo, lse, T, Hq, Hk, softmax_scale * kLog2eF, causal,
+                status};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (hd == 128) return launch_fwd<128>(tmQ, tmK, tmV, a, max_tiles, st);
+  if (hd == 64) return launch_fwd<64>(tmQ, tmK, tmV, a, max_tiles, st);
+  if (hd == 256) return launch_fwd<256>(tmQ, tmK, tmV, a, max_tiles, st);
+  return -3;
+}

@@ -1,0 +1,425 @@
+// RMSNorm and LayerNorm, forward and backward, each with an optional fused residual add.
+//
+//   rms  : nr = bf16(r + a) (when a residual is given);  rstd = rsqrt(mean(nr^2) + eps);
+//          y = bf16(nr * rstd) * (w + w_off)          (w_off = 1 for Gemma's "(1 + w)" weights)
+//   ln   : same with mean subtraction and a bias.
+// The normalised value is rounded to bf16 before the weight multiply, and the weight gradient
+// accumulates dy * bf16(xhat) in fp32: the rounding points of the reference kernels
+// (lset/kernels/rmsnorm.py:68-73,99-114; lset/kernels/residual_rmsnorm.py:58-77;
+// lset/kernels/layernorm.py:73-77; lset/kernels/residual_layernorm.py:46-139).
+//
+// Backward runs on a persistent grid; every CTA writes one fp32 partial row of dW (and dB) to a
+// caller-provided scratch buffer, and a second small kernel sums the partials.
+#include "../common/row.cuh"
+
+namespace lb {
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+template <int TPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+    rms_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res_in,
+                   const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ res_out,
+                   float* __restrict__ rstd_out, int N, int H, float eps, float w_off) {
+  __shared__ float sred[8];
+  constexpr int ROWS = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int r = threadIdx.x / TPR;
+  float wv[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+    if (idx < H) {
+      unpack8(ld16(w + idx), wv[v]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wv[v][i] += w_off;
+    }
+  }
+  for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
+    const long long row = row0 + r;
+    const bool valid = row < N;
+    float xv[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        unpack8(ld16(x + row * H + idx), xv[v]);
+        if (res_in != nullptr) {
+          float rv[8];
+          unpack8(ld16(res_in + row * H + idx), rv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xv[v][i] = bf16_round(xv[v][i] + rv[i]);
+          st16(res_out + row * H + idx, pack8(xv[v]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += xv[v][i] * xv[v][i];
+      }
+    }
+    ss = row_sum<TPR>(ss, sred);
+    const float rstd = rsqrtf(ss / float(H) + eps);
+    if (valid && t == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = bf16_round(xv[v][i] * rstd) * wv[v][i];
+        st16(y + row * H + idx, pack8(o));
+      }
+    }
+  }
+}
+
+template <int TPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+    rms_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dres,
+                   const bf16* __restrict__ xin, const bf16* __restrict__ w,
+                   const float* __restrict__ rstd_in, bf16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int N, int H, float w_off) {
+  __shared__ float sred[8];
+  extern __shared__ float sdw[];
+  constexpr int ROWS = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int r = threadIdx.x / TPR;
+  float wv[NV][8], dwacc[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[v][i] = 0.f;
+    if (idx < H) {
+      unpack8(ld16(w + idx), wv[v]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wv[v][i] += w_off;
+    }
+  }
+  for (int i = threadIdx.x; i < H; i += kRowThreads) sdw[i] = 0.f;
+
+  for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
+    const long long row = row0 + r;
+    const bool valid = row < N;
+    const float rstd = valid ? rstd_in[row] : 0.f;
+    float xh[NV][8], m[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float g[8];
+        unpack8(ld16(xin + row * H + idx), xh[v]);
+        unpack8(ld16(dy + row * H + idx), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[v][i] *= rstd;
+          m[v][i] = g[i] * wv[v][i];
+          dot += m[v][i] * xh[v][i];
+          dwacc[v][i] += g[i] * bf16_round(xh[v][i]);
+        }
+      }
+    }
+    dot = row_sum<TPR>(dot, sred) / float(H);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (m[v][i] - xh[v][i] * dot);
+        if (dres != nullptr) {
+          float dr[8];
+          unpack8(ld16(dres + row * H + idx), dr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += dr[i];
+        }
+        st16(dx + row * H + idx, pack8(o));
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+    if (idx < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&sdw[idx + i], dwacc[v][i]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += kRowThreads) dw_partial[1LL * blockIdx.x * H + i] = sdw[i];
+}
+
+template <int TPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+    ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res_in,
+                  const bf16* __restrict__ w, const bf16* __restrict__ b, bf16* __restrict__ y,
+                  bf16* __restrict__ res_out, float* __restrict__ mean_out,
+                  float* __restrict__ rstd_out, int N, int H, float eps) {
+  __shared__ float sred[8];
+  constexpr int ROWS = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int r = threadIdx.x / TPR;
+  float wv[NV][8], bv[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+    if (idx < H) {
+      unpack8(ld16(w + idx), wv[v]);
+      if (b != nullptr) {
+        unpack8(ld16(b + idx), bv[v]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bv[v][i] = 0.f;
+      }
+    }
+  }
+  for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
+    const long long row = row0 + r;
+    const bool valid = row < N;
+    float xv[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        unpack8(ld16(x + row * H + idx), xv[v]);
+        if (res_in != nullptr) {
+          float rv[8];
+          unpack8(ld16(res_in + row * H + idx), rv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xv[v][i] = bf16_round(xv[v][i] + rv[i]);
+          st16(res_out + row * H + idx, pack8(xv[v]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += xv[v][i];
+      }
+    }
+    const float mean = row_sum<TPR>(s, sred) / float(H);
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = xv[v][i] - mean;
+          ss += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(row_sum<TPR>(ss, sred) / float(H) + eps);
+    if (valid && t == 0) {
+      if (mean_out != nullptr) mean_out[row] = mean;
+      if (rstd_out != nullptr) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          o[i] = bf16_round((xv[v][i] - mean) * rstd) * wv[v][i] + bv[v][i];
+        st16(y + row * H + idx, pack8(o));
+      }
+    }
+  }
+}
+
+template <int TPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+    ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dres,
+                  const bf16* __restrict__ xin, const bf16* __restrict__ w,
+                  const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                  bf16* __restrict__ dx, float* __restrict__ dwb_partial, int N, int H) {
+  __shared__ float sred[8];
+  extern __shared__ float sdw[];  // [2, H]: dW then dB
+  constexpr int ROWS = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int r = threadIdx.x / TPR;
+  float wv[NV][8], dwacc[NV][8], dbacc[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[v][i] = dbacc[v][i] = 0.f;
+    if (idx < H) unpack8(ld16(w + idx), wv[v]);
+  }
+  for (int i = threadIdx.x; i < 2 * H; i += kRowThreads) sdw[i] = 0.f;
+
+  for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
+    const long long row = row0 + r;
+    const bool valid = row < N;
+    const float rstd = valid ? rstd_in[row] : 0.f;
+    const float mean = valid ? mean_in[row] : 0.f;
+    float xh[NV][8], m[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float g[8];
+        unpack8(ld16(xin + row * H + idx), xh[v]);
+        unpack8(ld16(dy + row * H + idx), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[v][i] = (xh[v][i] - mean) * rstd;
+          m[v][i] = g[i] * wv[v][i];
+          s1 += m[v][i];
+          s2 += m[v][i] * xh[v][i];
+          dwacc[v][i] += g[i] * bf16_round(xh[v][i]);
+          dbacc[v][i] += g[i];
+        }
+      }
+    }
+    s1 = row_sum<TPR>(s1, sred) / float(H);
+    s2 = row_sum<TPR>(s2, sred) / float(H);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (m[v][i] - s1 - xh[v][i] * s2);
+        if (dres != nullptr) {
+          float dr[8];
+          unpack8(ld16(dres + row * H + idx), dr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += dr[i];
+        }
+        st16(dx + row * H + idx, pack8(o));
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int idx = (v * TPR + t) * 8;
+    if (idx < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(&sdw[idx + i], dwacc[v][i]);
+        atomicAdd(&sdw[H + idx + i], dbacc[v][i]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * H; i += kRowThreads)
+    dwb_partial[1LL * blockIdx.x * 2 * H + i] = sdw[i];
+}
+
+// out[c] (+)= sum_p partial[p, c]; one thread per column, coalesced across the warp.
+__global__ void colsum_kernel(const float* __restrict__ partial, int P, int C, void* out,
+                              int out_fp32, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[1LL * p * C + c];
+  if (out_fp32) {
+    float* o = reinterpret_cast<float*>(out);
+    o[c] = accumulate ? o[c] + s : s;
+  } else {
+    bf16* o = reinterpret_cast<bf16*>(out);
+    o[c] = __float2bfloat16_rn(accumulate ? __bfloat162float(o[c]) + s : s);
+  }
+}
+
+int bwd_grid(int N, int rows_per_cta) {
+  const int need = (N + rows_per_cta - 1) / rows_per_cta;
+  const int cap = row_num_sms() * 2;
+  return need < cap ? (need > 0 ? need : 1) : cap;
+}
+
+}  // namespace
+}  // namespace lb
+
+using namespace lb;
+
+// Number of fp32 partial rows that the backward kernels may write (scratch = rows * H floats for
+// RMSNorm, rows * 2H for LayerNorm).
+extern "C" int lb_norm_bwd_partial_rows() { return row_num_sms() * 2; }
+
+extern "C" int lb_rms_norm_fwd(const void* x, const void* res_in, const void* w, void* y,
+                               void* res_out, float* rstd, int N, int H, float eps, float w_off,
+                               void* stream) {
+  if (N <= 0) return 0;
+  if (H & 7) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    const int grid = (N + ROWS - 1) / ROWS;
+    rms_fwd_kernel<TPR, NV><<<grid, kRowThreads, 0, st>>>(
+        (const bf16*)x, (const bf16*)res_in, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, N, H,
+        eps, w_off);
+  });
+  return launch_rc();
+}
+
+// dw_out: [H] fp32 or bf16; scratch: lb_norm_bwd_partial_rows() * H floats.
+extern "C" int lb_rms_norm_bwd(const void* dy, const void* dres, const void* xin, const void* w,
+                               const float* rstd, void* dx, float* scratch, void* dw_out,
+                               int dw_fp32, int dw_accumulate, int N, int H, float w_off,
+                               void* stream) {
+  if (N <= 0) return 0;
+  if (H & 7) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = 1;
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    grid = bwd_grid(N, ROWS);
+    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
+        (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
+        scratch, N, H, w_off);
+  });
+  if (dw_out != nullptr)
+    colsum_kernel<<<(H + 127) / 128, 128, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
+  return launch_rc();
+}
+
+extern "C" int lb_layer_norm_fwd(const void* x, const void* res_in, const void* w, const void* b,
+                                 void* y, void* res_out, float* mean, float* rstd, int N, int H,
+                                 float eps, void* stream) {
+  if (N <= 0) return 0;
+  if (H & 7) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    const int grid = (N + ROWS - 1) / ROWS;
+    ln_fwd_kernel<TPR, NV><<<grid, kRowThreads, 0, st>>>(
+        (const bf16*)x, (const bf16*)res_in, (const bf16*)w, (const bf16*)b, (bf16*)y,
+        (bf16*)res_out, mean, rstd, N, H, eps);
+  });
+  return launch_rc();
+}
+
+// dwb_out: [2, H] (dW then dB), fp32 or bf16; scratch: lb_norm_bwd_partial_rows() * 2H floats.
+extern "C" int lb_layer_norm_bwd(const void* dy, const void* dres, const void* xin, const void* w,
+                                 const float* mean, const float* rstd, void* dx, float* scratch,
+                                 void* dwb_out, int dw_fp32, int dw_accumulate, int N, int H,
+                                 void* stream) {
+  if (N <= 0) return 0;
+  if (H & 7) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = 1;
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    grid = bwd_grid(N, ROWS);
+    ln_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
+        (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, mean, rstd, (bf16*)dx,
+        scratch, N, H);
+  });
+  if (dwb_out != nullptr)
+    colsum_kernel<<<(2 * H + 127) / 128, 128, 0, st>>>(scratch, grid, 2 * H, dwb_out, dw_fp32,
+                                                       dw_accumulate);
+  return launch_rc();
+}
+
+extern "C" int lb_colsum(const float* partial, int P, int C, void* out, int out_fp32,
+                         int accumulate, void* stream) {
+  if (C <= 0) return 0;
+  colsum_kernel<<<(C + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      partial, P, C, out, out_fp32, accumulate);
+  return launch_rc();
+}

@@ -1,0 +1,172 @@
+"""Varlen (packed) attention on the native tcgen05 kernels, plus the eager oracle.
+
+``AttnPlan`` is built once per packed batch from ``cu_seqlens`` (a device-side planning kernel, no
+host sync) and reused by every layer's forward and backward. Padded batches are handled by the
+same kernels: a ``[B, S]`` batch is a packed stream with ``cu_seqlens = arange(B+1) * S`` when
+there is no padding, or is packed by its attention mask.
+
+Replaces flash_attn_varlen_func / torch varlen_attn / SDPA of the reference
+(lset/models/decoder/qwen3/attention.py:112-115,169-272).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as nv
+
+
+class AttnPlan:
+    """Tile lists for one packed batch. ``cu_seqlens``: int32 ``[B+1]`` on the device."""
+
+    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int, total_tokens: int):
+        self.cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
+        self.max_seqlen = int(max_seqlen)
+        self.T = int(total_tokens)
+        self.B = int(cu_seqlens.numel() - 1)
+        self._plans = {}
+
+    def tiles(self, tile_tokens: int):
+        """(plan tensor, capacity) for a tile of ``tile_tokens`` tokens."""
+        hit = self._plans.get(tile_tokens)
+        if hit is not None:
+            return hit
+        cap = (self.T + tile_tokens - 1) // tile_tokens + self.B
+        plan = torch.empty(1 + 2 * cap, dtype=torch.int32, device=self.cu_seqlens.device)
+        rc = nv.load().lb_attn_plan(nv.c_void_p(self.cu_seqlens.data_ptr()), nv.c_int(self.B),
+                                    nv.c_int(tile_tokens), nv.c_void_p(plan.data_ptr()),
+                                    nv.c_int(cap), nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_attn_plan")
+        nv.count_launch()
+        self._plans[tile_tokens] = (plan, cap)
+        return plan, cap
+
+
+def attention_ref(q, k, v, cu_seqlens, causal: bool, scale: float | None = None):
+    """Eager oracle: per-sequence softmax attention in fp32. q: [T,Hq,hd]; k, v: [T,Hk,hd]."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    out = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
+    cu = cu_seqlens.tolist()
+    rep = Hq // Hk
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
+        if e <= s:
+            continue
+        qs = q[s:e].float().transpose(0, 1)
+        ks = k[s:e].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vs = v[s:e].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        att = torch.matmul(qs, ks.transpose(1, 2)) * scale
+        if causal:
+            L = e - s
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            att = att.masked_fill(~mask, float("-inf"))
+        out[s:e] = torch.matmul(att.softmax(-1), vs).transpose(0, 1).to(q.dtype)
+    return out
+
+
+def _native_fwd(q, k, v, plan: AttnPlan, causal, scale):
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    G = Hq // Hk
+    ptiles, cap = plan.tiles(128 // G)
+    o = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    rc = nv.load().lb_attn_fwd(
+        nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
+        nv.c_ll(k.stride(0)), nv.c_void_p(v.data_ptr()), nv.c_ll(v.stride(0)),
+        nv.c_void_p(plan.cu_seqlens.data_ptr()), nv.c_void_p(ptiles.data_ptr()), nv.c_int(cap),
+        nv.c_void_p(o.data_ptr()), nv.c_ll(Hq * hd), nv.c_void_p(lse.data_ptr()), nv.c_int(T),
+        nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd), nv.c_float(scale), nv.c_int(int(causal)),
+        nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
+    nv.check_rc(rc, "lb_attn_fwd")
+    nv.count_launch()
+    return o, lse
+
+
+def _native_bwd(do, q, k, v, o, lse, plan: AttnPlan, causal, scale, dq, dk, dv):
+    """Writes dq [T,Hq,hd], dk, dv [T,Hk,hd] (strided views allowed, unit inner stride)."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    G = Hq // Hk
+    lib = nv.load()
+    delta = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    ptq, capq = plan.tiles(128 // G)
+    ptk, capk = plan.tiles(128)
+    rc = lib.lb_attn_bwd(
+        nv.c_void_p(do.data_ptr()), nv.c_ll(do.stride(0)), nv.c_void_p(q.data_ptr()),
+        nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()), nv.c_ll(k.stride(0)),
+        nv.c_void_p(v.data_ptr()), nv.c_ll(v.stride(0)), nv.c_void_p(o.data_ptr()),
+        nv.c_ll(o.stride(0)), nv.c_void_p(lse.data_ptr()), nv.c_void_p(delta.data_ptr()),
+        nv.c_void_p(plan.cu_seqlens.data_ptr()), nv.c_void_p(ptq.data_ptr()), nv.c_int(capq),
+        nv.c_void_p(ptk.data_ptr()), nv.c_int(capk), nv.c_void_p(dq.data_ptr()),
+        nv.c_ll(dq.stride(0)), nv.c_void_p(dk.data_ptr()), nv.c_ll(dk.stride(0)),
+        nv.c_void_p(dv.data_ptr()), nv.c_ll(dv.stride(0)), nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk),
+        nv.c_int(hd), nv.c_float(scale), nv.c_int(int(causal)),
+        nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
+    nv.check_rc(rc, "lb_attn_bwd")
+    nv.count_launch(3)
+
+
+def _unit_inner(t):
+    return t if (t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0) \
+        else t.contiguous()
+
+
+class _VarlenAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, plan, causal, scale):
+        q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
+        o, lse = _native_fwd(q, k, v, plan, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.plan, ctx.causal, ctx.scale = plan, causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        do = do if do.is_contiguous() else do.contiguous()
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        _native_bwd(do, q, k, v, o, lse, ctx.plan, ctx.causal, ctx.scale, dq, dk, dv)
+        return dq, dk, dv, None, None, None
+
+
+def native_supported(q, k) -> bool:
+    if not (nv.use_native(q, k) and q.dtype == torch.bfloat16):
+        return False
+    Hq, hd = q.shape[1], q.shape[2]
+    Hk = k.shape[1]
+    return hd in (64, 128, 256) and Hq % Hk == 0 and (Hq // Hk) in (1, 2, 4, 8)
+
+
+def varlen_attention(q, k, v, plan: AttnPlan, causal: bool, scale: float | None = None):
+    """Attention over a packed token stream. q: ``[T,Hq,hd]``, k/v: ``[T,Hk,hd]``; sequences are
+    delimited by ``plan.cu_seqlens``. Returns ``[T,Hq,hd]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if native_supported(q, k):
+        return _VarlenAttn.apply(q, k, v, plan, bool(causal), float(scale))
+    return attention_ref(q, k, v, plan.cu_seqlens, causal, scale)
+
+
+def padded_attention_ref(q, k, v, attn_mask, causal: bool, scale: float | None = None):
+    """Oracle for padded batches. q: [B,S,Hq,hd]; k, v: [B,S,Hk,hd]; attn_mask: [B,S] 1 = token."""
+    B, S, Hq, hd = q.shape
+    Hk = k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    qf = q.transpose(1, 2).float()
+    kf = k.transpose(1, 2).float().repeat_interleave(Hq // Hk, dim=1)
+    vf = v.transpose(1, 2).float().repeat_interleave(Hq // Hk, dim=1)
+    att = torch.matmul(qf, kf.transpose(2, 3)) * scale
+    neg = torch.finfo(torch.float32).min
+    if causal:
+        tri = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        att = att.masked_fill(~tri, neg)
+    if attn_mask is not None:
+        att = att.masked_fill(~attn_mask.bool()[:, None, None, :], neg)
+    out = torch.matmul(att.softmax(-1), vf)
+    return out.transpose(1, 2).to(q.dtype)
