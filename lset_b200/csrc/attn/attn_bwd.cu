@@ -51,7 +51,8 @@ __global__ void __launch_bounds__(256)
 }
 
 struct AttnBwdArgs {
-  const int* cu_seqlens;
+  const int* seq_start;  // first token of each sequence
+  const int* seq_end;    // one past its last token
   const int* plan;
   const float* lse;    // [Hq, T]
   const float* delta;  // [Hq, T]
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(128)
   const int hk = blockIdx.y;
   const int G = a.Hq / a.Hk;
   const int QT = 128 / G;
-  const int seq0 = a.cu_seqlens[b];
-  const int len = a.cu_seqlens[b + 1] - seq0;
+  const int seq0 = a.seq_start[b];
+  const int len = a.seq_end[b] - seq0;
   const int q0 = qt * QT;
   const int kv_end = a.causal ? min(len, q0 + QT) : len;
   const int nblk = (kv_end + kAttnKvBlock - 1) / kAttnKvBlock;
@@ -344,8 +345,8 @@ __global__ void __launch_bounds__(128)
   const int kt = plan.tile(blockIdx.x);
   const int hk = blockIdx.y;
   const int G = a.Hq / a.Hk;
-  const int seq0 = a.cu_seqlens[b];
-  const int len = a.cu_seqlens[b + 1] - seq0;
+  const int seq0 = a.seq_start[b];
+  const int len = a.seq_end[b] - seq0;
   const int kv0 = kt * 128;
   const int nqb = (len + 63) / 64;
   const int qb_start = a.causal ? (kv0 / 64) : 0;
@@ -604,7 +605,8 @@ using namespace lb;
 extern "C" int lb_attn_bwd(const void* dO, long long lddo, const void* q, long long ldq,
                            const void* k, long long ldk, const void* v, long long ldv,
                            const void* o, long long ldo, const float* lse, float* delta,
-                           const int* cu_seqlens, const int* plan_q, int cap_q, const int* plan_kv,
+                           const int* seq_start, const int* seq_end, const int* plan_q, int cap_q,
+                           const int* plan_kv,
                            int cap_kv, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                            long long lddv, int T, int Hq, int Hk, int hd, float softmax_scale,
                            int causal, int* status, void* stream) {
@@ -613,7 +615,7 @@ extern "C" int lb_attn_bwd(const void* dO, long long lddo, const void* q, long l
   const int G = Hq / Hk;
   if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
   if ((lddo | ldq | ldk | ldv | ldo | lddq | lddk | lddv) & 7) return -3;
-  AttnBwdArgs a{cu_seqlens, nullptr, lse, delta, (bf16*)dq, lddq, (bf16*)dk, lddk, (bf16*)dv, lddv,
+  AttnBwdArgs a{seq_start, seq_end, nullptr, lse, delta, (bf16*)dq, lddq, (bf16*)dk, lddk, (bf16*)dv, lddv,
                 T, Hq, Hk, softmax_scale, softmax_scale * kLog2eF, causal, status};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (hd == 128)

@@ -21,7 +21,8 @@ namespace {
 using bf16 = __nv_bfloat16;
 
 struct AttnFwdArgs {
-  const int* cu_seqlens;
+  const int* seq_start;  // first token of each sequence
+  const int* seq_end;    // one past its last token
   const int* plan;
   bf16* O;
   long long ldo;   // elements between consecutive tokens of O
@@ -57,8 +58,8 @@ __global__ void __launch_bounds__(128)
   const int hk = blockIdx.y;
   const int G = a.Hq / a.Hk;
   const int QT = 128 / G;
-  const int seq0 = a.cu_seqlens[b];
-  const int len = a.cu_seqlens[b + 1] - seq0;
+  const int seq0 = a.seq_start[b];
+  const int len = a.seq_end[b] - seq0;
   const int q0 = qt * QT;
   const int kv_end = a.causal ? min(len, q0 + QT) : len;
   const int nblk = (kv_end + kAttnKvBlock - 1) / kAttnKvBlock;
@@ -298,7 +299,8 @@ __global__ void __launch_bounds__(128)
 }
 
 // One block: prefix over sequences -> (sequence, tile) list. plan[0] = tile count.
-__global__ void attn_plan_kernel(const int* __restrict__ cu, int B, int tile_tokens,
+__global__ void attn_plan_kernel(const int* __restrict__ seq_start,
+                                 const int* __restrict__ seq_end, int B, int tile_tokens,
                                  int* __restrict__ plan, int capacity) {
   __shared__ int s_base;
   if (threadIdx.x == 0) s_base = 0;
@@ -306,7 +308,7 @@ __global__ void attn_plan_kernel(const int* __restrict__ cu, int B, int tile_tok
   for (int b0 = 0; b0 < B; b0 += blockDim.x) {
     const int b = b0 + threadIdx.x;
     int nt = 0;
-    if (b < B) nt = (cu[b + 1] - cu[b] + tile_tokens - 1) / tile_tokens;
+    if (b < B) nt = max(0, (seq_end[b] - seq_start[b] + tile_tokens - 1) / tile_tokens);
     // inclusive scan over the block (simple Hillis-Steele in shared memory)
     __shared__ int scan[256];
     scan[threadIdx.x] = nt;
@@ -354,18 +356,21 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
 using namespace lb;
 
 // plan: int32 [1 + 2 * capacity]; capacity >= ceil(T / tile_tokens) + B always suffices.
-extern "C" int lb_attn_plan(const int* cu_seqlens, int B, int tile_tokens, int* plan, int capacity,
-                            void* stream) {
+extern "C" int lb_attn_plan(const int* seq_start, const int* seq_end, int B, int tile_tokens,
+                            int* plan, int capacity, void* stream) {
   if (B <= 0) return -3;
-  attn_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(cu_seqlens, B, tile_tokens,
-                                                                         plan, capacity);
+  attn_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(seq_start, seq_end, B,
+                                                                         tile_tokens, plan, capacity);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// Sequence b owns tokens [seq_start[b], seq_end[b]) of the stream (for a packed batch these are
+// cu_seqlens and cu_seqlens + 1; for a padded batch they skip the padding).
 // q: [T, Hq, hd] with token stride ldq (elements); k, v: [T, Hk, hd] with strides ldk, ldv.
 // plan was built with tile_tokens = 128 / (Hq / Hk). o: [T, Hq, hd] stride ldo; lse: [Hq, T] fp32.
 extern "C" int lb_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
-                           long long ldv, const int* cu_seqlens, const int* plan, int max_tiles,
+                           long long ldv, const int* seq_start, const int* seq_end, const int* plan,
+                           int max_tiles,
                            void* o, long long ldo, float* lse, int T, int Hq, int Hk, int hd,
                            float softmax_scale, int causal, int* status, void* stream) {
   if (T <= 0 || max_tiles <= 0) return 0;
@@ -383,7 +388,7 @@ extern "C" int lb_attn_fwd(const void* q, long long ldq, const void* k, long lon
   rc = make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * hd, (uint64_t)T, (uint64_t)ldv * 2, 64, kAttnKvBlock,
                     true);
   if (rc) return rc;
-  AttnFwdArgs a{cu_seqlens, plan, (bf16*)o, ldo, lse, T, Hq, Hk, softmax_scale * kLog2eF, causal,
+  AttnFwdArgs a{seq_start, seq_end, plan, (bf16*)o, ldo, lse, T, Hq, Hk, softmax_scale * kLog2eF, causal,
                 status};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (hd == 128) return launch_fwd<128>(tmQ, tmK, tmV, a, max_tiles, st);

@@ -21,12 +21,31 @@ from . import _native as nv
 class AttnPlan:
     """Tile lists for one packed batch. ``cu_seqlens``: int32 ``[B+1]`` on the device."""
 
-    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int, total_tokens: int):
-        self.cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
+    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int, total_tokens: int,
+                 seq_start: torch.Tensor | None = None, seq_end: torch.Tensor | None = None):
+        self.cu_seqlens = cu_seqlens.to(torch.int32).contiguous() if cu_seqlens is not None else None
+        if seq_start is None:
+            # packed stream: sequence b is [cu[b], cu[b+1])
+            seq_start, seq_end = self.cu_seqlens[:-1], self.cu_seqlens[1:]
+        self.seq_start = seq_start.to(torch.int32)
+        self.seq_end = seq_end.to(torch.int32)
+        assert self.seq_start.stride(0) == 1 and self.seq_end.stride(0) == 1
         self.max_seqlen = int(max_seqlen)
         self.T = int(total_tokens)
-        self.B = int(cu_seqlens.numel() - 1)
+        self.B = int(self.seq_start.numel())
         self._plans = {}
+
+    @classmethod
+    def from_mask(cls, attention_mask: torch.Tensor) -> "AttnPlan":
+        """Plan for a padded ``[B, S]`` batch flattened to ``B*S`` tokens: every row is one sequence
+        that covers only its unmasked (contiguous) span, left- or right-padded. No host sync."""
+        B, S = attention_mask.shape
+        m = attention_mask.to(torch.int32)
+        lens = m.sum(1, dtype=torch.int32)
+        first = torch.argmax(m, dim=1).to(torch.int32)
+        base = torch.arange(B, device=m.device, dtype=torch.int32) * S
+        start = (base + first).contiguous()
+        return cls(None, S, B * S, seq_start=start, seq_end=(start + lens).contiguous())
 
     def tiles(self, tile_tokens: int):
         """(plan tensor, capacity) for a tile of ``tile_tokens`` tokens."""
@@ -34,8 +53,9 @@ class AttnPlan:
         if hit is not None:
             return hit
         cap = (self.T + tile_tokens - 1) // tile_tokens + self.B
-        plan = torch.empty(1 + 2 * cap, dtype=torch.int32, device=self.cu_seqlens.device)
-        rc = nv.load().lb_attn_plan(nv.c_void_p(self.cu_seqlens.data_ptr()), nv.c_int(self.B),
+        plan = torch.empty(1 + 2 * cap, dtype=torch.int32, device=self.seq_start.device)
+        rc = nv.load().lb_attn_plan(nv.c_void_p(self.seq_start.data_ptr()),
+                                    nv.c_void_p(self.seq_end.data_ptr()), nv.c_int(self.B),
                                     nv.c_int(tile_tokens), nv.c_void_p(plan.data_ptr()),
                                     nv.c_int(cap), nv.c_void_p(nv.stream_ptr()))
         nv.check_rc(rc, "lb_attn_plan")
@@ -44,16 +64,21 @@ class AttnPlan:
         return plan, cap
 
 
-def attention_ref(q, k, v, cu_seqlens, causal: bool, scale: float | None = None):
-    """Eager oracle: per-sequence softmax attention in fp32. q: [T,Hq,hd]; k, v: [T,Hk,hd]."""
+def attention_ref(q, k, v, cu_seqlens, causal: bool, scale: float | None = None, seq_end=None):
+    """Eager oracle: per-sequence softmax attention in fp32. q: [T,Hq,hd]; k, v: [T,Hk,hd].
+    Sequences are ``[cu[b], cu[b+1])``, or ``[cu_seqlens[b], seq_end[b])`` when ``seq_end`` is given;
+    tokens outside every sequence get zeros."""
     T, Hq, hd = q.shape
     Hk = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
-    out = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
-    cu = cu_seqlens.tolist()
+    out = torch.zeros(T, Hq, hd, dtype=q.dtype, device=q.device)
+    if seq_end is None:
+        cu = cu_seqlens.tolist()
+        spans = list(zip(cu[:-1], cu[1:]))
+    else:
+        spans = list(zip(cu_seqlens.tolist(), seq_end.tolist()))
     rep = Hq // Hk
-    for b in range(len(cu) - 1):
-        s, e = cu[b], cu[b + 1]
+    for s, e in spans:
         if e <= s:
             continue
         qs = q[s:e].float().transpose(0, 1)
@@ -73,12 +98,15 @@ def _native_fwd(q, k, v, plan: AttnPlan, causal, scale):
     Hk = k.shape[1]
     G = Hq // Hk
     ptiles, cap = plan.tiles(128 // G)
-    o = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
+    # tokens outside every sequence (padding) are never written by the kernel: keep them zero
+    o = (torch.empty if plan.cu_seqlens is not None else torch.zeros)(
+        T, Hq, hd, dtype=q.dtype, device=q.device)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
     rc = nv.load().lb_attn_fwd(
         nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
         nv.c_ll(k.stride(0)), nv.c_void_p(v.data_ptr()), nv.c_ll(v.stride(0)),
-        nv.c_void_p(plan.cu_seqlens.data_ptr()), nv.c_void_p(ptiles.data_ptr()), nv.c_int(cap),
+        nv.c_void_p(plan.seq_start.data_ptr()), nv.c_void_p(plan.seq_end.data_ptr()),
+        nv.c_void_p(ptiles.data_ptr()), nv.c_int(cap),
         nv.c_void_p(o.data_ptr()), nv.c_ll(Hq * hd), nv.c_void_p(lse.data_ptr()), nv.c_int(T),
         nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd), nv.c_float(scale), nv.c_int(int(causal)),
         nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
@@ -101,7 +129,8 @@ def _native_bwd(do, q, k, v, o, lse, plan: AttnPlan, causal, scale, dq, dk, dv):
         nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()), nv.c_ll(k.stride(0)),
         nv.c_void_p(v.data_ptr()), nv.c_ll(v.stride(0)), nv.c_void_p(o.data_ptr()),
         nv.c_ll(o.stride(0)), nv.c_void_p(lse.data_ptr()), nv.c_void_p(delta.data_ptr()),
-        nv.c_void_p(plan.cu_seqlens.data_ptr()), nv.c_void_p(ptq.data_ptr()), nv.c_int(capq),
+        nv.c_void_p(plan.seq_start.data_ptr()), nv.c_void_p(plan.seq_end.data_ptr()),
+        nv.c_void_p(ptq.data_ptr()), nv.c_int(capq),
         nv.c_void_p(ptk.data_ptr()), nv.c_int(capk), nv.c_void_p(dq.data_ptr()),
         nv.c_ll(dq.stride(0)), nv.c_void_p(dk.data_ptr()), nv.c_ll(dk.stride(0)),
         nv.c_void_p(dv.data_ptr()), nv.c_ll(dv.stride(0)), nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk),
@@ -148,9 +177,12 @@ def varlen_attention(q, k, v, plan: AttnPlan, causal: bool, scale: float | None 
     """Attention over a packed token stream. q: ``[T,Hq,hd]``, k/v: ``[T,Hk,hd]``; sequences are
     delimited by ``plan.cu_seqlens``. Returns ``[T,Hq,hd]``."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if native_supported(q, k):
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    # The dK/dV kernel keeps two head_dim-wide accumulators in TMEM: head_dim 256 does not fit, so
+    # training at that width runs the eager path (inference still uses the native forward).
+    if native_supported(q, k) and not (needs_grad and q.shape[-1] > 128):
         return _VarlenAttn.apply(q, k, v, plan, bool(causal), float(scale))
-    return attention_ref(q, k, v, plan.cu_seqlens, causal, scale)
+    return attention_ref(q, k, v, plan.seq_start, causal, scale, seq_end=plan.seq_end)
 
 
 def padded_attention_ref(q, k, v, attn_mask, causal: bool, scale: float | None = None):

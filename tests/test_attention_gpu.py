@@ -64,3 +64,24 @@ def test_backward(lens, Hq, Hk, hd, causal):
         err = (a.float() - b).abs().max().item()
         scale = b.abs().max().item() + 1e-6
         assert err / scale < 3e-2, (name, err, scale)
+
+
+@pytest.mark.parametrize("left", [True, False])
+def test_padded_plan(left):
+    torch.manual_seed(3)
+    B, S, Hq, Hk, hd = 3, 96, 4, 2, 128
+    lens = [96, 40, 7]
+    mask = torch.zeros(B, S, dtype=torch.long, device="cuda")
+    for b, L in enumerate(lens):
+        if left:
+            mask[b, S - L:] = 1
+        else:
+            mask[b, :L] = 1
+    plan = AttnPlan.from_mask(mask)
+    q = torch.randn(B * S, Hq, hd, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B * S, Hk, hd, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B * S, Hk, hd, device="cuda").to(torch.bfloat16)
+    o = varlen_attention(q, k, v, plan, True)
+    nv.check_status()
+    ref = attention_ref(q.float(), k.float(), v.float(), plan.seq_start, True, seq_end=plan.seq_end)
+    assert (o.float() - ref).abs().max().item() < 3e-2
