@@ -1,0 +1,435 @@
+"""Headline benchmark: contrastive training throughput of the Qwen3-0.6B embedder (bf16, packed
+sequences, sharded data parallel), pairs/s and tokens/s on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref
+
+Per GPU and step: 64 (query, positive) pairs, query lengths U[16,64], passage lengths U[128,512],
+token ids U[0,151642), random N(0,0.02) weights, InfoNCE at temperature 0.02 over the global
+in-batch negatives, AdamW, gradient clipping at 1.0. Weak scaling: the global batch grows with N.
+
+Two timed regions of K steps each, after W warm-up steps, both bracketed by a barrier and a
+device synchronisation and timed with CUDA events (max over ranks):
+  * device: batches already resident on the GPU  -> "value" / "ms_per_step"
+  * e2e:    ``TrainingEngine.train_step`` on pinned host batches (H2D copy of the step's inputs) plus
+            a device->host read of the step's loss every step -> "e2e"
+Every step touches several GB of weights, optimizer state and activations, far more than the
+126 MB L2, so no explicit L2 flush is needed between steps (stated in "config").
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+MODEL = dict(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+             num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+             max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1_000_000.0,
+             tie_word_embeddings=True, attention_bias=False)
+PAIRS_PER_GPU = 64
+QUERY_LEN = (16, 64)
+DOC_LEN = (128, 512)
+TOKEN_ID_MAX = 151642
+TEMPERATURE = 0.02
+LR = 2e-5
+PUBLISHED_BASELINE = None  # the reference publishes no throughput number
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self._t = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self._t = threading.Thread(target=self._pump, daemon=True)
+        self._t.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# data
+# ----------------------------------------------------------------------------------------------
+def make_samples(n_batches: int, rank: int, seed: int = 1234):
+    """Pre-tokenised samples: ``n_batches * PAIRS_PER_GPU`` (query, positive) dicts for one rank."""
+    import torch
+
+    gen = torch.Generator().manual_seed(seed + 7919 * rank)
+    out = []
+    for _ in range(n_batches * PAIRS_PER_GPU):
+        ql = int(torch.randint(QUERY_LEN[0], QUERY_LEN[1] + 1, (1,), generator=gen))
+        dl = int(torch.randint(DOC_LEN[0], DOC_LEN[1] + 1, (1,), generator=gen))
+        q = torch.randint(0, TOKEN_ID_MAX, (ql,), generator=gen).tolist()
+        d = torch.randint(0, TOKEN_ID_MAX, (dl,), generator=gen).tolist()
+        out.append({"query": {"input_ids": q, "attention_mask": [1] * ql},
+                    "positive": {"input_ids": d, "attention_mask": [1] * dl}})
+    return out
+
+
+class ListDataset:
+    def __init__(self, items):
+        self.items = items
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        return self.items[i]
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+def max_over_ranks(value: float, device) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return value
+
+
+def sum_over_ranks(value: float, device) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+    return value
+
+
+def barrier_sync(device):
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+
+
+def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, launches, extra_cfg):
+    pairs_s = pairs / (ms / 1e3)
+    line = {
+        "metric": "pairs/sec & tokens/sec, Qwen3-0.6B embed FSDP2 bf16, 1/2/4/8 B200, max over ranks",
+        "value": pairs_s, "unit": "pairs/s", "tokens_per_sec": tokens / (ms / 1e3),
+        "n_gpus": n_gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (pairs_s / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
+        "dtype": "bf16", "data": "synthetic", "impl": impl,
+        "config": dict({
+            "model": "Qwen3-0.6B (28L, H1024, 16q/8kv heads, hd128, FFN3072, vocab 151936), random init",
+            "global_batch": PAIRS_PER_GPU * n_gpus, "pairs_per_gpu": PAIRS_PER_GPU,
+            "seq_len": "query U[16,64], passage U[128,512], packed varlen stream (cu_seqlens)",
+            "parallelism": f"dp{n_gpus}" + (" (sharded optimizer/grad, ZeRO)" if n_gpus > 1 else ""),
+            "loss": "InfoNCE T=0.02, global in-batch negatives", "optimizer": "AdamW lr 2e-5, clip 1.0",
+            "l2": "per-step working set (weights+optimizer+activations, several GB) exceeds the "
+                  "126 MB L2; no explicit flush",
+            "timing": "CUDA events on the launching stream, max over ranks, barrier+sync both sides",
+        }, **extra_cfg),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+    }
+    return line
+
+
+# ----------------------------------------------------------------------------------------------
+# this framework
+# ----------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    from lset_b200.models import Qwen3Config
+    from lset_b200.ops import _native as nv
+    from lset_b200.train.data.collator import PackedCollator
+    from lset_b200.train.engine import TrainingEngine, batch_bytes, pin, to_device
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    nv.load()
+    K, W = args.steps, args.warmup
+    engine = TrainingEngine(
+        "qwen3", None, dataset=None, dp_size=world, tp_size=1, batch_size=PAIRS_PER_GPU, lr=LR,
+        max_steps=10**9, grad_clip=1.0, temperature=TEMPERATURE, packed=True, log_interval=0,
+        scheduler_type="constant", model_config=Qwen3Config(**MODEL), fused_projections=True,
+        collator=PackedCollator())
+    device = engine.device
+    n_batches = W + 2 * K
+    samples = make_samples(n_batches, rank)
+    coll = PackedCollator()
+    host = [pin(coll(samples[i * PAIRS_PER_GPU:(i + 1) * PAIRS_PER_GPU])) for i in range(n_batches)]
+    tokens = [int(b["query"]["input_ids"].numel() + b["doc"]["input_ids"].numel()) for b in host]
+
+    for i in range(W):
+        engine.train_step(host[i]).item()
+    nv.check_status(device)
+
+    # ---- device-timed region: inputs staged on the GPU beforehand
+    staged = [to_device(host[W + i], device) for i in range(K)]
+    barrier_sync(device)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    nv.reset_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        engine.forward_backward(staged[i], True)
+        engine.optimizer_step()
+        engine.micro_step += 1
+    e1.record()
+    barrier_sync(device)
+    ms_dev = max_over_ranks(e0.elapsed_time(e1) / K, device)
+    launches = nv.launches()
+    tok_dev = sum_over_ranks(float(sum(tokens[W:W + K])) / K, device)
+    del staged
+
+    # ---- end-to-end region: pinned host batch -> H2D -> step -> loss read back, every step
+    barrier_sync(device)
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    last = 0.0
+    for i in range(K):
+        last = engine.train_step(host[W + K + i]).item()
+    e3.record()
+    barrier_sync(device)
+    clocks = sampler.stop()
+    ms_e2e = max_over_ranks(e2.elapsed_time(e3) / K, device)
+    nv.check_status(device)
+    h2d = sum(batch_bytes(b) for b in host[W + K:W + 2 * K]) / K
+    pairs = PAIRS_PER_GPU * world
+    e2e = {"value": pairs / (ms_e2e / 1e3), "unit": "pairs/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "last_loss": last,
+           "api": "lset_b200.train.engine.TrainingEngine.train_step(pinned host batch) + loss.item()"}
+    if rank == 0:
+        print(json.dumps(result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e,
+                                     launches,
+                                     {"fused_projections": True, "native_library": str(nv.lib_path().name)})))
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------
+# reference arm: the unmodified reference package from baseline/_ref, through its own engine
+# ----------------------------------------------------------------------------------------------
+def run_reference(args):
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "lset")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lset is not installed"}))
+        return
+    try:
+        import torch
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        sys.path.insert(0, ref_root)
+        import lset  # noqa: F401
+        from lset.train.data.packed_collator import PackedCollator as RefPacked
+        from lset.train.engine import TrainingEngine as RefEngine
+    except Exception as exc:  # pragma: no cover - depends on the box
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {exc!r}"[:300]}))
+        return
+    import torch.distributed as dist
+
+    rank, local_rank, world = dist_env()
+    K, W = args.steps, args.warmup
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+
+    # The reference engine loads a checkpoint directory: write config.json and random N(0, 0.02)
+    # weights once (rank 0) and let the other ranks wait for the marker file.
+    model_dir = os.path.join(tempfile.gettempdir(), f"lset_ref_qwen3_06b_{os.environ.get('MASTER_PORT', '0')}")
+    marker = os.path.join(model_dir, "READY")
+    if rank == 0 and not os.path.exists(marker):
+        os.makedirs(model_dir, exist_ok=True)
+        cfg = dict(MODEL, model_type="qwen3", architectures=["Qwen3ForCausalLM"])
+        with open(os.path.join(model_dir, "config.json"), "w") as fh:
+            json.dump(cfg, fh)
+        from lset.models import get_model_spec
+        from safetensors.torch import save_file
+
+        spec = get_model_spec("qwen3")
+        torch.manual_seed(0)
+        m = spec.model_cls(spec.config_cls.from_hf_json(os.path.join(model_dir, "config.json")))
+        sd = {}
+        for k, v in m.state_dict().items():
+            t = v.detach().clone()
+            if t.dim() >= 2:
+                t.normal_(0.0, 0.02)
+            sd["model." + k] = t.to(torch.bfloat16).contiguous()
+        save_file(sd, os.path.join(model_dir, "model.safetensors"))
+        del m, sd
+        open(marker, "w").close()
+    t_wait = time.time()
+    while not os.path.exists(marker):
+        time.sleep(0.5)
+        if time.time() - t_wait > 600:
+            print(json.dumps({"impl": "reference", "unavailable": "timed out waiting for weights"}))
+            return
+
+    n_batches = W + K + 1
+    # with dp > 1 the reference's DistributedSampler gives each rank 1/world of its dataset
+    samples = make_samples(n_batches * world, rank)
+    tokens = []
+    state = {"i": 0, "e0": None, "e1": None}
+    inner = RefPacked()
+
+    def timing_collator(batch):
+        # called by the engine's DataLoader right before each step (num_workers = 0)
+        i = state["i"]
+        if i == W:
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+            state["sampler"] = ClockSampler(local_rank)
+            state["sampler"].start()
+            state["e0"] = torch.cuda.Event(enable_timing=True)
+            state["e0"].record()
+        if i == W + K:
+            state["e1"] = torch.cuda.Event(enable_timing=True)
+            state["e1"].record()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+            state["clocks"] = state["sampler"].stop()
+        out = inner(batch)
+        if W <= i < W + K:
+            tokens.append(int(out["query"]["input_ids"].numel() + out["doc"]["input_ids"].numel()))
+            state["h2d"] = state.get("h2d", 0) + sum(
+                v.numel() * v.element_size() for part in (out["query"], out["doc"])
+                for v in part.values() if torch.is_tensor(v))
+        state["i"] = i + 1
+        return out
+
+    class SeqDataset(ListDataset):
+        pass
+
+    try:
+        engine = RefEngine(
+            model_name="qwen3", model_path=model_dir, dataset=SeqDataset(samples), dp_size=world,
+            tp_size=1, batch_size=PAIRS_PER_GPU, lr=LR, max_steps=n_batches, grad_clip=1.0,
+            temperature=TEMPERATURE, log_interval=10**9, packed=True, scheduler_type="constant",
+            collator=timing_collator)
+        # keep the batches in order (the stock DataLoader shuffles; order does not change the work)
+        engine.train()
+    except Exception as exc:  # pragma: no cover - depends on the box
+        print(json.dumps({"impl": "reference", "unavailable": f"reference run failed: {exc!r}"[:400]}))
+        return
+    ms = state["e0"].elapsed_time(state["e1"]) / K
+    if world > 1 and not dist.is_initialized():
+        # the reference engine destroys the process group at the end of train(); reduce via files
+        ms_all = _file_allreduce(ms, rank, world, "ms", max)
+        tok_all = _file_allreduce(float(sum(tokens)) / K, rank, world, "tok", sum)
+    else:
+        ms_all, tok_all = ms, float(sum(tokens)) / K
+    pairs = PAIRS_PER_GPU * world
+    e2e = {"value": pairs / (ms_all / 1e3), "unit": "pairs/s", "ms_per_step": ms_all,
+           "h2d_bytes_per_step": int(state.get("h2d", 0) / K), "d2h_bytes_per_step": 4,
+           "api": "lset.train.engine.TrainingEngine.train() (stock loop: .to(device) + loss.item() per step)"}
+    if rank == 0:
+        line = result_line("reference", world, K, W, ms_all, pairs, tok_all, state.get("clocks"), e2e,
+                           None, {"note": "timed region = steps W..W+K-1 of the reference's own "
+                                          "train() loop, marked from its DataLoader collate calls"})
+        line.pop("gpu_launches")
+        print(json.dumps(line))
+
+
+def _file_allreduce(value, rank, world, tag, op):
+    d = os.path.join(tempfile.gettempdir(), f"lset_bench_{os.environ.get('MASTER_PORT', '0')}_{tag}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, f"{rank}.txt"), "w") as fh:
+        fh.write(repr(float(value)))
+    t0 = time.time()
+    while time.time() - t0 < 120:
+        try:
+            vals = [float(open(os.path.join(d, f"{r}.txt")).read()) for r in range(world)]
+            return op(vals)
+        except (OSError, ValueError):
+            time.sleep(0.2)
+    return value
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,398 @@
+"""Sharded data parallelism (ZeRO) over flat parameter groups, and the AdamW that runs on it.
+
+This is the framework's counterpart of the reference's FSDP2 set-up
+(lset/distributed/parallel.py:129-160: one group per transformer layer plus a root group, bf16
+compute parameters, fp32 gradient reduction and fp32 optimizer state) built for B200 memory sizes:
+
+* every group owns one flat **bf16** buffer holding its trainable parameters (the tensors the
+  kernels read), one flat **fp32 gradient accumulator** (``param.main_grad`` views; weight-gradient
+  GEMMs add straight into it, so gradient accumulation and the bf16->fp32 cast cost nothing), and,
+  for the 1/W slice this rank owns, fp32 master weights and AdamW moments;
+* backward: as soon as a layer's backward has run, its gradient buffer is reduce-scattered (fp32,
+  averaged) on a side stream, overlapping the rest of backward; with gradient accumulation the
+  reduction only happens on the boundary micro-step;
+* step: global-norm clipping with the coefficient kept on the device, one fused AdamW kernel per
+  group that also writes the new bf16 shard, then an all-gather of the shards that the next
+  forward waits for per layer. With 180 GB per GPU the bf16 replica stays resident (no re-gather
+  in backward); ``reshard_after_forward`` is accepted for interface parity and ignored.
+
+Collectives go through ``torch.distributed`` (NCCL on GPUs, gloo on CPU for tests) unless the
+symmetric-memory kernels of ``lset_b200.dist.symm`` are enabled, which fuse the gradient
+reduce-scatter, the optimizer step and the parameter all-gather into two launches over NVLink.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import _native as nv
+from ..ops.norm import scratch
+
+_ALIGN = 8  # elements; keeps every parameter 16-byte aligned in the bf16 buffer
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatGroup:
+    """One communication / optimizer unit: the trainable parameters of a set of modules."""
+
+    def __init__(self, name: str, params: Sequence[nn.Parameter], world: int, rank: int,
+                 compute_dtype: torch.dtype, device: torch.device):
+        self.name = name
+        self.params = list(params)
+        self.world, self.rank = world, rank
+        offs, n = [], 0
+        for p in self.params:
+            offs.append(n)
+            n += _round_up(p.numel(), _ALIGN)
+        self.offsets = offs
+        self.numel = _round_up(max(n, _ALIGN), _ALIGN * world)
+        self.shard_numel = self.numel // world
+        self.lo = rank * self.shard_numel
+        self.hi = self.lo + self.shard_numel
+        self.device = device
+        self.compute_dtype = compute_dtype
+        # master values come from the parameters as given (fp32 when the module was built in fp32)
+        full_master = torch.zeros(self.numel, dtype=torch.float32, device=device)
+        for p, o in zip(self.params, offs):
+            full_master[o:o + p.numel()] = p.data.detach().reshape(-1).to(device, torch.float32)
+        self.flat_param = full_master.to(compute_dtype)
+        self.flat_grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
+        self.master = full_master[self.lo:self.hi].clone()
+        del full_master
+        self.exp_avg = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+        self.exp_avg_sq = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+        self.grad_shard = (self.flat_grad if world == 1 else
+                           torch.zeros(self.shard_numel, dtype=torch.float32, device=device))
+        for p, o in zip(self.params, offs):
+            p.data = self.flat_param[o:o + p.numel()].view(p.shape)
+            p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
+            p.grad = None
+        self.reduce_event = None     # recorded after the gradient reduction of this group
+        self.gather_event = None     # recorded after the parameter all-gather of this group
+        self.reduced = False
+
+    def collect_autograd_grads(self) -> None:
+        """Fold any ``param.grad`` that autograd produced (ops without main_grad support) into the
+        fp32 accumulator."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+
+class ParamStore:
+    """Flat, sharded storage for a module's trainable parameters."""
+
+    def __init__(self, module: nn.Module, layer_modules: Optional[Iterable[nn.Module]] = None,
+                 dp_group=None, compute_dtype: torch.dtype = torch.bfloat16,
+                 device: Optional[torch.device] = None, reshard_after_forward: bool = False,
+                 overlap: bool = True):
+        self.module = module
+        self.dp_group = dp_group
+        if dist.is_available() and dist.is_initialized():
+            self.world, self.rank = dist.get_world_size(dp_group), dist.get_rank(dp_group)
+        else:
+            self.world, self.rank = 1, 0
+        if device is None:
+            device = next(module.parameters()).device
+        self.device = torch.device(device)
+        self.compute_dtype = compute_dtype
+        self.requires_gradient_sync = True
+        self.groups: List[FlatGroup] = []
+        claimed = set()
+        layers = list(layer_modules) if layer_modules is not None else list(getattr(module, "layers", []))
+        self._layer_of_group = {}
+        for i, layer in enumerate(layers):
+            ps = [p for p in layer.parameters() if p.requires_grad and id(p) not in claimed]
+            claimed.update(id(p) for p in ps)
+            if ps:
+                g = FlatGroup(f"layers.{i}", ps, self.world, self.rank, compute_dtype, self.device)
+                self._layer_of_group[len(self.groups)] = layer
+                self.groups.append(g)
+        rest = [p for p in module.parameters() if p.requires_grad and id(p) not in claimed]
+        if rest:
+            self.groups.append(FlatGroup("root", rest, self.world, self.rank, compute_dtype, self.device))
+        # frozen parameters and buffers: just move / cast, they stay replicated
+        for p in module.parameters():
+            if not p.requires_grad:
+                p.data = p.data.to(self.device, compute_dtype if p.is_floating_point() else p.dtype)
+        for b in module.buffers():
+            b.data = b.data.to(self.device)
+        self.overlap = overlap and self.device.type == "cuda" and self.world > 1
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
+        self._hooks = []
+        if self.world > 1:
+            self._install_hooks()
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self) -> None:
+        for gi, layer in self._layer_of_group.items():
+            g = self.groups[gi]
+
+            def after_backward(_mod, _gin, _gout, g=g):
+                if self.requires_gradient_sync:
+                    self._reduce_group(g)
+
+            def before_forward(_mod, _args, g=g):
+                self._wait_gather(g)
+
+            self._hooks.append(layer.register_full_backward_hook(after_backward))
+            self._hooks.append(layer.register_forward_pre_hook(before_forward))
+
+    def set_requires_gradient_sync(self, flag: bool) -> None:
+        """False on non-boundary micro-steps of gradient accumulation (gradients only accumulate)."""
+        self.requires_gradient_sync = bool(flag)
+
+    # ------------------------------------------------------------------ collectives
+    def _reduce_group(self, g: FlatGroup) -> None:
+        if g.reduced or self.world == 1:
+            g.reduced = True
+            return
+        g.collect_autograd_grads()
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self._reduce_scatter(g)
+                g.reduce_event = torch.cuda.Event()
+                g.reduce_event.record(self.comm_stream)
+        else:
+            self._reduce_scatter(g)
+        g.reduced = True
+
+    def _reduce_scatter(self, g: FlatGroup) -> None:
+        if g.flat_grad.is_cuda:
+            dist.reduce_scatter_tensor(g.grad_shard, g.flat_grad, op=dist.ReduceOp.AVG,
+                                       group=self.dp_group)
+        else:  # gloo: no reduce-scatter
+            dist.all_reduce(g.flat_grad, op=dist.ReduceOp.SUM, group=self.dp_group)
+            g.grad_shard.copy_(g.flat_grad[g.lo:g.hi]).div_(self.world)
+
+    def finish_backward(self) -> None:
+        """Call after ``loss.backward()``: reduces whatever the hooks did not cover (root group,
+        layers whose inputs carry no gradient) and folds stray autograd grads in."""
+        for g in self.groups:
+            g.collect_autograd_grads()
+        if not self.requires_gradient_sync:
+            return
+        for g in reversed(self.groups):
+            if not g.reduced:
+                self._reduce_group(g)
+
+    def wait_reductions(self) -> None:
+        for g in self.groups:
+            if g.reduce_event is not None:
+                torch.cuda.current_stream().wait_event(g.reduce_event)
+                g.reduce_event = None
+
+    def gather_params(self) -> None:
+        """All-gather the updated bf16 shards (after an optimizer step)."""
+        if self.world == 1:
+            return
+        for g in self.groups:
+            if self.comm_stream is not None:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    dist.all_gather_into_tensor(g.flat_param, g.flat_param[g.lo:g.hi],
+                                                group=self.dp_group)
+                    g.gather_event = torch.cuda.Event()
+                    g.gather_event.record(self.comm_stream)
+            else:
+                dist.all_gather_into_tensor(g.flat_param, g.flat_param[g.lo:g.hi].clone(),
+                                            group=self.dp_group)
+
+    def _wait_gather(self, g: FlatGroup) -> None:
+        if g.gather_event is not None:
+            torch.cuda.current_stream().wait_event(g.gather_event)
+            g.gather_event = None
+
+    def wait_all_gathers(self) -> None:
+        for g in self.groups:
+            self._wait_gather(g)
+
+    # ------------------------------------------------------------------ utilities
+    def zero_grad(self) -> None:
+        for g in self.groups:
+            g.flat_grad.zero_()
+            g.reduced = False
+
+    def trainable_parameters(self):
+        for g in self.groups:
+            yield from g.params
+
+    def named_master_tensors(self):
+        """``(name, fp32 tensor)`` for every trainable parameter, gathered across ranks (a
+        collective when world > 1). Used for checkpoints."""
+        names = {id(p): n for n, p in self.module.named_parameters()}
+        for g in self.groups:
+            full = self._gather_fp32(g, g.master)
+            for p, o in zip(g.params, g.offsets):
+                yield names[id(p)], full[o:o + p.numel()].view(p.shape)
+
+    def _gather_fp32(self, g: FlatGroup, shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return shard
+        full = torch.empty(g.numel, dtype=torch.float32, device=shard.device)
+        if shard.is_cuda:
+            dist.all_gather_into_tensor(full, shard.contiguous(), group=self.dp_group)
+        else:
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.contiguous(), group=self.dp_group)
+            full = torch.cat(parts)
+        return full
+
+    def load_master(self, name_to_tensor: dict) -> None:
+        """Overwrite master weights and bf16 parameters from full tensors keyed by parameter name."""
+        names = {id(p): n for n, p in self.module.named_parameters()}
+        for g in self.groups:
+            full = torch.zeros(g.numel, dtype=torch.float32, device=self.device)
+            full_now = self._gather_fp32(g, g.master)
+            full.copy_(full_now)
+            for p, o in zip(g.params, g.offsets):
+                t = name_to_tensor.get(names[id(p)])
+                if t is not None:
+                    full[o:o + p.numel()] = t.reshape(-1).to(self.device, torch.float32)
+            g.master.copy_(full[g.lo:g.hi])
+            g.flat_param.copy_(full.to(self.compute_dtype))
+
+
+class ShardedAdamW:
+    """AdamW over a ``ParamStore`` (torch.optim.AdamW semantics, decoupled weight decay) with
+    global-norm clipping folded in. ``state_dict`` follows torch's AdamW schema so checkpoints are
+    interchangeable with the reference's (lset/train/checkpoint.py:9-53)."""
+
+    def __init__(self, store: ParamStore, lr: float = 2e-5, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, grad_clip: float = 0.0):
+        self.store = store
+        self.defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        self.param_groups = [dict(self.defaults, params=list(store.trainable_parameters()),
+                                  initial_lr=lr)]
+        self.grad_clip = grad_clip
+        self.step_count = 0
+        dev = store.device
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(2, dtype=torch.float32, device=dev)  # [clip coefficient, norm]
+        self.state = {}  # torch.optim.Optimizer API expected by LR schedulers
+
+    # -- torch.optim-like surface ------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.store.zero_grad()
+
+    @property
+    def lr(self) -> float:
+        return self.param_groups[0]["lr"]
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global gradient norm of the last ``step`` (device scalar)."""
+        return self._coef[1]
+
+    def _global_sumsq(self) -> None:
+        st = self.store
+        native = st.device.type == "cuda"
+        self._sumsq.zero_()
+        for g in st.groups:
+            if native:
+                lib = nv.load()
+                scr = scratch("sumsq", lib.lb_sumsq_partial_rows(), st.device)
+                rc = lib.lb_sumsq_f32(nv.c_void_p(g.grad_shard.data_ptr()), nv.c_ll(g.grad_shard.numel()),
+                                      nv.c_void_p(scr.data_ptr()), nv.c_void_p(self._sumsq.data_ptr()),
+                                      nv.c_int(1), nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_sumsq_f32")
+                nv.count_launch(2)
+            else:
+                self._sumsq.add_(g.grad_shard.float().pow(2).sum())
+        if st.world > 1:
+            dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=st.dp_group)
+
+    @torch.no_grad()
+    def step(self) -> None:
+        st = self.store
+        st.wait_reductions()
+        self.step_count += 1
+        pg = self.param_groups[0]
+        lr, (b1, b2), eps, wd = pg["lr"], pg["betas"], pg["eps"], pg["weight_decay"]
+        bc1 = 1.0 - b1 ** self.step_count
+        bc2s = math.sqrt(1.0 - b2 ** self.step_count)
+        self._global_sumsq()
+        native = st.device.type == "cuda"
+        if native:
+            rc = nv.load().lb_clip_coef(nv.c_void_p(self._sumsq.data_ptr()), nv.c_float(self.grad_clip),
+                                        nv.c_void_p(self._coef.data_ptr()), nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_clip_coef")
+            nv.count_launch()
+        else:
+            norm = self._sumsq.sqrt()
+            self._coef[1] = norm[0]
+            self._coef[0] = torch.clamp(self.grad_clip / (norm[0] + 1e-6), max=1.0) \
+                if self.grad_clip > 0 else 1.0
+        for g in st.groups:
+            pshard = g.flat_param[g.lo:g.hi]
+            if native:
+                rc = nv.load().lb_adamw_f32(
+                    nv.c_void_p(g.master.data_ptr()), nv.c_void_p(g.grad_shard.data_ptr()),
+                    nv.c_void_p(g.exp_avg.data_ptr()), nv.c_void_p(g.exp_avg_sq.data_ptr()),
+                    nv.c_void_p(pshard.data_ptr() if g.compute_dtype == torch.bfloat16 else 0),
+                    nv.c_ll(g.shard_numel), nv.c_float(lr), nv.c_float(b1), nv.c_float(b2),
+                    nv.c_float(eps), nv.c_float(wd), nv.c_float(bc1), nv.c_float(bc2s),
+                    nv.c_float(1.0), nv.c_void_p(self._coef.data_ptr()), nv.c_int(0),
+                    nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_adamw_f32")
+                nv.count_launch()
+                if g.compute_dtype != torch.bfloat16:
+                    pshard.copy_(g.master)
+            else:
+                grad = g.grad_shard * self._coef[0]
+                g.master.mul_(1.0 - lr * wd)
+                g.exp_avg.mul_(b1).add_(grad, alpha=1.0 - b1)
+                g.exp_avg_sq.mul_(b2).addcmul_(grad, grad, value=1.0 - b2)
+                denom = g.exp_avg_sq.sqrt().div_(bc2s).add_(eps)
+                g.master.addcdiv_(g.exp_avg, denom, value=-lr / bc1)
+                pshard.copy_(g.master)
+        st.gather_params()
+
+    # -- checkpoint schema ---------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        """torch AdamW layout: per-parameter ``step / exp_avg / exp_avg_sq`` (full tensors; a
+        collective when world > 1) plus ``param_groups`` with integer parameter ids."""
+        st = self.store
+        state, idx = {}, 0
+        step_t = torch.tensor(float(self.step_count))
+        for g in st.groups:
+            m = st._gather_fp32(g, g.exp_avg)
+            v = st._gather_fp32(g, g.exp_avg_sq)
+            for p, o in zip(g.params, g.offsets):
+                state[idx] = {"step": step_t.clone(),
+                              "exp_avg": m[o:o + p.numel()].view(p.shape).clone(),
+                              "exp_avg_sq": v[o:o + p.numel()].view(p.shape).clone()}
+                idx += 1
+        pg = {k: v for k, v in self.param_groups[0].items() if k != "params"}
+        pg.update(amsgrad=False, maximize=False, foreach=None, capturable=False,
+                  differentiable=False, fused=True, params=list(range(idx)))
+        return {"state": state, "param_groups": [pg]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        st = self.store
+        idx = 0
+        for g in st.groups:
+            m = torch.zeros(g.numel, dtype=torch.float32, device=st.device)
+            v = torch.zeros(g.numel, dtype=torch.float32, device=st.device)
+            for p, o in zip(g.params, g.offsets):
+                ent = sd["state"].get(idx, sd["state"].get(str(idx)))
+                if ent is not None:
+                    m[o:o + p.numel()] = ent["exp_avg"].reshape(-1).to(st.device, torch.float32)
+                    v[o:o + p.numel()] = ent["exp_avg_sq"].reshape(-1).to(st.device, torch.float32)
+                    self.step_count = int(float(ent["step"]))
+                idx += 1
+            g.exp_avg.copy_(m[g.lo:g.hi])
+            g.exp_avg_sq.copy_(v[g.lo:g.hi])
+        if sd.get("param_groups"):
+            for k in ("lr", "betas", "eps", "weight_decay", "initial_lr"):
+                if k in sd["param_groups"][0]:
+                    val = sd["param_groups"][0][k]
+                    self.param_groups[0][k] = tuple(val) if k == "betas" else val

@@ -165,6 +165,61 @@ class _VarlenAttn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _QkvAttention(torch.autograd.Function):
+    """Fused path for a fused QKV projection output ``qkv [T, Hq + 2Hk, hd]``: per-head RMSNorm +
+    RoPE on q and k, then attention. The backward writes one ``dqkv`` buffer, so the projection's
+    dgrad/wgrad GEMMs consume it without any slicing or concatenation."""
+
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, cos, sin, pos, plan, Hq, Hk, causal, scale, eps, w_off):
+        from .rope import rope_fwd_native
+
+        q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hk], qkv[:, Hq + Hk:]
+        q_r, k_r, q_rstd, k_rstd = rope_fwd_native(q, k, qw, kw, cos, sin, pos, eps, w_off)
+        o, lse = _native_fwd(q_r, k_r, v, plan, causal, scale)
+        ctx.save_for_backward(qkv, qw, kw, cos, sin, pos, q_r, k_r, q_rstd, k_rstd, o, lse)
+        ctx.meta = (plan, Hq, Hk, causal, scale, w_off)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from .rope import deliver_norm_wgrads, rope_bwd_native
+
+        qkv, qw, kw, cos, sin, pos, q_r, k_r, q_rstd, k_rstd, o, lse = ctx.saved_tensors
+        plan, Hq, Hk, causal, scale, w_off = ctx.meta
+        T, _, hd = qkv.shape
+        do = do if do.is_contiguous() else do.contiguous()
+        q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hk], qkv[:, Hq + Hk:]
+        dqkv = torch.empty_like(qkv) if plan.cu_seqlens is not None else torch.zeros_like(qkv)
+        dq_r = torch.empty(T, Hq, hd, dtype=qkv.dtype, device=qkv.device)
+        dk_r = torch.empty(T, Hk, hd, dtype=qkv.dtype, device=qkv.device)
+        if plan.cu_seqlens is None:
+            dq_r.zero_()
+            dk_r.zero_()
+        _native_bwd(do, q_r, k_r, v, o, lse, plan, causal, scale, dq_r, dk_r, dqkv[:, Hq + Hk:])
+        dwb = rope_bwd_native(dq_r, dk_r, q, k, qw, kw, cos, sin, pos, q_rstd, k_rstd, w_off,
+                              dqkv[:, :Hq], dqkv[:, Hq:Hq + Hk])
+        dqw, dkw = deliver_norm_wgrads(qw, kw, dwb, hd)
+        return dqkv, dqw, dkw, None, None, None, None, None, None, None, None, None, None
+
+
+def qkv_attention(qkv, qw, kw, cos, sin, pos, plan: AttnPlan, Hq: int, Hk: int, causal: bool,
+                  scale: float | None = None, eps: float = 1e-6, w_off: float = 0.0):
+    """RoPE (with per-head RMSNorm when ``qw`` is given) + attention on a fused ``[T, Hq+2Hk, hd]``
+    projection output. Returns ``[T, Hq, hd]``."""
+    from .rope import qk_norm_rope
+
+    hd = qkv.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hk], qkv[:, Hq + Hk:]
+    needs_grad = torch.is_grad_enabled() and qkv.requires_grad
+    if native_supported(q, k) and qkv.is_contiguous() and not (needs_grad and hd > 128):
+        return _QkvAttention.apply(qkv, qw, kw, cos, sin, pos, plan, Hq, Hk, bool(causal),
+                                   float(scale), float(eps), float(w_off))
+    q, k = qk_norm_rope(q, k, qw, kw, cos, sin, pos, eps, w_off)
+    return varlen_attention(q, k, v, plan, causal, scale)
+
+
 def native_supported(q, k) -> bool:
     if not (nv.use_native(q, k) and q.dtype == torch.bfloat16):
         return False

@@ -63,30 +63,77 @@ def qk_norm_rope_ref(q, k, qw, kw, cos, sin, pos, eps=1e-6, w_off=0.0):
     return (_rotate_ref(norm(q, qw), c, s).to(q.dtype), _rotate_ref(norm(k, kw), c, s).to(k.dtype))
 
 
+def rope_fwd_native(q, k, qw, kw, cos, sin, pos, eps, w_off):
+    """Raw launcher. q: [T,Hq,hd], k: [T,Hk,hd] (strided views allowed). Returns
+    ``(q_out, k_out, q_rstd, k_rstd)`` with contiguous outputs."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    assert q.stride(2) == 1 and k.stride(2) == 1 and q.stride(1) == hd and k.stride(1) == hd
+    do_norm = qw is not None
+    q_out = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
+    k_out = torch.empty(T, Hk, hd, dtype=k.dtype, device=k.device)
+    q_rstd = torch.empty(T, Hq, dtype=torch.float32, device=q.device) if do_norm else None
+    k_rstd = torch.empty(T, Hk, dtype=torch.float32, device=q.device) if do_norm else None
+    rc = nv.load().lb_qk_norm_rope_fwd(
+        nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
+        nv.c_ll(k.stride(0)), nv.c_void_p(nv.ptr(qw)), nv.c_void_p(nv.ptr(kw)),
+        nv.c_void_p(cos.data_ptr()), nv.c_void_p(sin.data_ptr()), nv.c_void_p(pos.data_ptr()),
+        nv.c_int(int(pos.dtype == torch.int64)), nv.c_int(1),
+        nv.c_void_p(q_out.data_ptr()), nv.c_ll(Hq * hd), nv.c_void_p(k_out.data_ptr()),
+        nv.c_ll(Hk * hd), nv.c_void_p(nv.ptr(q_rstd)), nv.c_void_p(nv.ptr(k_rstd)),
+        nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd), nv.c_float(eps),
+        nv.c_float(w_off), nv.c_int(int(do_norm)), nv.c_void_p(nv.stream_ptr()))
+    nv.check_rc(rc, "lb_qk_norm_rope_fwd")
+    nv.count_launch()
+    return q_out, k_out, q_rstd, k_rstd
+
+
+def rope_bwd_native(dq, dk, q, k, qw, kw, cos, sin, pos, q_rstd, k_rstd, w_off, dq_in, dk_in):
+    """Raw launcher. dq/dk: contiguous grads of the rotated outputs; dq_in/dk_in: destination views
+    (unit inner stride). Returns the fp32 ``[2*hd]`` weight gradient (q then k) or None."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    do_norm = qw is not None
+    lib = nv.load()
+    rows = lib.lb_rope_bwd_partial_rows()
+    scr = scratch("rope_bwd", rows * 2 * hd, q.device) if do_norm else None
+    dwb = torch.empty(2 * hd, dtype=torch.float32, device=q.device) if do_norm else None
+    rc = lib.lb_qk_norm_rope_bwd(
+        nv.c_void_p(dq.data_ptr()), nv.c_ll(dq.stride(0)), nv.c_void_p(dk.data_ptr()),
+        nv.c_ll(dk.stride(0)), nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
+        nv.c_void_p(k.data_ptr()), nv.c_ll(k.stride(0)), nv.c_void_p(nv.ptr(qw)),
+        nv.c_void_p(nv.ptr(kw)), nv.c_void_p(cos.data_ptr()), nv.c_void_p(sin.data_ptr()),
+        nv.c_void_p(pos.data_ptr()), nv.c_int(int(pos.dtype == torch.int64)), nv.c_int(1),
+        nv.c_void_p(nv.ptr(q_rstd)), nv.c_void_p(nv.ptr(k_rstd)),
+        nv.c_void_p(dq_in.data_ptr()), nv.c_ll(dq_in.stride(0)), nv.c_void_p(dk_in.data_ptr()),
+        nv.c_ll(dk_in.stride(0)), nv.c_void_p(nv.ptr(scr)), nv.c_void_p(nv.ptr(dwb)),
+        nv.c_int(1), nv.c_int(0), nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd),
+        nv.c_float(w_off), nv.c_int(int(do_norm)), nv.c_void_p(nv.stream_ptr()))
+    nv.check_rc(rc, "lb_qk_norm_rope_bwd")
+    nv.count_launch(2 if do_norm else 1)
+    return dwb
+
+
+def deliver_norm_wgrads(qw, kw, dwb, hd):
+    """Route the fp32 q/k norm-weight gradients to ``main_grad`` or return them as tensors."""
+    dqw = dkw = None
+    if dwb is None:
+        return dqw, dkw
+    for w, sl, is_q in ((qw, dwb[:hd], True), (kw, dwb[hd:], False)):
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            mg.add_(sl)
+        elif is_q:
+            dqw = sl.to(w.dtype)
+        else:
+            dkw = sl.to(w.dtype)
+    return dqw, dkw
+
+
 class _QkNormRope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, qw, kw, cos, sin, pos, eps, w_off):
-        # q: [T, Hq, hd], k: [T, Hk, hd]; both may be strided views of one fused QKV tensor.
-        T, Hq, hd = q.shape
-        Hk = k.shape[1]
-        assert q.stride(2) == 1 and k.stride(2) == 1 and q.stride(1) == hd and k.stride(1) == hd
-        do_norm = qw is not None
-        q_out = torch.empty(T, Hq, hd, dtype=q.dtype, device=q.device)
-        k_out = torch.empty(T, Hk, hd, dtype=k.dtype, device=k.device)
-        q_rstd = torch.empty(T, Hq, dtype=torch.float32, device=q.device) if do_norm else None
-        k_rstd = torch.empty(T, Hk, dtype=torch.float32, device=q.device) if do_norm else None
-        lib = nv.load()
-        rc = lib.lb_qk_norm_rope_fwd(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
-            nv.c_ll(k.stride(0)), nv.c_void_p(nv.ptr(qw)), nv.c_void_p(nv.ptr(kw)),
-            nv.c_void_p(cos.data_ptr()), nv.c_void_p(sin.data_ptr()), nv.c_void_p(pos.data_ptr()),
-            nv.c_int(int(pos.dtype == torch.int64)), nv.c_int(1),
-            nv.c_void_p(q_out.data_ptr()), nv.c_ll(Hq * hd), nv.c_void_p(k_out.data_ptr()),
-            nv.c_ll(Hk * hd), nv.c_void_p(nv.ptr(q_rstd)), nv.c_void_p(nv.ptr(k_rstd)),
-            nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd), nv.c_float(eps),
-            nv.c_float(w_off), nv.c_int(int(do_norm)), nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_qk_norm_rope_fwd")
-        nv.count_launch()
+        q_out, k_out, q_rstd, k_rstd = rope_fwd_native(q, k, qw, kw, cos, sin, pos, eps, w_off)
         ctx.save_for_backward(q, k, qw, kw, cos, sin, pos, q_rstd, k_rstd)
         ctx.w_off = w_off
         return q_out, k_out
@@ -96,40 +143,13 @@ class _QkNormRope(torch.autograd.Function):
         q, k, qw, kw, cos, sin, pos, q_rstd, k_rstd = ctx.saved_tensors
         T, Hq, hd = q.shape
         Hk = k.shape[1]
-        do_norm = qw is not None
         dq = dq if dq.is_contiguous() else dq.contiguous()
         dk = dk if dk.is_contiguous() else dk.contiguous()
-        # Gradients land in one [T, Hq + Hk, hd] buffer so that a fused QKV projection can view
-        # them without a concatenation.
         dqk = torch.empty(T, Hq + Hk, hd, dtype=q.dtype, device=q.device)
         dq_in, dk_in = dqk[:, :Hq], dqk[:, Hq:]
-        lib = nv.load()
-        rows = lib.lb_rope_bwd_partial_rows()
-        scr = scratch("rope_bwd", rows * 2 * hd, q.device) if do_norm else None
-        dwb = torch.empty(2 * hd, dtype=torch.float32, device=q.device) if do_norm else None
-        rc = lib.lb_qk_norm_rope_bwd(
-            nv.c_void_p(dq.data_ptr()), nv.c_ll(Hq * hd), nv.c_void_p(dk.data_ptr()),
-            nv.c_ll(Hk * hd), nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
-            nv.c_void_p(k.data_ptr()), nv.c_ll(k.stride(0)), nv.c_void_p(nv.ptr(qw)),
-            nv.c_void_p(nv.ptr(kw)), nv.c_void_p(cos.data_ptr()), nv.c_void_p(sin.data_ptr()),
-            nv.c_void_p(pos.data_ptr()), nv.c_int(int(pos.dtype == torch.int64)), nv.c_int(1),
-            nv.c_void_p(nv.ptr(q_rstd)), nv.c_void_p(nv.ptr(k_rstd)),
-            nv.c_void_p(dq_in.data_ptr()), nv.c_ll(dqk.stride(0)), nv.c_void_p(dk_in.data_ptr()),
-            nv.c_ll(dqk.stride(0)), nv.c_void_p(nv.ptr(scr)), nv.c_void_p(nv.ptr(dwb)),
-            nv.c_int(1), nv.c_int(0), nv.c_int(T), nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd),
-            nv.c_float(ctx.w_off), nv.c_int(int(do_norm)), nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_qk_norm_rope_bwd")
-        nv.count_launch(2 if do_norm else 1)
-        dqw = dkw = None
-        if do_norm:
-            for w, sl, name in ((qw, dwb[:hd], "q"), (kw, dwb[hd:], "k")):
-                mg = getattr(w, "main_grad", None)
-                if mg is not None:
-                    mg.add_(sl)
-                elif name == "q":
-                    dqw = sl.to(w.dtype)
-                else:
-                    dkw = sl.to(w.dtype)
+        dwb = rope_bwd_native(dq, dk, q, k, qw, kw, cos, sin, pos, q_rstd, k_rstd, ctx.w_off,
+                              dq_in, dk_in)
+        dqw, dkw = deliver_norm_wgrads(qw, kw, dwb, hd)
         return dq_in, dk_in, dqw, dkw, None, None, None, None, None
 
 
