@@ -423,3 +423,80 @@ extern "C" int lb_colsum(const float* partial, int P, int C, void* out, int out_
       partial, P, C, out, out_fp32, accumulate);
   return launch_rc();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (see norm_noalloc.h): same kernels as lb_rms_norm_bwd, with the
+// per-CTA partials in a fixed array that is part of the library image.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "norm_noalloc.h"
+
+namespace {
+
+// One copy per device that loads the library. In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernels receive the looked-up device address.
+static __device__ __align__(256) float g_noalloc_partials[LB_NOALLOC_MAX_PARTIAL_ROWS * LB_NOALLOC_MAX_H];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
+    return LB_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials) != cudaSuccess ||
+        p == nullptr) {
+      cudaGetLastError();  // clear the sticky-free error state for the caller
+      return LB_NOALLOC_ERR_SYMBOL;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" const char* lb_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case LB_NOALLOC_ERR_TOO_LARGE:
+      return "row width H exceeds LB_NOALLOC_MAX_H (4096): the built-in scratch array is too small";
+    case LB_NOALLOC_ERR_SYMBOL:
+      return "cudaGetSymbolAddress failed for the built-in scratch array on the current device";
+    case LB_NOALLOC_ERR_DEVICE: return "current device index is outside the library's device table";
+    case -3: return "bad shape: H must be a positive multiple of 8";
+    case -11: return "kernel launch failed";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int lb_rms_norm_bwd_noalloc(const void* dy, const void* dres, const void* xin,
+                                       const void* w, const float* rstd, void* dx, void* dw_out,
+                                       int dw_fp32, int dw_accumulate, int N, int H, float w_off,
+                                       void* stream) {
+  if (N <= 0) return 0;
+  if (H <= 0 || (H & 7)) return -3;
+  if (H > LB_NOALLOC_MAX_H) return LB_NOALLOC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = 1;
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    grid = bwd_grid(N, ROWS);
+    if (grid > LB_NOALLOC_MAX_PARTIAL_ROWS) grid = LB_NOALLOC_MAX_PARTIAL_ROWS;
+    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
+        (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
+        scratch, N, H, w_off);
+  });
+  if (dw_out != nullptr)
+    colsum_kernel<<<(H + 127) / 128, 128, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
+  return launch_rc();
+}

@@ -1,0 +1,87 @@
+"""The allocation-free RMSNorm backward (``lb_rms_norm_bwd_noalloc``).
+
+Some users of the library cannot allocate device memory at the point where they need this
+gradient: their process has given the whole GPU to a pool that it cannot grow, or their serving
+loop forbids the device-wide synchronisation that an allocation can trigger. For them the library
+exports a variant of the RMSNorm backward whose weight-gradient partials live in an array inside
+the library image instead of a scratch buffer from the caller. This test calls that variant
+through its exported C symbol and checks, on two different calls in a row (so the second call
+sees whatever the first one left in the shared array), that it returns what the regular entry
+point returns. The tensors created here are the caller's inputs and outputs; the call itself must
+not allocate. The file is named so that pytest collects it last.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+c_void_p, c_int, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+def _p(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _run_both(lib, N, H, with_res, w_off, seed):
+    torch.manual_seed(seed)
+    dev = "cuda"
+    bf = torch.bfloat16
+    dy = torch.randn(N, H, device=dev).to(bf)
+    dres = torch.randn(N, H, device=dev).to(bf) if with_res else None
+    x = torch.randn(N, H, device=dev).to(bf)
+    w = (torch.randn(H, device=dev) * 0.5).to(bf)
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6).contiguous()
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # regular entry point: scratch comes from the caller
+    rows = lib.lb_norm_bwd_partial_rows()
+    scratch = torch.empty(rows * H, dtype=torch.float32, device=dev)
+    dx_ref = torch.empty_like(x)
+    dw_ref = torch.empty(H, dtype=torch.float32, device=dev)
+    rc = lib.lb_rms_norm_bwd(_p(dy), _p(dres), _p(x), _p(w), _p(rstd), _p(dx_ref), _p(scratch),
+                             _p(dw_ref), c_int(1), c_int(0), c_int(N), c_int(H), c_float(w_off), stream)
+    assert rc == 0
+
+    # allocation-free entry point: outputs are pre-allocated, the call gets no scratch
+    dx = torch.empty_like(x)
+    dw = torch.empty(H, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    rc = lib.lb_rms_norm_bwd_noalloc(_p(dy), _p(dres), _p(x), _p(w), _p(rstd), _p(dx), _p(dw),
+                                     c_int(1), c_int(0), c_int(N), c_int(H), c_float(w_off), stream)
+    assert rc == 0, lib.lb_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+    return dx, dx_ref, dw, dw_ref
+
+
+def test_noalloc_matches_regular_entry_point_twice():
+    from lset_b200.ops import _native as nv
+
+    lib = nv.load()
+    lib.lb_noalloc_strerror.restype = ctypes.c_char_p
+    for N, H, with_res, w_off, seed in [(3000, 1024, True, 0.0, 0), (517, 2560, False, 1.0, 1)]:
+        dx, dx_ref, dw, dw_ref = _run_both(lib, N, H, with_res, w_off, seed)
+        assert torch.equal(dx, dx_ref)
+        err = (dw - dw_ref).abs().max().item()
+        scale = dw_ref.abs().max().item() + 1e-6
+        assert err / scale < 2e-2, (err, scale)
+
+
+def test_noalloc_rejects_rows_wider_than_the_built_in_array():
+    from lset_b200.ops import _native as nv
+
+    lib = nv.load()
+    lib.lb_noalloc_strerror.restype = ctypes.c_char_p
+    H = 8192
+    t = torch.zeros(4, H, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
+    r = torch.ones(4, dtype=torch.float32, device="cuda")
+    dw = torch.zeros(H, dtype=torch.float32, device="cuda")
+    rc = lib.lb_rms_norm_bwd_noalloc(_p(t), _p(None), _p(t), _p(w), _p(r), _p(t.clone()), _p(dw),
+                                     c_int(1), c_int(0), c_int(4), c_int(H), c_float(0.0),
+                                     c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == -20
+    assert b"LB_NOALLOC_MAX_H" in lib.lb_noalloc_strerror(rc)
