@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native as nv
+from .runtime_options import options as _rt
 
 
 class AttnPlan:
@@ -221,6 +222,8 @@ def qkv_attention(qkv, qw, kw, cos, sin, pos, plan: AttnPlan, Hq: int, Hk: int, 
 
 
 def native_supported(q, k) -> bool:
+    if _rt.attention_backend == "sdpa":
+        return False
     if not (nv.use_native(q, k) and q.dtype == torch.bfloat16):
         return False
     Hq, hd = q.shape[1], q.shape[2]

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from . import _native as nv
+from .runtime_options import enabled
 
 
 # --------------------------------------------------------------------------- eager oracles
@@ -149,14 +150,14 @@ class _RmsNorm(torch.autograd.Function):
 
 def rms_norm(x, w, eps=1e-6, w_off=0.0):
     """``y = bf16(x * rsqrt(mean(x²) + eps)) * (w + w_off)``."""
-    if not _native_ok(x, w):
+    if not (_native_ok(x, w) and enabled("fused_rmsnorm")):
         return rms_norm_ref(x, w, eps, w_off)
     return _RmsNorm.apply(x, None, w, eps, w_off)[0]
 
 
 def residual_rms_norm(residual, x, w, eps=1e-6, w_off=0.0):
     """``nr = residual + x`` then RMSNorm; returns ``(y, nr)``."""
-    if not _native_ok(residual, x, w):
+    if not (_native_ok(residual, x, w) and enabled("fused_residual_rmsnorm")):
         return residual_rms_norm_ref(residual, x, w, eps, w_off)
     return _RmsNorm.apply(x, residual, w, eps, w_off)
 
@@ -164,7 +165,7 @@ def residual_rms_norm(residual, x, w, eps=1e-6, w_off=0.0):
 def double_residual_rms_norm(residual, a, w1, w2, eps=1e-6, w_off=0.0):
     """Gemma post-norm pair: ``z = rmsnorm(a)·w1; nr = residual + z; out = rmsnorm(nr)·w2``;
     returns ``(out, nr)``. Runs as two native launches (norm, then residual-add + norm)."""
-    if not _native_ok(residual, a, w1, w2):
+    if not (_native_ok(residual, a, w1, w2) and enabled("fused_double_rmsnorm")):
         return double_residual_rms_norm_ref(residual, a, w1, w2, eps, w_off)
     z = rms_norm(a, w1, eps, w_off)
     return residual_rms_norm(residual, z, w2, eps, w_off)
@@ -242,13 +243,13 @@ class _LayerNorm(torch.autograd.Function):
 
 
 def layer_norm(x, w, b, eps=1e-12):
-    if not _native_ok(x, w, b):
+    if not (_native_ok(x, w, b) and enabled("fused_layernorm")):
         return layer_norm_ref(x, w, b, eps)
     return _LayerNorm.apply(x, None, w, b, eps)[0]
 
 
 def residual_layer_norm(residual, x, w, b, eps=1e-12):
     """``nr = residual + x`` then LayerNorm; returns ``(y, nr)`` (BERT post-norm)."""
-    if not _native_ok(residual, x, w, b):
+    if not (_native_ok(residual, x, w, b) and enabled("fused_layernorm")):
         return residual_layer_norm_ref(residual, x, w, b, eps)
     return _LayerNorm.apply(x, residual, w, b, eps)

@@ -12,12 +12,13 @@ import torch
 import torch.nn.functional as F
 
 from . import _native as nv
+from .runtime_options import enabled
 
 _EPS = 1e-12
 
 
 def _bf16_cuda(*ts):
-    return nv.use_native(*ts) and all(t.dtype == torch.bfloat16 for t in ts if t.is_floating_point())
+    return enabled("fused_pool_normalize") and nv.use_native(*ts) and all(t.dtype == torch.bfloat16 for t in ts if t.is_floating_point())
 
 
 class _GatherL2Norm(torch.autograd.Function):

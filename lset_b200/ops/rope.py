@@ -12,6 +12,7 @@ import torch
 
 from . import _native as nv
 from .norm import scratch
+from .runtime_options import enabled
 
 _tables = {}
 
@@ -156,7 +157,8 @@ class _QkNormRope(torch.autograd.Function):
 def qk_norm_rope(q, k, qw, kw, cos, sin, pos, eps=1e-6, w_off=0.0):
     """Per-head RMSNorm (skipped when ``qw`` is None) followed by RoPE on ``q [T,Hq,hd]`` and
     ``k [T,Hk,hd]``; ``pos [T]`` holds each token's position. Returns new ``(q, k)`` tensors."""
-    native = nv.use_native(q, k) and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128, 256)
+    native = (nv.use_native(q, k) and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128, 256)
+              and enabled("fused_qk_norm_rope"))
     if not native:
         return qk_norm_rope_ref(q, k, qw, kw, cos, sin, pos, eps, w_off)
     return _QkNormRope.apply(q, k, qw, kw, cos, sin, pos, eps, w_off)
