@@ -328,7 +328,7 @@ __global__ void colsum_kernel(const float* __restrict__ partial, int P, int C, v
 
 int bwd_grid(int N, int rows_per_cta) {
   const int need = (N + rows_per_cta - 1) / rows_per_cta;
-  const int cap = row_num_sms() * 2;
+  const int cap = row_num_sms() * 8;
   return need < cap ? (need > 0 ? need : 1) : cap;
 }
 
@@ -339,7 +339,7 @@ using namespace lb;
 
 // Number of fp32 partial rows that the backward kernels may write (scratch = rows * H floats for
 // RMSNorm, rows * 2H for LayerNorm).
-extern "C" int lb_norm_bwd_partial_rows() { return row_num_sms() * 2; }
+extern "C" int lb_norm_bwd_partial_rows() { return row_num_sms() * 8; }
 
 extern "C" int lb_rms_norm_fwd(const void* x, const void* res_in, const void* w, void* y,
                                void* res_out, float* rstd, int N, int H, float eps, float w_off,

@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_bwd_kernel(RopeBwdArgs a)
 
 using namespace lb;
 
-extern "C" int lb_rope_bwd_partial_rows() { return row_num_sms() * 2; }
+extern "C" int lb_rope_bwd_partial_rows() { return row_num_sms() * 8; }
 
 extern "C" int lb_qk_norm_rope_fwd(const void* q_in, long long ldq_in, const void* k_in,
                                    long long ldk_in, const void* qw, const void* kw,
@@ -307,7 +307,7 @@ extern "C" int lb_qk_norm_rope_bwd(const void* dq, long long lddq, const void* d
   auto grid_for = [&](int lph) {
     const long long upb = kRowThreads / lph;
     long long g = (units + upb - 1) / upb;
-    const long long cap = 1LL * row_num_sms() * 2;
+    const long long cap = 1LL * row_num_sms() * 8;
     return int(g < cap ? (g > 0 ? g : 1) : cap);
   };
   int grid;

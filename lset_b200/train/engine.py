@@ -164,10 +164,10 @@ class TrainingEngine:
 
             if qlora:
                 apply_qlora(model, r=lora_r, alpha=lora_alpha, dropout=lora_dropout,
-                            targets=lora_targets, block_size=qlora_block_size)
+                            target_modules=lora_targets, block_size=qlora_block_size)
             else:
                 apply_lora(model, r=lora_r, alpha=lora_alpha, dropout=lora_dropout,
-                           targets=lora_targets)
+                           target_modules=lora_targets)
         if fp8:
             from .quantization.fp8 import apply_fp8_training
 
