@@ -1,0 +1,201 @@
+// Sharded-optimizer collectives fused with their compute, over NVLink peer memory.
+//
+// Every rank keeps, per parameter group, a full fp32 gradient buffer and a full bf16 parameter
+// buffer in symmetric memory (same size on all ranks, all peers mapped). Rank r owns the slice
+// [lo, lo + n) of each.
+//
+//   reduce_shard   g[i] = scale * sum_p grad_p[lo + i]   (p over all ranks, plain peer loads, fp32
+//                  accumulation in a rank-rotated order)  + per-CTA sum of squares for the norm.
+//                  = reduce-scatter fused with the averaging and the gradient-norm reduction.
+//   adamw_push     AdamW on the owned slice (fp32 master + moments), then the new bf16 values are
+//                  stored into EVERY rank's parameter buffer = optimizer step fused with the
+//                  parameter all-gather (a push: each byte crosses NVLink once per peer).
+//
+// Neither kernel waits on another GPU: ordering between ranks (gradients complete before they are
+// read, pushes complete before the next forward) is established on the host side by stream-ordered
+// collectives, so there is no device-side spin here at all.
+//
+// Replaces, for the sharded runtime, the NCCL reduce-scatter / all-gather that FSDP2 issues for the
+// reference (lset/distributed/parallel.py:129-160) plus clip_grad_norm_ and AdamW(fused=True)
+// (lset/train/engine.py:258-264,399-406).
+#include "../common/row.cuh"
+
+namespace lb {
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int kMaxPeers = 16;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+__global__ void __launch_bounds__(256)
+    reduce_shard_kernel(PeerPtrs grads, int world, int rank, long long lo, long long n, float scale,
+                        float* __restrict__ out, float* __restrict__ sumsq_partial) {
+  __shared__ float sred[8];
+  float ss = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += 1LL * gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;  // start with the local copy, then walk the peers
+      const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + lo)[i];
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    acc.x *= scale;
+    acc.y *= scale;
+    acc.z *= scale;
+    acc.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float a = 0.f;
+      for (int k = 0; k < world; ++k)
+        a += static_cast<const float*>(grads.p[(rank + k) % world])[lo + i];
+      a *= scale;
+      out[i] = a;
+      ss += a * a;
+    }
+  }
+  ss = row_sum<256>(ss, sred);
+  if (threadIdx.x == 0) sumsq_partial[blockIdx.x] = ss;
+}
+
+__global__ void __launch_bounds__(256)
+    sumsq_fold_kernel(const float* __restrict__ partial, int P, float* __restrict__ out) {
+  __shared__ float sred[8];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < P; i += blockDim.x) s += partial[i];
+  s = row_sum<256>(s, sred);
+  if (threadIdx.x == 0) out[0] += s;
+}
+
+struct AdamPushArgs {
+  float* p;
+  const float* g;
+  float* m;
+  float* v;
+  PeerPtrs params;  // bf16 parameter buffers of all ranks
+  int world, rank;
+  long long lo, n;
+  float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt;
+  const float* coef;
+};
+
+__global__ void __launch_bounds__(256) adamw_push_kernel(AdamPushArgs a) {
+  const float gs = a.coef != nullptr ? a.coef[0] : 1.f;
+  const float step = a.lr / a.bc1;
+  const float decay = 1.f - a.lr * a.wd;
+  const long long n4 = a.n / 4;
+  for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += 1LL * gridDim.x * blockDim.x) {
+    float4 p = reinterpret_cast<float4*>(a.p)[i];
+    const float4 g = reinterpret_cast<const float4*>(a.g)[i];
+    float4 m = reinterpret_cast<float4*>(a.m)[i];
+    float4 v = reinterpret_cast<float4*>(a.v)[i];
+    float* pp = &p.x;
+    const float* gp = &g.x;
+    float* mp = &m.x;
+    float* vp = &v.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gp[j] * gs;
+      mp[j] = a.beta1 * mp[j] + (1.f - a.beta1) * gj;
+      vp[j] = a.beta2 * vp[j] + (1.f - a.beta2) * gj * gj;
+      pp[j] = pp[j] * decay - step * mp[j] / (sqrtf(vp[j]) / a.bc2_sqrt + a.eps);
+    }
+    reinterpret_cast<float4*>(a.p)[i] = p;
+    reinterpret_cast<float4*>(a.m)[i] = m;
+    reinterpret_cast<float4*>(a.v)[i] = v;
+    __nv_bfloat162 lo2 = __floats2bfloat162_rn(p.x, p.y);
+    __nv_bfloat162 hi2 = __floats2bfloat162_rn(p.z, p.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo2);
+    o.y = *reinterpret_cast<uint32_t*>(&hi2);
+    for (int k = 0; k < a.world; ++k) {
+      bf16* dst = static_cast<bf16*>(a.params.p[(a.rank + k) % a.world]) + a.lo;
+      reinterpret_cast<uint2*>(dst)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < a.n; i += blockDim.x) {
+      const float gj = a.g[i] * gs;
+      const float mj = a.beta1 * a.m[i] + (1.f - a.beta1) * gj;
+      const float vj = a.beta2 * a.v[i] + (1.f - a.beta2) * gj * gj;
+      const float pj = a.p[i] * decay - step * mj / (sqrtf(vj) / a.bc2_sqrt + a.eps);
+      a.p[i] = pj;
+      a.m[i] = mj;
+      a.v[i] = vj;
+      for (int k = 0; k < a.world; ++k)
+        (static_cast<bf16*>(a.params.p[(a.rank + k) % a.world]) + a.lo)[i] = __float2bfloat16_rn(pj);
+    }
+  }
+}
+
+int comm_grid(long long n4) {
+  long long g = (n4 + 255) / 256;
+  const long long cap = 1LL * row_num_sms() * 4;
+  if (g > cap) g = cap;
+  return int(g < 1 ? 1 : g);
+}
+
+}  // namespace
+}  // namespace lb
+
+using namespace lb;
+
+extern "C" int lb_reduce_shard_partial_rows() { return row_num_sms() * 4; }
+
+// grad_ptrs: host array of `world` device pointers (fp32 full gradient buffers, own included).
+// out: fp32 [n]; sumsq: device scalar that receives += sum(out^2); scratch: partial_rows floats.
+// lo must be a multiple of 4 elements.
+extern "C" int lb_reduce_shard_f32(const void* const* grad_ptrs, int world, int rank, long long lo,
+                                   long long n, float scale, float* out, float* scratch,
+                                   float* sumsq, void* stream) {
+  if (n <= 0) return 0;
+  if (world < 1 || world > kMaxPeers || (lo & 3)) return -3;
+  PeerPtrs pp;
+  for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(grad_ptrs[i]);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = comm_grid(n / 4);
+  reduce_shard_kernel<<<grid, 256, 0, st>>>(pp, world, rank, lo, n, scale, out, scratch);
+  if (sumsq != nullptr) sumsq_fold_kernel<<<1, 256, 0, st>>>(scratch, grid, sumsq);
+  return launch_rc();
+}
+
+// param_ptrs: host array of `world` device pointers to the bf16 parameter buffers of all ranks.
+extern "C" int lb_adamw_push(float* p, const float* g, float* m, float* v,
+                             const void* const* param_ptrs, int world, int rank, long long lo,
+                             long long n, float lr, float beta1, float beta2, float eps, float wd,
+                             float bc1, float bc2_sqrt, const float* coef, void* stream) {
+  if (n <= 0) return 0;
+  if (world < 1 || world > kMaxPeers || (lo & 3)) return -3;
+  AdamPushArgs a;
+  a.p = p;
+  a.g = g;
+  a.m = m;
+  a.v = v;
+  for (int i = 0; i < world; ++i) a.params.p[i] = const_cast<void*>(param_ptrs[i]);
+  a.world = world;
+  a.rank = rank;
+  a.lo = lo;
+  a.n = n;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.wd = wd;
+  a.bc1 = bc1;
+  a.bc2_sqrt = bc2_sqrt;
+  a.coef = coef;
+  adamw_push_kernel<<<comm_grid(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return launch_rc();
+}

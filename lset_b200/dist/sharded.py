@@ -43,7 +43,7 @@ class FlatGroup:
     """One communication / optimizer unit: the trainable parameters of a set of modules."""
 
     def __init__(self, name: str, params: Sequence[nn.Parameter], world: int, rank: int,
-                 compute_dtype: torch.dtype, device: torch.device):
+                 compute_dtype: torch.dtype, device: torch.device, group=None, use_symm: bool = False):
         self.name = name
         self.params = list(params)
         self.world, self.rank = world, rank
@@ -62,8 +62,21 @@ class FlatGroup:
         full_master = torch.zeros(self.numel, dtype=torch.float32, device=device)
         for p, o in zip(self.params, offs):
             full_master[o:o + p.numel()] = p.data.detach().reshape(-1).to(device, torch.float32)
-        self.flat_param = full_master.to(compute_dtype)
-        self.flat_grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
+        self.symm_param = self.symm_grad = None
+        if use_symm and compute_dtype == torch.bfloat16:
+            from . import symm
+
+            self.symm_param = symm.try_alloc(self.numel, compute_dtype, device, group)
+            self.symm_grad = (symm.try_alloc(self.numel, torch.float32, device, group)
+                              if self.symm_param is not None else None)
+        if self.symm_grad is not None:
+            self.flat_param = self.symm_param.local
+            self.flat_param.copy_(full_master.to(compute_dtype))
+            self.flat_grad = self.symm_grad.local
+        else:
+            self.symm_param = None
+            self.flat_param = full_master.to(compute_dtype)
+            self.flat_grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
         self.master = full_master[self.lo:self.hi].clone()
         del full_master
         self.exp_avg = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
@@ -93,9 +106,10 @@ class ParamStore:
     def __init__(self, module: nn.Module, layer_modules: Optional[Iterable[nn.Module]] = None,
                  dp_group=None, compute_dtype: torch.dtype = torch.bfloat16,
                  device: Optional[torch.device] = None, reshard_after_forward: bool = False,
-                 overlap: bool = True):
+                 overlap: bool = True, tp_group=None):
         self.module = module
         self.dp_group = dp_group
+        self.tp_group = tp_group
         if dist.is_available() and dist.is_initialized():
             self.world, self.rank = dist.get_world_size(dp_group), dist.get_rank(dp_group)
         else:
@@ -105,20 +119,40 @@ class ParamStore:
         self.device = torch.device(device)
         self.compute_dtype = compute_dtype
         self.requires_gradient_sync = True
+        from . import symm as _symm
+
+        self.use_symm = _symm.enabled(self.world, self.device)
         self.groups: List[FlatGroup] = []
         claimed = set()
         layers = list(layer_modules) if layer_modules is not None else list(getattr(module, "layers", []))
-        self._layer_of_group = {}
+        self._groups_of_layer = []  # (layer module, [groups])
+
+        def make_groups(name, ps):
+            # tensor-parallel shards and replicated parameters go to separate groups: their
+            # squared norms are combined differently across the tensor-parallel ranks
+            out = []
+            for tag, sel in (("", [p for p in ps if not getattr(p, "_tp_sharded", False)]),
+                             (".tp", [p for p in ps if getattr(p, "_tp_sharded", False)])):
+                if sel:
+                    g = FlatGroup(name + tag, sel, self.world, self.rank, compute_dtype, self.device,
+                                  dp_group, self.use_symm)
+                    g.tp_sharded = bool(tag)
+                    out.append(g)
+            return out
+
         for i, layer in enumerate(layers):
             ps = [p for p in layer.parameters() if p.requires_grad and id(p) not in claimed]
             claimed.update(id(p) for p in ps)
             if ps:
-                g = FlatGroup(f"layers.{i}", ps, self.world, self.rank, compute_dtype, self.device)
-                self._layer_of_group[len(self.groups)] = layer
-                self.groups.append(g)
+                gs = make_groups(f"layers.{i}", ps)
+                self._groups_of_layer.append((layer, gs))
+                self.groups.extend(gs)
         rest = [p for p in module.parameters() if p.requires_grad and id(p) not in claimed]
         if rest:
-            self.groups.append(FlatGroup("root", rest, self.world, self.rank, compute_dtype, self.device))
+            self.groups.extend(make_groups("root", rest))
+        self.use_symm = self.use_symm and all(g.symm_grad is not None for g in self.groups)
+        # squared norm of the reduced shards: [0] replicated parameters, [1] tensor-parallel shards
+        self.sumsq = torch.zeros(2, dtype=torch.float32, device=self.device)
         # frozen parameters and buffers: just move / cast, they stay replicated
         for p in module.parameters():
             if not p.requires_grad:
@@ -133,15 +167,16 @@ class ParamStore:
 
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self) -> None:
-        for gi, layer in self._layer_of_group.items():
-            g = self.groups[gi]
+        for layer, gs in self._groups_of_layer:
 
-            def after_backward(_mod, _gin, _gout, g=g):
+            def after_backward(_mod, _gin, _gout, gs=gs):
                 if self.requires_gradient_sync:
-                    self._reduce_group(g)
+                    for g in gs:
+                        self._reduce_group(g)
 
-            def before_forward(_mod, _args, g=g):
-                self._wait_gather(g)
+            def before_forward(_mod, _args, gs=gs):
+                for g in gs:
+                    self._wait_gather(g)
 
             self._hooks.append(layer.register_full_backward_hook(after_backward))
             self._hooks.append(layer.register_forward_pre_hook(before_forward))
@@ -167,12 +202,32 @@ class ParamStore:
         g.reduced = True
 
     def _reduce_scatter(self, g: FlatGroup) -> None:
+        if self.use_symm:
+            # All ranks' gradients for this group must be complete before anyone reads them: a
+            # one-element all-reduce on this (side) stream orders the kernels across ranks.
+            dist.all_reduce(self._token(), group=self.dp_group)
+            lib = nv.load()
+            scr = scratch("reduce_shard", lib.lb_reduce_shard_partial_rows(), self.device)
+            rc = lib.lb_reduce_shard_f32(
+                g.symm_grad.c_ptr_array(), nv.c_int(self.world), nv.c_int(self.rank), nv.c_ll(g.lo),
+                nv.c_ll(g.shard_numel), nv.c_float(1.0 / self.world),
+                nv.c_void_p(g.grad_shard.data_ptr()), nv.c_void_p(scr.data_ptr()),
+                nv.c_void_p(self.sumsq.data_ptr() + (4 if getattr(g, "tp_sharded", False) else 0)),
+                nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_reduce_shard_f32")
+            nv.count_launch(2)
+            return
         if g.flat_grad.is_cuda:
             dist.reduce_scatter_tensor(g.grad_shard, g.flat_grad, op=dist.ReduceOp.AVG,
                                        group=self.dp_group)
         else:  # gloo: no reduce-scatter
             dist.all_reduce(g.flat_grad, op=dist.ReduceOp.SUM, group=self.dp_group)
             g.grad_shard.copy_(g.flat_grad[g.lo:g.hi]).div_(self.world)
+
+    def _token(self) -> torch.Tensor:
+        if getattr(self, "_tok", None) is None:
+            self._tok = torch.zeros(1, dtype=torch.float32, device=self.device)
+        return self._tok
 
     def finish_backward(self) -> None:
         """Call after ``loss.backward()``: reduces whatever the hooks did not cover (root group,
@@ -194,6 +249,11 @@ class ParamStore:
     def gather_params(self) -> None:
         """All-gather the updated bf16 shards (after an optimizer step)."""
         if self.world == 1:
+            return
+        if self.use_symm:
+            # adamw_push already stored the new shards into every rank's buffer; one collective
+            # orders "all pushes done" before the next forward on every rank.
+            dist.all_reduce(self._token(), group=self.dp_group)
             return
         for g in self.groups:
             if self.comm_stream is not None:
@@ -221,6 +281,7 @@ class ParamStore:
         for g in self.groups:
             g.flat_grad.zero_()
             g.reduced = False
+        self.sumsq.zero_()
 
     def trainable_parameters(self):
         for g in self.groups:
@@ -277,6 +338,7 @@ class ShardedAdamW:
         self.step_count = 0
         dev = store.device
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._parts = torch.zeros(2, dtype=torch.float32, device=dev)
         self._coef = torch.ones(2, dtype=torch.float32, device=dev)  # [clip coefficient, norm]
         self.state = {}  # torch.optim.Optimizer API expected by LR schedulers
 
@@ -293,20 +355,32 @@ class ShardedAdamW:
         return self._coef[1]
 
     def _global_sumsq(self) -> None:
+        """Squared global gradient norm into ``self._sumsq``: shards of tensor-parallel parameters
+        are summed over the tensor-parallel group, replicated ones counted once, then everything is
+        summed over the data-parallel shards."""
         st = self.store
         native = st.device.type == "cuda"
-        self._sumsq.zero_()
-        for g in st.groups:
-            if native:
-                lib = nv.load()
-                scr = scratch("sumsq", lib.lb_sumsq_partial_rows(), st.device)
-                rc = lib.lb_sumsq_f32(nv.c_void_p(g.grad_shard.data_ptr()), nv.c_ll(g.grad_shard.numel()),
-                                      nv.c_void_p(scr.data_ptr()), nv.c_void_p(self._sumsq.data_ptr()),
-                                      nv.c_int(1), nv.c_void_p(nv.stream_ptr()))
-                nv.check_rc(rc, "lb_sumsq_f32")
-                nv.count_launch(2)
-            else:
-                self._sumsq.add_(g.grad_shard.float().pow(2).sum())
+        parts = self._parts
+        parts.zero_()
+        if st.use_symm:
+            parts.copy_(st.sumsq)  # accumulated by the reduce kernels
+        else:
+            for g in st.groups:
+                slot = 1 if getattr(g, "tp_sharded", False) else 0
+                if native:
+                    lib = nv.load()
+                    scr = scratch("sumsq", lib.lb_sumsq_partial_rows(), st.device)
+                    rc = lib.lb_sumsq_f32(nv.c_void_p(g.grad_shard.data_ptr()),
+                                          nv.c_ll(g.grad_shard.numel()), nv.c_void_p(scr.data_ptr()),
+                                          nv.c_void_p(parts.data_ptr() + 4 * slot), nv.c_int(1),
+                                          nv.c_void_p(nv.stream_ptr()))
+                    nv.check_rc(rc, "lb_sumsq_f32")
+                    nv.count_launch(2)
+                else:
+                    parts[slot] += g.grad_shard.float().pow(2).sum()
+        if st.tp_group is not None and dist.get_world_size(st.tp_group) > 1:
+            dist.all_reduce(parts[1:2], op=dist.ReduceOp.SUM, group=st.tp_group)
+        torch.sum(parts, dim=0, keepdim=True, out=self._sumsq)
         if st.world > 1:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=st.dp_group)
 
@@ -333,7 +407,17 @@ class ShardedAdamW:
                 if self.grad_clip > 0 else 1.0
         for g in st.groups:
             pshard = g.flat_param[g.lo:g.hi]
-            if native:
+            if st.use_symm:
+                rc = nv.load().lb_adamw_push(
+                    nv.c_void_p(g.master.data_ptr()), nv.c_void_p(g.grad_shard.data_ptr()),
+                    nv.c_void_p(g.exp_avg.data_ptr()), nv.c_void_p(g.exp_avg_sq.data_ptr()),
+                    g.symm_param.c_ptr_array(), nv.c_int(st.world), nv.c_int(st.rank), nv.c_ll(g.lo),
+                    nv.c_ll(g.shard_numel), nv.c_float(lr), nv.c_float(b1), nv.c_float(b2),
+                    nv.c_float(eps), nv.c_float(wd), nv.c_float(bc1), nv.c_float(bc2s),
+                    nv.c_void_p(self._coef.data_ptr()), nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_adamw_push")
+                nv.count_launch()
+            elif native:
                 rc = nv.load().lb_adamw_f32(
                     nv.c_void_p(g.master.data_ptr()), nv.c_void_p(g.grad_shard.data_ptr()),
                     nv.c_void_p(g.exp_avg.data_ptr()), nv.c_void_p(g.exp_avg_sq.data_ptr()),

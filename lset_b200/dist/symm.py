@@ -1,0 +1,57 @@
+"""Symmetric memory: buffers of identical size on every rank of a group, with every peer's copy
+mapped into this process, for kernels that read or write other GPUs directly over NVLink.
+
+Allocation and handle exchange go through ``torch.distributed._symmetric_memory`` (the plumbing);
+what is returned to the kernels is just the list of peer base pointers. ``enabled()`` reports
+whether the runtime should use the peer-memory kernels: CUDA, more than one rank, and
+``LSET_B200_SYMM`` not set to ``0``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def enabled(world: int, device: torch.device) -> bool:
+    return (world > 1 and device.type == "cuda" and os.environ.get("LSET_B200_SYMM", "1") != "0")
+
+
+class SymmBuffer:
+    """A 1-D symmetric tensor. ``local`` is this rank's copy; ``peer_ptrs[r]`` is rank r's base
+    address as seen from this process (``peer_ptrs[rank] == local.data_ptr()``)."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.local = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group)
+        self.world = self.handle.world_size
+        self.rank = self.handle.rank
+        self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self._c_ptrs = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
+        self.local.zero_()
+
+    def c_ptr_array(self):
+        """``void* const*`` argument for the native launchers (host array of peer pointers)."""
+        return self._c_ptrs
+
+    def offset_ptrs(self, byte_offset: int):
+        return (ctypes.c_void_p * self.world)(*[p + byte_offset for p in self.peer_ptrs])
+
+
+def try_alloc(numel: int, dtype, device, group=None) -> Optional[SymmBuffer]:
+    """SymmBuffer, or None with a one-line notice when peer mapping is unavailable on this system."""
+    try:
+        return SymmBuffer(numel, dtype, device, group)
+    except Exception as exc:  # pragma: no cover - depends on the machine
+        if not getattr(try_alloc, "_warned", False):
+            print(f"[lset_b200] symmetric memory unavailable ({type(exc).__name__}: {exc}); "
+                  "using NCCL collectives for the sharded runtime", flush=True)
+            try_alloc._warned = True
+        return None

@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native as nv
+from ._ac import run_expensive
 from .runtime_options import options as _rt
 
 
@@ -150,7 +151,7 @@ class _VarlenAttn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, plan, causal, scale):
         q, k, v = _unit_inner(q), _unit_inner(k), _unit_inner(v)
-        o, lse = _native_fwd(q, k, v, plan, causal, scale)
+        o, lse = run_expensive(lambda: _native_fwd(q, k, v, plan, causal, scale))
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.plan, ctx.causal, ctx.scale = plan, causal, scale
         return o
@@ -177,7 +178,7 @@ class _QkvAttention(torch.autograd.Function):
 
         q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hk], qkv[:, Hq + Hk:]
         q_r, k_r, q_rstd, k_rstd = rope_fwd_native(q, k, qw, kw, cos, sin, pos, eps, w_off)
-        o, lse = _native_fwd(q_r, k_r, v, plan, causal, scale)
+        o, lse = run_expensive(lambda: _native_fwd(q_r, k_r, v, plan, causal, scale))
         ctx.save_for_backward(qkv, qw, kw, cos, sin, pos, q_r, k_r, q_rstd, k_rstd, o, lse)
         ctx.meta = (plan, Hq, Hk, causal, scale, w_off)
         return o

@@ -195,7 +195,8 @@ class TrainingEngine:
 
         # ---------------------------------------------------------------- sharded runtime + optimizer
         self.store = ParamStore(model, dp_group=self.dp_group if world > 1 else None,
-                                compute_dtype=self.compute_dtype, device=self.device)
+                                compute_dtype=self.compute_dtype, device=self.device,
+                                tp_group=self.tp_group)
         if self.task.logit_scale is not None:
             self.task_store = ParamStore(self.task, layer_modules=[], dp_group=None,
                                          compute_dtype=torch.float32, device=self.device)

@@ -1,0 +1,64 @@
+"""Host-side failure detection: a step watchdog.
+
+The training loop calls ``beat()`` once per step. A daemon thread checks the time since the last
+beat; when it exceeds the limit (a hung collective, a dead peer, a stuck data loader) it prints a
+diagnostic, runs the optional ``on_timeout`` callback and ends the process with a non-zero exit
+code, so that the launcher (``torchrun --max-restarts``) can restart the job, which then resumes
+from the newest complete checkpoint. The reference has no counterpart (no watchdog, heartbeat or
+timeout anywhere; lset/cli.py:56-67 only propagates the launcher's return code).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import threading
+import time
+from typing import Callable, Optional
+
+EXIT_CODE = 75  # EX_TEMPFAIL: the job may be retried
+
+
+class StepWatchdog:
+    def __init__(self, limit_s: float, on_timeout: Optional[Callable[[float], None]] = None,
+                 poll_s: Optional[float] = None, exit_process: bool = True):
+        self.limit_s = float(limit_s)
+        self.on_timeout = on_timeout
+        self.poll_s = poll_s if poll_s is not None else max(0.05, min(1.0, self.limit_s / 4))
+        self.exit_process = exit_process
+        self.fired = False
+        self._last = time.monotonic()
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    def beat(self) -> None:
+        self._last = time.monotonic()
+
+    def start(self) -> None:
+        if self._thread is not None:
+            return
+        self.beat()
+        self._thread = threading.Thread(target=self._run, name="lset-b200-watchdog", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2 * self.poll_s + 1)
+            self._thread = None
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.poll_s):
+            idle = time.monotonic() - self._last
+            if idle > self.limit_s:
+                self.fired = True
+                rank = os.environ.get("RANK", "0")
+                print(f"[watchdog] rank {rank}: no training step finished for {idle:.1f} s "
+                      f"(limit {self.limit_s:.1f} s); aborting", file=sys.stderr, flush=True)
+                if self.on_timeout is not None:
+                    try:
+                        self.on_timeout(idle)
+                    except Exception as exc:  # pragma: no cover
+                        print(f"[watchdog] on_timeout raised {exc!r}", file=sys.stderr)
+                if self.exit_process:
+                    os._exit(EXIT_CODE)
+                return
