@@ -1,10 +1,15 @@
 // Varlen flash attention backward on tcgen05, without atomics: three launches.
 //
 //   delta     delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]
-//   dQ        one CTA per (sequence, query tile, KV head), walking KV blocks of 64:
-//               S = Q·Kᵀ, dP = dO·Vᵀ (TMEM) -> dS = P∘(dP − delta)·scale (bf16, smem) -> dQ += dS·K
-//   dK/dV     one CTA per (sequence, 128-row KV tile, KV head), walking (query block, head) pairs:
+//   dQ        one 256-thread CTA per (sequence, query tile, KV head), two CTAs per SM, walking KV
+//             blocks of 64:
+//               S = Q·Kᵀ, dP = dO·Vᵀ (TMEM) -> dS = P∘(dP − delta)·scale (bf16, written over the V
+//               block in smem) -> dQ += dS·K
+//   dK/dV     one 256-thread CTA per (sequence, 128-row KV tile, KV head), walking (query block,
+//             head) pairs through a 3-deep TMA ring, with Sᵀ/dPᵀ double-buffered in TMEM so the
+//             products of step i+1 run while step i is in the softmax-gradient math:
 //               Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (TMEM) -> Pᵀ, dSᵀ (bf16, smem) -> dV += Pᵀ·dO, dK += dSᵀ·Q
+// In both kernels thread t owns accumulator row t % 128 and half (t / 128) of the 64 columns.
 // The Q / dO / K / V tiles are loaded once by TMA and serve both as K-major operands (contraction
 // over head_dim) and as MN-major operands (contraction over tokens); nothing is transposed in
 // memory. Probabilities are recomputed from the forward's LSE.
@@ -93,6 +98,51 @@ __device__ __forceinline__ void st_row_bf16_swz(uint8_t* tile, int row, const fl
   }
 }
 
+__device__ __forceinline__ void ld_row32(uint32_t taddr, float (&s)[32]) {
+  uint32_t t0[32];
+  tmem_ld_32x32b_x32(taddr, t0);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(t0[c]);
+}
+
+// Write 32 values of one row into columns [32*half, 32*half+32) of a 128-row x 64-column bf16 tile
+// stored K-major with the 128-byte swizzle.
+__device__ __forceinline__ void st_half_row_bf16_swz(uint8_t* tile, int row, int half,
+                                                     const float (&v)[32]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = pack_bf16x2(v[c * 8 + 0], v[c * 8 + 1]);
+    q.y = pack_bf16x2(v[c * 8 + 2], v[c * 8 + 3]);
+    q.z = pack_bf16x2(v[c * 8 + 4], v[c * 8 + 5]);
+    q.w = pack_bf16x2(v[c * 8 + 6], v[c * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + swz128_offset(row, half * 4 + c)) = q;
+  }
+}
+
+// Store NCOLS accumulator columns (fp32, starting at taddr) of one row as bf16 to dst when `pred`.
+template <int NCOLS>
+__device__ __forceinline__ void store_acc_cols(uint32_t taddr, bf16* dst, bool pred) {
+#pragma unroll 1
+  for (int c = 0; c < NCOLS / 32; ++c) {
+    uint32_t o[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, o);
+    tmem_ld_wait();
+    if (pred) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 q;
+        q.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+        q.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+        q.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+        q.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = q;
+      }
+    }
+  }
+}
+
 // Store one accumulator row (HD fp32 columns starting at taddr) as bf16 to dst when `pred`.
 template <int HD>
 __device__ __forceinline__ void store_acc_row(uint32_t taddr, bf16* dst, bool pred) {
@@ -116,19 +166,23 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, bf16* dst, bool pr
 }
 
 // ------------------------------------------------------------------------------------ dQ
+constexpr int kBwdThreads = 256;
+
 template <int HD>
 struct DqCfg {
   static constexpr int PANELS = HD / 64;
   static constexpr int Q_BYTES = 128 * HD * 2;
   static constexpr int KV_BYTES = kAttnKvBlock * HD * 2;
   static constexpr int DS_BYTES = 128 * kAttnKvBlock * 2;
-  static constexpr int SMEM_BYTES = 2 * Q_BYTES + 4 * KV_BYTES + DS_BYTES + 1024 + 128;
+  // dS is written over the V block (V is dead once dP = dO·Vᵀ has completed) when it fits.
+  static constexpr bool DS_IN_V = KV_BYTES >= DS_BYTES;
+  static constexpr int SMEM_BYTES = 2 * Q_BYTES + 2 * KV_BYTES + (DS_IN_V ? 0 : DS_BYTES) + 1024 + 128;
   static constexpr int DQ_COL = 128;
   static constexpr int TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kBwdThreads)
     attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    AttnBwdArgs a) {
@@ -152,21 +206,21 @@ __global__ void __launch_bounds__(128)
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + C::Q_BYTES;
   uint8_t* sK = sdO + C::Q_BYTES;
-  uint8_t* sV = sK + 2 * C::KV_BYTES;
-  uint8_t* sdS = sV + 2 * C::KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + C::DS_BYTES);
+  uint8_t* sV = sK + C::KV_BYTES;
+  uint8_t* sdS = C::DS_IN_V ? sV : (sV + C::KV_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + C::KV_BYTES + (C::DS_IN_V ? 0 : C::DS_BYTES));
   uint64_t* bar_q = bars;
-  uint64_t* bar_kv = bars + 1;  // [2]
-  uint64_t* bar_s = bars + 3;
-  uint64_t* bar_dq = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_kv = bars + 1;
+  uint64_t* bar_s = bars + 2;
+  uint64_t* bar_dq = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int half = warp >> 2;  // which 32 of the 64 KV columns this thread handles
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(&bar_kv[0], 1);
-    mbar_init(&bar_kv[1], 1);
+    mbar_init(bar_kv, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_dq, 1);
     mbar_fence_init();
@@ -179,17 +233,16 @@ __global__ void __launch_bounds__(128)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
 
   auto load_kv = [&](int j) {
-    const int buf = j & 1;
-    mbar_expect_tx(&bar_kv[buf], 2 * C::KV_BYTES);
+    mbar_expect_tx(bar_kv, 2 * C::KV_BYTES);
 #pragma unroll
     for (int p = 0; p < C::PANELS; ++p) {
-      tma_load_2d(sK + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmK, &bar_kv[buf],
-                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
-      tma_load_2d(sV + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmV, &bar_kv[buf],
-                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
+      tma_load_2d(sK + p * (kAttnKvBlock * 128), &tmK, bar_kv, hk * HD + p * 64,
+                  seq0 + j * kAttnKvBlock);
+      tma_load_2d(sV + p * (kAttnKvBlock * 128), &tmV, bar_kv, hk * HD + p * 64,
+                  seq0 + j * kAttnKvBlock);
     }
   };
   if (tid == 0) {
@@ -205,7 +258,7 @@ __global__ void __launch_bounds__(128)
     load_kv(0);
   }
 
-  const int r = tid;
+  const int r = tid & 127;
   const int g = r / QT;
   const int qpos = q0 + r % QT;
   const bool row_valid = qpos < len;
@@ -224,9 +277,8 @@ __global__ void __launch_bounds__(128)
     }
   }
   for (int j = 0; j < nblk && !failed; ++j) {
-    const int buf = j & 1;
     {
-      const bool ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1);
+      const bool ok = mbar_wait(bar_kv, j & 1);
       if (__syncthreads_or(!ok)) {
         report_status(a.status, kStatusTimeoutProducer);
         failed = true;
@@ -236,8 +288,7 @@ __global__ void __launch_bounds__(128)
     if (tid == 0) {
       tc_fence_after();
       const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
-      const uint32_t ka = smem_u32(sK + buf * C::KV_BYTES);
-      const uint32_t va = smem_u32(sV + buf * C::KV_BYTES);
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks) {
         const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
@@ -263,38 +314,29 @@ __global__ void __launch_bounds__(128)
       }
     }
     tc_fence_after();
-    float ds[64];
+    float ds[32];
     {
-      float s[64];
-      ld_row64(tmem_row, s);
-      ld_row64(tmem_row + 64, ds);
-      const int kv0 = j * kAttnKvBlock;
+      float s[32];
+      ld_row32(tmem_row + half * 32, s);
+      ld_row32(tmem_row + 64 + half * 32, ds);
+      const int kv0 = j * kAttnKvBlock + half * 32;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         const int kvpos = kv0 + c;
         const bool valid = row_valid && kvpos < len && (!a.causal || kvpos <= qpos);
         const float p = valid ? exp2f(s[c] * a.scale_log2 - lse2) : 0.f;
         ds[c] = p * (ds[c] - dlt) * a.scale;
       }
     }
-    if (j > 0) {
-      const bool ok = mbar_wait(bar_dq, (j - 1) & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
-      }
-      tc_fence_after();
-    }
-    if (tid == 0 && j + 1 < nblk) load_kv(j + 1);
-    st_row_bf16_swz(sdS, r, ds);
+    // S and dP are complete (bar_s), so the V block may be overwritten by dS
+    st_half_row_bf16_swz(sdS, r, half, ds);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
       const uint32_t sa = smem_u32(sdS);
-      const uint32_t ka = smem_u32(sK + buf * C::KV_BYTES);
+      const uint32_t ka = smem_u32(sK);
 #pragma unroll
       for (int ks = 0; ks < kAttnKvBlock / 16; ++ks)
         umma_bf16(tmem_base + C::DQ_COL, umma_smem_desc(sa + ks * 32, 16, 1024),
@@ -302,17 +344,21 @@ __global__ void __launch_bounds__(128)
                   (j > 0 || ks > 0) ? 1u : 0u);
       umma_commit(bar_dq);
     }
-  }
-  if (!failed) {
-    const bool ok = mbar_wait(bar_dq, (nblk - 1) & 1);
-    if (__syncthreads_or(!ok)) {
-      report_status(a.status, kStatusTimeoutMma);
-      failed = true;
+    // the K block and the dS/V slot are in use until this block's dQ product is done
+    {
+      const bool ok = mbar_wait(bar_dq, j & 1);
+      if (__syncthreads_or(!ok)) {
+        report_status(a.status, kStatusTimeoutMma);
+        failed = true;
+        break;
+      }
     }
+    if (tid == 0 && j + 1 < nblk) load_kv(j + 1);
   }
   if (!failed) {
     tc_fence_after();
-    store_acc_row<HD>(tmem_row + C::DQ_COL, a.dQ + tok * a.lddq + head * HD, row_valid);
+    store_acc_cols<HD / 2>(tmem_row + C::DQ_COL + half * (HD / 2),
+                           a.dQ + tok * a.lddq + head * HD + half * (HD / 2), row_valid);
   }
   tc_fence_before();
   __syncthreads();
@@ -325,16 +371,19 @@ struct DkvCfg {
   static constexpr int PANELS = HD / 64;
   static constexpr int KV_BYTES = 128 * HD * 2;  // resident K tile and V tile
   static constexpr int QB_BYTES = 64 * HD * 2;   // one query block of Q or dO
+  static constexpr int QBUFS = 3;                // TMA ring depth for (Q, dO) blocks
   static constexpr int PT_BYTES = 128 * 64 * 2;
-  static constexpr int SMEM_BYTES = 2 * KV_BYTES + 4 * QB_BYTES + 2 * PT_BYTES + 1024 + 1024 + 128;
-  static constexpr int DV_COL = 128;
-  static constexpr int DK_COL = 128 + HD;
-  static constexpr int TMEM_COLS = (128 + 2 * HD) <= 256 ? 256 : 512;
-  static_assert(128 + 2 * HD <= 512, "head_dim too large for the dK/dV accumulators");
+  static constexpr int SMEM_BYTES =
+      2 * KV_BYTES + 2 * QBUFS * QB_BYTES + 2 * PT_BYTES + 1024 /*stats*/ + 1024 /*align*/ + 128;
+  // TMEM: two (Sᵀ, dPᵀ) buffers of 64 + 64 columns, then the dV and dK accumulators.
+  static constexpr int DV_COL = 256;
+  static constexpr int DK_COL = 256 + HD;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(256 + 2 * HD <= 512, "head_dim too large for the dK/dV accumulators");
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kBwdThreads)
     attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     AttnBwdArgs a) {
@@ -357,25 +406,26 @@ __global__ void __launch_bounds__(128)
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::KV_BYTES;
-  uint8_t* sQ = sV + C::KV_BYTES;       // [2]
-  uint8_t* sdO = sQ + 2 * C::QB_BYTES;  // [2]
-  uint8_t* sPT = sdO + 2 * C::QB_BYTES;
+  uint8_t* sQ = sV + C::KV_BYTES;               // [QBUFS]
+  uint8_t* sdO = sQ + C::QBUFS * C::QB_BYTES;   // [QBUFS]
+  uint8_t* sPT = sdO + C::QBUFS * C::QB_BYTES;
   uint8_t* sdST = sPT + C::PT_BYTES;
   float* sStat = reinterpret_cast<float*>(sdST + C::PT_BYTES);  // [2 bufs][2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
   uint64_t* bar_kv = bars;
-  uint64_t* bar_q = bars + 1;  // [2]
-  uint64_t* bar_s = bars + 3;
-  uint64_t* bar_acc = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bar_q = bars + 1;    // [QBUFS]
+  uint64_t* bar_s = bars + 4;    // [2]
+  uint64_t* bar_acc = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int half = warp >> 2;
   if (tid == 0) {
     mbar_init(bar_kv, 1);
-    mbar_init(&bar_q[0], 1);
-    mbar_init(&bar_q[1], 1);
-    mbar_init(bar_s, 1);
+    for (int i = 0; i < C::QBUFS; ++i) mbar_init(&bar_q[i], 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
     mbar_init(bar_acc, 1);
     mbar_fence_init();
   }
@@ -387,10 +437,12 @@ __global__ void __launch_bounds__(128)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+  constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
+  constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
 
   auto load_q = [&](int i) {
-    const int buf = i & 1;
+    const int buf = i % C::QBUFS;
     const int qb = qb_start + i / G;
     const int head = hk * G + i % G;
     mbar_expect_tx(&bar_q[buf], 2 * C::QB_BYTES);
@@ -402,6 +454,36 @@ __global__ void __launch_bounds__(128)
                   seq0 + qb * 64);
     }
   };
+  // Sᵀ = K·Qᵀ and dPᵀ = V·dOᵀ of inner step i into TMEM buffer i & 1 (issued by thread 0).
+  auto issue_scores = [&](int i) -> bool {
+    const int buf = i % C::QBUFS;
+    if (!mbar_wait(&bar_q[buf], (i / C::QBUFS) & 1)) {
+      report_status(a.status, kStatusTimeoutProducer);
+      return false;
+    }
+    tc_fence_after();
+    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+    const uint32_t qa = smem_u32(sQ + buf * C::QB_BYTES);
+    const uint32_t da = smem_u32(sdO + buf * C::QB_BYTES);
+    const uint32_t dcol = tmem_base + (i & 1) * 128;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
+      const uint32_t boff = (ks / 4) * (64 * 128) + (ks % 4) * 32;
+      umma_bf16(dcol, umma_smem_desc(ka + aoff, 16, 1024), umma_smem_desc(qa + boff, 16, 1024),
+                idesc_s, ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
+      const uint32_t boff = (ks / 4) * (64 * 128) + (ks % 4) * 32;
+      umma_bf16(dcol + 64, umma_smem_desc(va + aoff, 16, 1024), umma_smem_desc(da + boff, 16, 1024),
+                idesc_s, ks > 0 ? 1u : 0u);
+    }
+    umma_commit(&bar_s[i & 1]);
+    return true;
+  };
+
   if (tid == 0) {
     mbar_expect_tx(bar_kv, 2 * C::KV_BYTES);
 #pragma unroll
@@ -409,13 +491,12 @@ __global__ void __launch_bounds__(128)
       tma_load_2d(sK + p * (128 * 128), &tmK, bar_kv, hk * HD + p * 64, seq0 + kv0);
       tma_load_2d(sV + p * (128 * 128), &tmV, bar_kv, hk * HD + p * 64, seq0 + kv0);
     }
-    load_q(0);
+    if (n_inner > 0) load_q(0);
+    if (n_inner > 1) load_q(1);
   }
-  const int r = tid;
+  const int r = tid & 127;
   const int kvpos = kv0 + r;
   const bool row_valid = kvpos < len;
-  constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
-  constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
   bool failed = false;
   {
     const bool ok = mbar_wait(bar_kv, 0);
@@ -424,48 +505,22 @@ __global__ void __launch_bounds__(128)
       failed = true;
     }
   }
+  if (!failed && tid == 0 && n_inner > 0) issue_scores(0);
+
   for (int i = 0; i < n_inner && !failed; ++i) {
-    const int buf = i & 1;
+    const int sb = i & 1;
+    const int qbuf = i % C::QBUFS;
     const int qb = qb_start + i / G;
     const int head = hk * G + i % G;
-    // stage this block's lse / delta (read by every row) while the tiles land
+    // stage this block's lse / delta (read by every row); visible after the barrier below
     if (tid < 64) {
       const int qp = qb * 64 + tid;
       const bool v = qp < len;
-      sStat[buf * 128 + tid] = v ? a.lse[1LL * head * a.T + seq0 + qp] * kLog2eF : 0.f;
-      sStat[buf * 128 + 64 + tid] = v ? a.delta[1LL * head * a.T + seq0 + qp] : 0.f;
+      sStat[sb * 128 + tid] = v ? a.lse[1LL * head * a.T + seq0 + qp] * kLog2eF : 0.f;
+      sStat[sb * 128 + 64 + tid] = v ? a.delta[1LL * head * a.T + seq0 + qp] : 0.f;
     }
     {
-      const bool ok = mbar_wait(&bar_q[buf], (i >> 1) & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutProducer);
-        failed = true;
-        break;
-      }
-    }
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      const uint32_t qa = smem_u32(sQ + buf * C::QB_BYTES);
-      const uint32_t da = smem_u32(sdO + buf * C::QB_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-        const uint32_t boff = (ks / 4) * (64 * 128) + (ks % 4) * 32;
-        umma_bf16(tmem_base, umma_smem_desc(ka + aoff, 16, 1024), umma_smem_desc(qa + boff, 16, 1024),
-                  idesc_s, ks > 0 ? 1u : 0u);
-      }
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-        const uint32_t boff = (ks / 4) * (64 * 128) + (ks % 4) * 32;
-        umma_bf16(tmem_base + 64, umma_smem_desc(va + aoff, 16, 1024),
-                  umma_smem_desc(da + boff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_s);
-    }
-    {
-      const bool ok = mbar_wait(bar_s, i & 1);
+      const bool ok = mbar_wait(&bar_s[sb], (i >> 1) & 1);
       if (__syncthreads_or(!ok)) {
         report_status(a.status, kStatusTimeoutMma);
         failed = true;
@@ -473,15 +528,15 @@ __global__ void __launch_bounds__(128)
       }
     }
     tc_fence_after();
-    float pt[64], dst[64];
-    ld_row64(tmem_row, pt);
-    ld_row64(tmem_row + 64, dst);
+    float pt[32], dst[32];
+    ld_row32(tmem_row + sb * 128 + half * 32, pt);
+    ld_row32(tmem_row + sb * 128 + 64 + half * 32, dst);
     {
-      const float* lse2 = sStat + buf * 128;
+      const float* lse2 = sStat + sb * 128 + half * 32;
       const float* dl = lse2 + 64;
-      const int qbase = qb * 64;
+      const int qbase = qb * 64 + half * 32;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         const int qp = qbase + c;
         const bool valid = row_valid && qp < len && (!a.causal || kvpos <= qp);
         const float p = valid ? exp2f(pt[c] * a.scale_log2 - lse2[c]) : 0.f;
@@ -490,6 +545,7 @@ __global__ void __launch_bounds__(128)
       }
     }
     if (i > 0) {
+      // previous dV/dK products done: the Pᵀ/dSᵀ tiles and ring slot (i-1) % 3 are free
       const bool ok = mbar_wait(bar_acc, (i - 1) & 1);
       if (__syncthreads_or(!ok)) {
         report_status(a.status, kStatusTimeoutMma);
@@ -498,17 +554,17 @@ __global__ void __launch_bounds__(128)
       }
       tc_fence_after();
     }
-    if (tid == 0 && i + 1 < n_inner) load_q(i + 1);
-    st_row_bf16_swz(sPT, r, pt);
-    st_row_bf16_swz(sdST, r, dst);
+    if (tid == 0 && i + 2 < n_inner) load_q(i + 2);
+    st_half_row_bf16_swz(sPT, r, half, pt);
+    st_half_row_bf16_swz(sdST, r, half, dst);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
       const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
-      const uint32_t qa = smem_u32(sQ + buf * C::QB_BYTES);
-      const uint32_t da = smem_u32(sdO + buf * C::QB_BYTES);
+      const uint32_t qa = smem_u32(sQ + qbuf * C::QB_BYTES);
+      const uint32_t da = smem_u32(sdO + qbuf * C::QB_BYTES);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma_bf16(tmem_base + C::DV_COL, umma_smem_desc(pa + ks * 32, 16, 1024),
@@ -520,6 +576,8 @@ __global__ void __launch_bounds__(128)
                   umma_smem_desc(qa + ks * 2048, 64 * 128, 1024), idesc_acc,
                   (i > 0 || ks > 0) ? 1u : 0u);
       umma_commit(bar_acc);
+      // run the next step's score products behind this step's accumulation
+      if (i + 1 < n_inner) issue_scores(i + 1);
     }
   }
   if (!failed && n_inner > 0) {
@@ -532,8 +590,10 @@ __global__ void __launch_bounds__(128)
   if (!failed && n_inner > 0) {
     tc_fence_after();
     const long long tok = 1LL * seq0 + kvpos;
-    store_acc_row<HD>(tmem_row + C::DV_COL, a.dV + tok * a.lddv + hk * HD, row_valid);
-    store_acc_row<HD>(tmem_row + C::DK_COL, a.dK + tok * a.lddk + hk * HD, row_valid);
+    store_acc_cols<HD / 2>(tmem_row + C::DV_COL + half * (HD / 2),
+                           a.dV + tok * a.lddv + hk * HD + half * (HD / 2), row_valid);
+    store_acc_cols<HD / 2>(tmem_row + C::DK_COL + half * (HD / 2),
+                           a.dK + tok * a.lddk + hk * HD + half * (HD / 2), row_valid);
   }
   tc_fence_before();
   __syncthreads();
@@ -573,7 +633,7 @@ int launch_bwd(const void* dO, long long lddo, const void* q, long long ldq, con
       configured = true;
     }
     a.plan = plan_q;
-    kern<<<dim3(cap_q, a.Hk), 128, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
+    kern<<<dim3(cap_q, a.Hk), kBwdThreads, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
   }
   // dK/dV kernel: resident K / V tiles of 128 rows, Q / dO blocks of 64 tokens.
   if ((rc = make_tmap_2d(&tmQ, q, 2, (uint64_t)a.Hq * HD, a.T, (uint64_t)ldq * 2, 64, 64, true))) return rc;
@@ -591,7 +651,7 @@ int launch_bwd(const void* dO, long long lddo, const void* q, long long ldq, con
       configured = true;
     }
     a.plan = plan_kv;
-    kern<<<dim3(cap_kv, a.Hk), 128, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
+    kern<<<dim3(cap_kv, a.Hk), kBwdThreads, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -33,7 +33,12 @@ class SymmBuffer:
         self.handle = symm_mem.rendezvous(self.local, group)
         self.world = self.handle.world_size
         self.rank = self.handle.rank
-        self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        # buffer_ptrs are the bases of the peers' symmetric blocks; this tensor may sit at an offset
+        off = int(getattr(self.handle, "offset", 0) or 0)
+        self.peer_ptrs: List[int] = [int(p) + off for p in self.handle.buffer_ptrs]
+        if self.peer_ptrs[self.rank] != self.local.data_ptr():
+            raise RuntimeError("symmetric memory: own peer pointer does not match the local tensor "
+                               f"({self.peer_ptrs[self.rank]:#x} vs {self.local.data_ptr():#x})")
         self._c_ptrs = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
         self.local.zero_()
 

@@ -32,6 +32,7 @@ from ..tasks.bi_encoder import BiEncoderTask, global_loss_value
 from .checkpoint import latest_checkpoint, load_checkpoint, load_extra, save_checkpoint
 from .logging import TrainLogger
 from .scheduler import build_scheduler
+from ..utils.tracing import PhaseTimer
 
 
 def to_device(obj, device, non_blocking: bool = True):
@@ -240,6 +241,8 @@ class TrainingEngine:
                 num_workers=num_workers, pin_memory=use_cuda, generator=gen)
         self.micro_step = 0
         self.epoch = 0
+        # per-phase device timing (h2d / forward_backward / optimizer); LSET_B200_PROFILE=1 enables it
+        self.timer = PhaseTimer(enabled=os.environ.get("LSET_B200_PROFILE", "0") == "1")
         self.watchdog = None
         if step_timeout_s and step_timeout_s > 0:
             from .watchdog import StepWatchdog
@@ -302,11 +305,14 @@ class TrainingEngine:
         boundary, the optimizer update. Returns the local loss share as a device tensor."""
         if self.watchdog is not None:
             self.watchdog.beat()
-        batch = to_device(batch, self.device)
+        with self.timer.phase("h2d"):
+            batch = to_device(batch, self.device)
         boundary = (self.micro_step + 1) % self.grad_accum_steps == 0
-        loss = self.forward_backward(batch, boundary)
+        with self.timer.phase("forward_backward"):
+            loss = self.forward_backward(batch, boundary)
         if boundary:
-            self.optimizer_step()
+            with self.timer.phase("optimizer"):
+                self.optimizer_step()
         self.micro_step += 1
         return loss
 
