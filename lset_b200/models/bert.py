@@ -108,6 +108,10 @@ class BertEncoder(nn.Module):
 
     def forward(self, input_ids, attention_mask=None, token_type_ids=None, *, position_ids=None,
                 cu_seqlens=None, max_seqlen=None, **_unused):
+        dev = self.embeddings.word_embeddings.weight.device
+        input_ids, attention_mask, token_type_ids, position_ids, cu_seqlens = (
+            t.to(dev) if torch.is_tensor(t) and t.device != dev else t
+            for t in (input_ids, attention_mask, token_type_ids, position_ids, cu_seqlens))
         ctx = make_stream_ctx(input_ids, attention_mask, position_ids, cu_seqlens, max_seqlen)
         types = token_type_ids.reshape(-1) if token_type_ids is not None else None
         x = self.embeddings(input_ids.reshape(-1), ctx.pos, types)

@@ -100,6 +100,10 @@ class DecoderModel(nn.Module):
     # ------------------------------------------------------------------ API
     def forward(self, input_ids, attention_mask=None, return_lm_logits: bool = False, *,
                 position_ids=None, cu_seqlens=None, max_seqlen=None, **_unused):
+        dev = self.embed_tokens.weight.device
+        input_ids, attention_mask, position_ids, cu_seqlens = (
+            t.to(dev) if torch.is_tensor(t) and t.device != dev else t
+            for t in (input_ids, attention_mask, position_ids, cu_seqlens))
         ctx = make_stream_ctx(input_ids, attention_mask, position_ids, cu_seqlens, max_seqlen)
         hidden = self._run(input_ids.reshape(-1), ctx)
         if ctx.padded_shape is not None:

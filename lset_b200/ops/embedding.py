@@ -61,10 +61,11 @@ def embedding(ids, table, scale: float = 1.0, extra=()):
         for i, t in extra:
             out = out + F.embedding(i, t)
         return out * scale if scale != 1.0 else out
-    flat = [ids.reshape(-1).to(torch.int64).contiguous()]
+    dev = table.device
+    flat = [ids.reshape(-1).to(device=dev, dtype=torch.int64).contiguous()]
     tabs = [table]
     for i, t in extra:
-        flat.append(i.expand_as(ids).reshape(-1).to(torch.int64).contiguous())
+        flat.append(i.expand_as(ids).reshape(-1).to(device=dev, dtype=torch.int64).contiguous())
         tabs.append(t)
     while len(flat) < 3:
         flat.append(None)

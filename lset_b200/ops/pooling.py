@@ -72,7 +72,7 @@ def gather_normalize(hidden, idx, do_norm=True):
     """Rows ``idx`` of ``hidden [T, H]`` (optionally L2-normalised) in one kernel."""
     if _bf16_cuda(hidden) and hidden.shape[-1] % 8 == 0 and hidden.shape[-1] <= 8192:
         h2 = hidden if hidden.stride(1) == 1 else hidden.contiguous()
-        return _GatherL2Norm.apply(h2, idx.to(torch.int64), h2.shape[1], do_norm)
+        return _GatherL2Norm.apply(h2, idx.to(device=h2.device, dtype=torch.int64), h2.shape[1], do_norm)
     out = hidden[idx.long()]
     return normalize(out) if do_norm else out
 
@@ -126,7 +126,7 @@ def segment_mean(hidden, cu_seqlens, weighted=False):
     """Mean (or position-weighted mean) of each packed segment: ``[T, H] -> [M, H]``."""
     if _bf16_cuda(hidden) and hidden.shape[1] % 8 == 0 and hidden.shape[1] <= 8192:
         h2 = hidden if hidden.is_contiguous() else hidden.contiguous()
-        return _SegmentMean.apply(h2, cu_seqlens.to(torch.int32), weighted)
+        return _SegmentMean.apply(h2, cu_seqlens.to(device=h2.device, dtype=torch.int32), weighted)
     return segment_mean_ref(hidden, cu_seqlens, weighted)
 
 

@@ -270,9 +270,10 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------ one micro-step
     def forward_backward(self, batch: dict, is_boundary: bool = True):
-        """Forward + backward of one micro-batch already on the device. Returns the detached local
+        """Forward + backward of one micro-batch (moved to the device if it is not there). Returns the detached local
         loss share (sum over ranks = global loss)."""
         ga = self.grad_accum_steps
+        batch = to_device(batch, self.device)  # no-op for tensors that are already there
         self.store.set_requires_gradient_sync(is_boundary)
         q, d, n = batch["query"], batch["doc"], batch.get("neg")
         labels = batch.get("labels") if self.use_label_matrix else None
