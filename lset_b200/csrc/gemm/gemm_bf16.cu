@@ -40,8 +40,19 @@ struct GemmArgs {
   int accumulate;             // fp32 output only: C += result (red.global.add)
   int splits;                 // >= 1, split of the K range
   int kb_per_split;
+  int raster_m_fast;          // tile order: consecutive tiles walk M first (B tile shared in L2)
+  // contrastive-loss epilogues (EPI_LSE / EPI_PGRAD): scores s = acc * scale
+  float scale;                // 1 / temperature
+  const float* lse;           // [M] natural-log LSE (EPI_PGRAD input)
+  float* part;                // [tiles_n, M, 2] running (max, sum) in log2 domain (EPI_LSE output)
+  float* pos;                 // [M] score of the target column (EPI_LSE output)
+  const float* coef;          // device scalar multiplied into the probabilities' gradient
+  long long target_offset;    // target column of row r is r + target_offset
   int* status;
 };
+
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_PGRAD = 2 };
+constexpr float kLog2e = 1.4426950408889634f;
 
 template <int BN>
 struct Cfg {
@@ -68,7 +79,7 @@ __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, 
                : "memory");
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT>
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      GemmArgs g) {
@@ -121,8 +132,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int split = tile / (tiles_m * tiles_n);
         const int mn = tile - split * (tiles_m * tiles_n);
-        const int m0 = (mn / tiles_n) * BM;
-        const int n0 = (mn % tiles_n) * BN;
+        const int m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
+        const int n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -215,8 +226,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
       const int split = tile / (tiles_m * tiles_n);
       const int mn = tile - split * (tiles_m * tiles_n);
-      const int m0 = (mn / tiles_n) * BM;
-      const int n0 = (mn % tiles_n) * BN;
+      const int m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
+      const int n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aphase)) {
@@ -226,6 +237,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const bool add_bias = (g.bias != nullptr) && (split == 0);
+      [[maybe_unused]] float m_run = -INFINITY, l_run = 0.f, pos_val = 0.f;
+      [[maybe_unused]] bool pos_here = false;
+      [[maybe_unused]] const long long target = row + g.target_offset;
+      [[maybe_unused]] const float s2 = g.scale * kLog2e;
+      [[maybe_unused]] float lse2 = 0.f, cf = 0.f;
+      if constexpr (EPI == EPI_PGRAD) {
+        lse2 = (row < g.M) ? g.lse[row] * kLog2e : 0.f;
+        cf = g.coef != nullptr ? g.coef[0] : 1.f;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -236,32 +256,67 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (add_bias) {
+          if constexpr (EPI == EPI_LSE) {
+            float cm = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
-          }
-          OutT* dst = Cout + static_cast<long long>(row) * g.ldc + col0;
-          if constexpr (sizeof(OutT) == 2) {
+            for (int j = 0; j < 32; ++j) {
+              const bool in = col0 + j < g.N;
+              if (in && col0 + j == target) {
+                pos_val = v[j] * g.scale;
+                pos_here = true;
+              }
+              v[j] = in ? v[j] * s2 : -INFINITY;
+              cm = fmaxf(cm, v[j]);
+            }
+            const float m_new = fmaxf(m_run, cm);
+            float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (col0 + 8 * j < g.N)
-                store8_bf16(reinterpret_cast<__nv_bfloat16*>(dst) + 8 * j, v + 8 * j);
+            for (int j = 0; j < 32; ++j) sum += exp2f(v[j] - m_new);
+            l_run = l_run * exp2f(m_run - m_new) + sum;
+            m_run = m_new;
           } else {
-            float* fd = reinterpret_cast<float*>(dst);
-            if (g.accumulate) {
+            if constexpr (EPI == EPI_PGRAD) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col0 + 4 * j < g.N)
-                  red_add4(fd + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              for (int j = 0; j < 32; ++j) {
+                const float p = exp2f(v[j] * s2 - lse2);
+                v[j] = (p - ((col0 + j == target) ? 1.f : 0.f)) * cf;
+              }
+            }
+            if (add_bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
+            }
+            OutT* dst = Cout + static_cast<long long>(row) * g.ldc + col0;
+            if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col0 + 8 * j < g.N)
+                  store8_bf16(reinterpret_cast<__nv_bfloat16*>(dst) + 8 * j, v + 8 * j);
             } else {
+              float* fd = reinterpret_cast<float*>(dst);
+              if (g.accumulate) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col0 + 4 * j < g.N)
-                  *reinterpret_cast<float4*>(fd + 4 * j) =
-                      make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                for (int j = 0; j < 8; ++j)
+                  if (col0 + 4 * j < g.N)
+                    red_add4(fd + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (col0 + 4 * j < g.N)
+                    *reinterpret_cast<float4*>(fd + 4 * j) =
+                        make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
             }
           }
+        }
+      }
+      if constexpr (EPI == EPI_LSE) {
+        if (row < g.M) {
+          float* pp = g.part + (static_cast<long long>(n0 / BN) * g.M + row) * 2;
+          pp[0] = m_run;
+          pp[1] = l_run;
+          if (pos_here) g.pos[row] = pos_val;
         }
       }
       tc_fence_before();
@@ -286,11 +341,11 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT>
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
            cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
@@ -362,7 +417,8 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, bn, true);
   if (rc) return rc;
 
-  GemmArgs g;
+  GemmArgs g{};
+  g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
   g.M = M;
   g.N = N;
   g.K = K;
@@ -385,4 +441,136 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if (a_mn && b_mn) return LB_DISPATCH(1, 1);
   return LB_DISPATCH(1, 0);
 #undef LB_DISPATCH
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Contrastive loss on the GEMM: scores s = (Q · Kᵀ) / temperature never leave tensor memory.
+//   forward   every 128 x BN tile folds its scores into a per-row running (max, sum) pair and picks
+//             out the target column; a small kernel merges the pairs into the row LSE and the loss.
+//   backward  the same product is recomputed and the epilogue writes W = (softmax − onehot) · coef
+//             in bf16; dQ = W · K and dK = Wᵀ · Q are two more calls of the plain GEMM above.
+// Replaces the reference's Triton / CUDA fused loss kernels for the diagonal-target case
+// (lset/kernels/loss.py:186-289,402-495; lset/kernels/experimental/csrc/loss_sm100.cu:340-643)
+// without an int8 label matrix.
+// ------------------------------------------------------------------------------------------------
+namespace lb {
+namespace {
+
+// lse[r] = ln(sum_j exp(s_rj)); loss_sum += sum_r (lse[r] − pos[r]) (one atomicAdd per block).
+__global__ void __launch_bounds__(256)
+    lse_merge_kernel(const float* __restrict__ part, int tiles_n, int M, const float* __restrict__ pos,
+                     float* __restrict__ lse, float* __restrict__ loss_sum) {
+  __shared__ float sred[8];
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  float contrib = 0.f;
+  if (r < M) {
+    float m = -INFINITY, l = 0.f;
+    for (int t = 0; t < tiles_n; ++t) {
+      const float mt = part[(1LL * t * M + r) * 2], lt = part[(1LL * t * M + r) * 2 + 1];
+      const float mn = fmaxf(m, mt);
+      if (mn > -INFINITY) l = l * exp2f(m - mn) + lt * exp2f(mt - mn);
+      m = mn;
+    }
+    const float v = (m + log2f(l)) * 0.6931471805599453f;
+    lse[r] = v;
+    contrib = v - pos[r];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
+  if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = contrib;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < 8; ++i) s += sred[i];
+    atomicAdd(loss_sum, s);
+  }
+}
+
+int loss_tile_bn(int M, int N) {
+  (void)M;
+  return N > 128 ? 256 : 128;
+}
+
+int prep_loss(const void* Q, const void* Kd, int M, int N, int D, long long ldq, long long ldk,
+              int bn, CUtensorMap* tmA, CUtensorMap* tmB, GemmArgs* g, int* grid) {
+  if (M <= 0 || N <= 0 || D <= 0) return -4;
+  if ((ldq & 7) || (ldk & 7)) return -3;
+  int rc = make_tmap_2d(tmA, Q, 2, (uint64_t)D, (uint64_t)M, (uint64_t)ldq * 2, BK, BM, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(tmB, Kd, 2, (uint64_t)D, (uint64_t)N, (uint64_t)ldk * 2, BK, bn, true);
+  if (rc) return rc;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
+  *g = GemmArgs{};
+  g->M = M;
+  g->N = N;
+  g->K = D;
+  g->splits = 1;
+  g->kb_per_split = (D + BK - 1) / BK;
+  g->raster_m_fast = tiles_n > tiles_m ? 1 : 0;
+  const long long total = 1LL * tiles_m * tiles_n;
+  const int sms = num_sms();
+  *grid = (int)(total < sms ? total : sms);
+  return 0;
+}
+
+}  // namespace
+}  // namespace lb
+
+// Number of floats of scratch that lb_infonce_fwd needs for M queries against N passages.
+extern "C" long long lb_infonce_scratch_floats(int M, int N) {
+  const int bn = lb::loss_tile_bn(M, N);
+  return 2LL * ((N + bn - 1) / bn) * M + M;
+}
+
+// q: [M, D] bf16 (row stride ldq), k: [N, D] bf16 (row stride ldk). The positive of query r is
+// passage r + target_offset. Outputs: lse [M] fp32, loss_sum (device scalar, += sum_r (lse − pos)).
+// scratch: lb_infonce_scratch_floats(M, N) floats.
+extern "C" int lb_infonce_fwd(const void* q, long long ldq, const void* k, long long ldk, int M,
+                              int N, int D, float inv_temperature, long long target_offset,
+                              float* scratch, float* lse, float* loss_sum, int* status,
+                              void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int bn = loss_tile_bn(M, N);
+  CUtensorMap tmA, tmB;
+  GemmArgs g;
+  int grid;
+  if (int rc = prep_loss(q, k, M, N, D, ldq, ldk, bn, &tmA, &tmB, &g, &grid)) return rc;
+  const int tiles_n = (N + bn - 1) / bn;
+  g.scale = inv_temperature;
+  g.part = scratch;
+  g.pos = scratch + 2LL * tiles_n * M;
+  g.target_offset = target_offset;
+  g.status = status;
+  int rc = bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_LSE>(tmA, tmB, g, grid, stream)
+                     : launch<0, 0, 128, __nv_bfloat16, EPI_LSE>(tmA, tmB, g, grid, stream);
+  if (rc) return rc;
+  lse_merge_kernel<<<(M + 255) / 256, 256, 0, stream>>>(g.part, tiles_n, M, g.pos, lse, loss_sum);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// W[r, c] = (exp(s_rc − lse[r]) − [c == r + target_offset]) * coef[0], bf16, row stride ldw
+// (multiple of 8, >= N). coef: device scalar (upstream gradient / (temperature * denominator)).
+extern "C" int lb_infonce_pgrad(const void* q, long long ldq, const void* k, long long ldk, int M,
+                                int N, int D, float inv_temperature, long long target_offset,
+                                const float* lse, const float* coef, void* W, long long ldw,
+                                int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if ((N & 7) || (ldw & 7)) return -3;
+  const int bn = loss_tile_bn(M, N);
+  CUtensorMap tmA, tmB;
+  GemmArgs g;
+  int grid;
+  if (int rc = prep_loss(q, k, M, N, D, ldq, ldk, bn, &tmA, &tmB, &g, &grid)) return rc;
+  g.scale = inv_temperature;
+  g.lse = lse;
+  g.coef = coef;
+  g.C = W;
+  g.ldc = ldw;
+  g.target_offset = target_offset;
+  g.status = status;
+  return bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream)
+                   : launch<0, 0, 128, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream);
 }

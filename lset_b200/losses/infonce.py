@@ -7,10 +7,14 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from ..ops.loss import similarity
+from ..ops.loss import fused_infonce, fused_infonce_supported, similarity
 
 
 def infonce_loss(query_embeds, doc_embeds, temperature=0.02, top_k=None, target_offset: int = 0):
+    if (top_k is None and isinstance(temperature, (int, float))
+            and fused_infonce_supported(query_embeds, doc_embeds)):
+        # streaming kernel: the score matrix is never written to memory in fp32
+        return fused_infonce(query_embeds, doc_embeds, float(temperature), target_offset)
     scale = 1.0 / temperature
     sim = similarity(query_embeds, doc_embeds) * scale
     B = query_embeds.shape[0]
