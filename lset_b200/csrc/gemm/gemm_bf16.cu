@@ -31,6 +31,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kGemmThreads = 192;
+constexpr int kGatherThreads = 256;  // + 2 pull warps
 
 struct GemmArgs {
   int M, N, K;
@@ -48,6 +49,20 @@ struct GemmArgs {
   float* pos;                 // [M] score of the target column (EPI_LSE output)
   const float* coef;          // device scalar multiplied into the probabilities' gradient
   long long target_offset;    // target column of row r is r + target_offset
+  // ---- peer gather of B (GATHER): rows of B live in `world` ranks' buffers, n_local rows each;
+  // two extra warps pull them into b_local ([world * n_local, K], the tensor map's base) and
+  // publish one flag per (rank, BN-row tile); tiles are visited in pull order, own rank first.
+  const void* b_peers[8];
+  void* b_local;
+  long long ldb_peer;         // row stride (elements) of every rank's buffer and of b_local
+  int n_local, world, rank;
+  unsigned* flags;            // [world * tiles_per_peer], value == epoch when the tile is local
+  unsigned* chunk_counter;    // work-stealing counter of the pull warps (reset by the host)
+  unsigned epoch;
+  // ---- peer scatter of C (fp32 accumulate only): row r belongs to rank r / c_rows_per_peer and
+  // is reduced into that rank's buffer with red.global.add over NVLink.
+  void* c_peers[8];
+  int c_rows_per_peer;        // 0 = C is a single local matrix
   int* status;
 };
 
@@ -79,8 +94,8 @@ __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, 
                : "memory");
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT, int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI, int GATHER = 0>
+__global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      GemmArgs g) {
   using C = Cfg<BN>;
@@ -118,10 +133,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + BN - 1) / BN : 0;
   const int tiles_m = (g.M + BM - 1) / BM;
-  const int tiles_n = (g.N + BN - 1) / BN;
+  const int tiles_n = GATHER ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
   const int kb_total = (g.K + BK - 1) / BK;
   const int total = tiles_m * tiles_n * g.splits;
+  // (m0, n0, flag index) of the `mn`-th output tile
+  auto decode = [&](int mn, int& m0, int& n0, int& chunk) {
+    if constexpr (GATHER) {
+      m0 = (mn % tiles_m) * BM;
+      const int ni = mn / tiles_m;
+      const int peer = (g.rank + ni / tiles_per_peer) % g.world;
+      chunk = peer * tiles_per_peer + ni % tiles_per_peer;
+      n0 = peer * g.n_local + (ni % tiles_per_peer) * BN;
+    } else {
+      m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
+      n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
+      chunk = 0;
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -132,8 +162,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int split = tile / (tiles_m * tiles_n);
         const int mn = tile - split * (tiles_m * tiles_n);
-        const int m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
-        const int n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
+        int m0, n0, chunk;
+        decode(mn, m0, n0, chunk);
+        if constexpr (GATHER) {
+          // the rows of this tile must have been pulled into local memory
+          bool landed = false;
+          const unsigned long long t0 = globaltimer_ns();
+          for (unsigned it2 = 0;; ++it2) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(g.flags + chunk) : "memory");
+            if (v == g.epoch) {
+              landed = true;
+              break;
+            }
+            if ((it2 & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+          }
+          if (!landed) {
+            report_status(g.status, kStatusTimeoutPeer);
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -218,6 +268,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
     __syncwarp();
+  } else if (GATHER && warp >= 6) {
+    // ------------------------------------------------------------------ pull warps (6, 7)
+    if constexpr (GATHER) {
+      const int chunks = g.world * tiles_per_peer;
+      const long long row_bytes = 2LL * g.K;
+      for (;;) {
+        unsigned c = 0;
+        if (lane == 0) c = atomicAdd(g.chunk_counter, 1u);
+        c = __shfl_sync(0xffffffffu, c, 0);
+        if (c >= unsigned(chunks)) break;
+        const int peer = (g.rank + int(c) / tiles_per_peer) % g.world;
+        const int t = int(c) % tiles_per_peer;
+        const int r0 = t * BN, r1 = min(r0 + BN, g.n_local);
+        const char* src = static_cast<const char*>(g.b_peers[peer]);
+        char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
+        const long long vec_per_row = row_bytes / 16;
+        const long long total_vec = vec_per_row * (r1 - r0);
+        for (long long i0 = 0; i0 < total_vec; i0 += 32 * 8) {
+          uint4 buf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const long long i = i0 + u * 32 + lane;
+            if (i < total_vec) {
+              const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+              buf[u] = *reinterpret_cast<const uint4*>(src + 2LL * rr * g.ldb_peer + cc * 16);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const long long i = i0 + u * 32 + lane;
+            if (i < total_vec) {
+              const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+              *reinterpret_cast<uint4*>(dst + 2LL * rr * g.ldb_peer + cc * 16) = buf[u];
+            }
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          const unsigned* fp = g.flags + (peer * tiles_per_peer + t);
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(fp), "r"(g.epoch) : "memory");
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -226,8 +320,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
       const int split = tile / (tiles_m * tiles_n);
       const int mn = tile - split * (tiles_m * tiles_n);
-      const int m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
-      const int n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
+      int m0, n0, chunk;
+      decode(mn, m0, n0, chunk);
+      const int n_limit = GATHER ? min(g.N, (n0 / g.n_local + 1) * g.n_local) : g.N;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aphase)) {
@@ -260,7 +355,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             float cm = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const bool in = col0 + j < g.N;
+              const bool in = col0 + j < n_limit;
               if (in && col0 + j == target) {
                 pos_val = v[j] * g.scale;
                 pos_here = true;
@@ -288,6 +383,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
             }
             OutT* dst = Cout + static_cast<long long>(row) * g.ldc + col0;
+            if constexpr (sizeof(OutT) == 4) {
+              if (g.c_rows_per_peer > 0)
+                dst = reinterpret_cast<OutT*>(g.c_peers[row / g.c_rows_per_peer]) +
+                      static_cast<long long>(row % g.c_rows_per_peer) * g.ldc + col0;
+            }
             if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
@@ -313,7 +413,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if constexpr (EPI == EPI_LSE) {
         if (row < g.M) {
-          float* pp = g.part + (static_cast<long long>(n0 / BN) * g.M + row) * 2;
+          const int part_idx = GATHER ? chunk : n0 / BN;
+          float* pp = g.part + (static_cast<long long>(part_idx) * g.M + row) * 2;
           pp[0] = m_run;
           pp[1] = l_run;
           if (pos_here) g.pos[row] = pos_val;
@@ -341,11 +442,11 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE>
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE, int GATHER = 0>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
            cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI, GATHER>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
@@ -353,7 +454,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, in
       return -10;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, g);
+  kern<<<grid, GATHER ? kGatherThreads : kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -374,10 +475,11 @@ int launch_out(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g
 //   splits: split of K (fp32 accumulate only; >1 forces accumulate). bn: 0 = auto, 128 or 256.
 // All leading dimensions and N must be multiples of 8 elements; base pointers 16-byte aligned.
 // Returns 0 or a negative code; device-side timeouts are reported through *status (device int).
-extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
-                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
-                            int out_fp32, int accumulate, const void* bias, int splits, int bn,
-                            int* status, void* stream_) {
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K,
+                          long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                          int out_fp32, int accumulate, const void* bias, int splits, int bn,
+                          int* status, void* stream_, const void* const* c_peers, int c_world,
+                          int c_rows_per_peer) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -429,6 +531,12 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   g.splits = splits;
   g.kb_per_split = kb_per;
   g.status = status;
+  if (c_peers != nullptr && c_rows_per_peer > 0) {
+    if (!out_fp32 || c_world > 8) return -3;
+    for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);
+    g.c_rows_per_peer = c_rows_per_peer;
+    g.accumulate = 1;
+  }
   const long long total = 1LL * tiles_m * tiles_n * splits;
   const int grid = (int)(total < sms ? total : sms);
   const bool f32 = out_fp32 != 0;
@@ -441,6 +549,26 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if (a_mn && b_mn) return LB_DISPATCH(1, 1);
   return LB_DISPATCH(1, 0);
 #undef LB_DISPATCH
+}
+
+extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                            int out_fp32, int accumulate, const void* bias, int splits, int bn,
+                            int* status, void* stream_) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bias,
+                        splits, bn, status, stream_, nullptr, 0, 0);
+}
+
+// GEMM fused with a reduce-scatter: C has M = world * rows_per_peer rows; row r is added (fp32
+// red.global.add over NVLink) into rank r / rows_per_peer's buffer c_peers[...] at local row
+// r % rows_per_peer. The buffers must be zeroed (or hold the value to accumulate onto) beforehand.
+extern "C" int lb_gemm_bf16_scatter(const void* A, const void* B, const void* const* c_peers,
+                                    int world, int rows_per_peer, int M, int N, int K,
+                                    long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                    int splits, int bn, int* status, void* stream_) {
+  if (M != world * rows_per_peer) return -3;
+  return gemm_bf16_impl(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 1, 1, nullptr, splits, bn,
+                        status, stream_, c_peers, world, rows_per_peer);
 }
 
 
@@ -573,4 +701,55 @@ extern "C" int lb_infonce_pgrad(const void* q, long long ldq, const void* k, lon
   g.status = status;
   return bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream)
                    : launch<0, 0, 128, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream);
+}
+
+
+// Cross-rank InfoNCE forward: the passages of all `world` ranks (n_local rows each, in symmetric
+// buffers k_peers[r]) are pulled into k_all ([world * n_local, D], local) by two extra warps per
+// CTA while the tensor-core tiles consume them in pull order, own rank first. The caller orders
+// the launch after every rank has written its passages and keeps k_all for the backward.
+// flags: [world * ceil(n_local / 256)] zero-initialised once; counter: one u32; epoch: a value
+// that differs from every earlier call on these flags. part/lse layout as in lb_infonce_fwd with
+// tiles = world * ceil(n_local / 256).
+extern "C" long long lb_infonce_xrank_scratch_floats(int M, int n_local, int world) {
+  return 2LL * world * ((n_local + 255) / 256) * M + M;
+}
+
+extern "C" int lb_infonce_fwd_xrank(const void* q, long long ldq, const void* const* k_peers,
+                                    void* k_all, long long ldk, int M, int n_local, int world,
+                                    int rank, int D, float inv_temperature, long long target_offset,
+                                    float* scratch, float* lse, float* loss_sum, unsigned* flags,
+                                    unsigned* counter, unsigned epoch, int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > 8 || (n_local & 7) || (D & 7)) return -3;
+  const int N = world * n_local;
+  CUtensorMap tmA, tmB;
+  GemmArgs g;
+  int grid;
+  if (int rc = prep_loss(q, k_all, M, N, D, ldq, ldk, 256, &tmA, &tmB, &g, &grid)) return rc;
+  const int tiles_per_peer = (n_local + 255) / 256;
+  const int chunks = world * tiles_per_peer;
+  const long long total = 1LL * ((M + BM - 1) / BM) * chunks;
+  const int sms = num_sms();
+  grid = (int)(total < sms ? total : sms);
+  g.scale = inv_temperature;
+  g.part = scratch;
+  g.pos = scratch + 2LL * chunks * M;
+  g.target_offset = target_offset;
+  for (int i = 0; i < world; ++i) g.b_peers[i] = k_peers[i];
+  g.b_local = k_all;
+  g.ldb_peer = ldk;
+  g.n_local = n_local;
+  g.world = world;
+  g.rank = rank;
+  g.flags = flags;
+  g.chunk_counter = counter;
+  g.epoch = epoch;
+  g.status = status;
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), stream) != cudaSuccess) return -12;
+  int rc = launch<0, 0, 256, __nv_bfloat16, EPI_LSE, 1>(tmA, tmB, g, grid, stream);
+  if (rc) return rc;
+  lse_merge_kernel<<<(M + 255) / 256, 256, 0, stream>>>(g.part, chunks, M, g.pos, lse, loss_sum);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

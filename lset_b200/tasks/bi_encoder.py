@@ -101,6 +101,13 @@ class BiEncoderTask(nn.Module):
         Returns the rank's share of the global mean (the shares sum to the global loss)."""
         W, rank = self._dp()
         Bq, Bd = q_emb.shape[0], d_emb.shape[0]
+        if (W > 1 and n_emb is None and labels is None and self.matryoshka_dims is None
+                and self.top_k is None and self.logit_scale is None and Bq == Bd):
+            from ..dist import xrank_loss
+
+            if xrank_loss.supported(q_emb, d_emb, self.dp_group):
+                # gather, similarity GEMM, logsumexp and the dK reduce-scatter fused over NVLink
+                return xrank_loss.cross_rank_infonce(q_emb, d_emb, self.temperature, self.dp_group)
         docs = gather_for_local_rows(d_emb, self.dp_group)
         if n_emb is not None:
             docs = torch.cat([docs, gather_for_local_rows(n_emb, self.dp_group)], dim=0)

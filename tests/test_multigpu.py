@@ -36,3 +36,22 @@ def test_symm_path_matches_nccl_path(tmp_path):
         assert abs(x - y) < 2e-2 * max(1.0, abs(x)), (a["norms"], b["norms"])
     for x, y in zip(a["sumsq"], b["sumsq"]):
         assert abs(x - y) < 1e-3 * max(1.0, abs(x)), (a["sumsq"], b["sumsq"])
+
+
+def _run_loss(world, tmp_path, port):
+    out = tmp_path / "loss.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(HERE, "mgpu_loss_worker.py"), str(out)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    return json.loads(out.read_text())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_cross_rank_infonce_matches_gather_path(tmp_path):
+    r = _run_loss(2, tmp_path, 29641)
+    for case in r["cases"]:
+        assert case["loss_err"] < 2e-2, case
+        assert case["dq_err"] < 3e-2 and case["dk_err"] < 3e-2, case
