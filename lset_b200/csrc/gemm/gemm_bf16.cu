@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         if (c >= unsigned(chunks)) break;
         const int peer = (g.rank + int(c) / tiles_per_peer) % g.world;
         const int t = int(c) % tiles_per_peer;
-        const int r0 = t * BN, r1 = min(r0 + BN, g.n_local);
+        const int r0 = t * BN, r1 = peer == g.rank ? t * BN : min(r0 + BN, g.n_local);  // own rows are in place
         const char* src = static_cast<const char*>(g.b_peers[peer]);
         char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
         const long long vec_per_row = row_bytes / 16;

@@ -8,8 +8,9 @@ recomputed as a bf16 ``W``, ``dQ = W · K`` stays local, and ``dK = Wᵀ · Q`` 
 whose epilogue adds every row straight into its *owner's* fp32 buffer with ``red.global.add`` over
 NVLink — the reduce-scatter is fused into the GEMM.
 
-Ranks are ordered on the host side: a one-element all-reduce before data is read or overwritten
-(stream-ordered, so no kernel ever spins on another GPU). Same value and gradients as
+Ranks are ordered on the host side with two one-element all-reduces per step (passages published
+and accumulators cleared; all dK contributions landed); they are stream-ordered, so no kernel ever
+spins on another GPU. Same value and gradients as
 ``gather_for_local_rows`` + ``infonce_loss``; replaces the reference's ``all_gather`` + loss kernel
 (lset/distributed/gather.py:7-35, lset/kernels/loss.py).
 """
@@ -34,7 +35,9 @@ class _Buffers:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.k_sym = symm.SymmBuffer(n_local * D, torch.bfloat16, device, group)
+        # two passage buffers used alternately: a rank may publish step t+1 while a slow peer is
+        # still pulling step t, so no "done reading" barrier is needed
+        self.k_sym = [symm.SymmBuffer(n_local * D, torch.bfloat16, device, group) for _ in range(2)]
         self.dk_sym = symm.SymmBuffer(n_local * D, torch.float32, device, group)
         self.k_all = torch.empty(self.world * n_local, D, dtype=torch.bfloat16, device=device)
         tiles = self.world * ((n_local + 255) // 256)
@@ -74,16 +77,18 @@ class _CrossRankInfoNCE(torch.autograd.Function):
         W, rank = buf.world, buf.rank
         lib = nv.load()
         lib.lb_infonce_xrank_scratch_floats.restype = nv.c_ll
-        buf.order_ranks()                      # peers are done reading last step's passages
-        buf.k_sym.local.view(n_local, D).copy_(d)
-        buf.order_ranks()                      # every rank's passages are published
         buf.epoch += 1
+        ksym = buf.k_sym[buf.epoch & 1]
+        ksym.local.view(n_local, D).copy_(d)
+        buf.k_all[rank * n_local:(rank + 1) * n_local].copy_(d)   # own rows need no pull
+        buf.dk_sym.local.zero_()               # owners' dK accumulators start at zero
+        buf.order_ranks()                      # passages published and accumulators cleared everywhere
         scr = torch.empty(int(lib.lb_infonce_xrank_scratch_floats(
             nv.c_int(B), nv.c_int(n_local), nv.c_int(W))), dtype=torch.float32, device=q.device)
         lse = torch.empty(B, dtype=torch.float32, device=q.device)
         loss_sum = torch.zeros(1, dtype=torch.float32, device=q.device)
         rc = lib.lb_infonce_fwd_xrank(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), buf.k_sym.c_ptr_array(),
+            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), ksym.c_ptr_array(),
             nv.c_void_p(buf.k_all.data_ptr()), nv.c_ll(D), nv.c_int(B), nv.c_int(n_local),
             nv.c_int(W), nv.c_int(rank), nv.c_int(D), nv.c_float(inv_t), nv.c_ll(rank * n_local),
             nv.c_void_p(scr.data_ptr()), nv.c_void_p(lse.data_ptr()),
@@ -118,9 +123,7 @@ class _CrossRankInfoNCE(torch.autograd.Function):
             nv.c_void_p(nv.stream_ptr()))
         nv.check_rc(rc, "lb_infonce_pgrad")
         dq = matmul_abt(Wm[:B], buf.k_all, b_mn=True)
-        # dK: every rank adds its contribution into the owners' buffers
-        buf.dk_sym.local.zero_()
-        buf.order_ranks()                      # all owners' buffers are zero
+        # dK: every rank adds its contribution into the owners' buffers (cleared in forward)
         qp = q if Bp == B else torch.cat([q, q.new_zeros(Bp - B, D)])
         rc = lib.lb_gemm_bf16_scatter(
             nv.c_void_p(Wm.data_ptr()), nv.c_void_p(qp.data_ptr()), buf.dk_sym.c_ptr_array(),
