@@ -248,6 +248,17 @@ class TrainingEngine:
             from .watchdog import StepWatchdog
 
             self.watchdog = StepWatchdog(step_timeout_s)
+        self.heartbeat = None
+        if step_timeout_s and step_timeout_s > 0 and world > 1 and dist.is_initialized():
+            from ..dist.health import RankHeartbeat
+
+            try:
+                store = dist.distributed_c10d._get_default_store()
+                self.heartbeat = RankHeartbeat(store, dist.get_rank(), dist.get_world_size(),
+                                               stale_s=max(2.0, step_timeout_s / 2))
+                self.heartbeat.start()
+            except Exception as exc:  # pragma: no cover - store not reachable
+                print(f"[lset_b200] heartbeat disabled: {exc}")
 
     # ------------------------------------------------------------------ helpers
     def _pick_collator(self, dataset, tokenizer, max_seq_length, length_sorted):
@@ -306,6 +317,8 @@ class TrainingEngine:
         boundary, the optimizer update. Returns the local loss share as a device tensor."""
         if self.watchdog is not None:
             self.watchdog.beat()
+        if self.heartbeat is not None:
+            self.heartbeat.check_peers()  # a dead peer is noticed before the next collective
         with self.timer.phase("h2d"):
             batch = to_device(batch, self.device)
         boundary = (self.micro_step + 1) % self.grad_accum_steps == 0
@@ -370,6 +383,8 @@ class TrainingEngine:
         finally:
             if self.watchdog is not None:
                 self.watchdog.stop()
+            if self.heartbeat is not None:
+                self.heartbeat.stop()
             self.logger.finish()
             if self.needs_dist_cleanup and dist.is_initialized():
                 dist.destroy_process_group()

@@ -164,3 +164,28 @@ def test_embedding():
     out3 = E.embedding(ids, tab.detach(), extra=((pos, pos_tab), (typ, typ_tab)))
     ref3 = tab.detach()[ids].float() + pos_tab[pos].float() + typ_tab[typ].float()
     _close(out3, ref3)
+
+
+def test_bounded_wait_times_out_with_status_and_context_survives():
+    import ctypes
+
+    lib = nv.load()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")      # nothing ever sets it
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    rc = lib.lb_bounded_wait_probe(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(1),
+                                   ctypes.c_ulonglong(200_000_000), ctypes.c_void_p(status.data_ptr()),
+                                   ctypes.c_void_p(waited.data_ptr()),
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 4 and 0.15e9 < waited.item() < 2e9
+    flag.fill_(1)                                                 # a set flag returns at once
+    status.zero_()
+    lib.lb_bounded_wait_probe(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(1),
+                              ctypes.c_ulonglong(200_000_000), ctypes.c_void_p(status.data_ptr()),
+                              ctypes.c_void_p(waited.data_ptr()),
+                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert status.item() == 0 and waited.item() < 50_000_000
+    assert torch.ones(4, device="cuda").sum().item() == 4.0       # the context is still usable
