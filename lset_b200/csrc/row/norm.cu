@@ -23,19 +23,12 @@ __global__ void __launch_bounds__(kRowThreads)
                    const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ res_out,
                    float* __restrict__ rstd_out, int N, int H, float eps, float w_off) {
   __shared__ float sred[8];
+  extern __shared__ float sw[];  // weights (+ offset) as fp32, shared by all rows of the CTA
   constexpr int ROWS = kRowThreads / TPR;
   const int t = threadIdx.x % TPR;
   const int r = threadIdx.x / TPR;
-  float wv[NV][8];
-#pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    const int idx = (v * TPR + t) * 8;
-    if (idx < H) {
-      unpack8(ld16(w + idx), wv[v]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) wv[v][i] += w_off;
-    }
-  }
+  for (int i = threadIdx.x; i < H; i += kRowThreads) sw[i] = __bfloat162float(w[i]) + w_off;
+  __syncthreads();
   for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
     const long long row = row0 + r;
     const bool valid = row < N;
@@ -65,58 +58,71 @@ __global__ void __launch_bounds__(kRowThreads)
       const int idx = (v * TPR + t) * 8;
       if (valid && idx < H) {
         float o[8];
+        const float4 w0 = *reinterpret_cast<const float4*>(sw + idx);
+        const float4 w1 = *reinterpret_cast<const float4*>(sw + idx + 4);
+        const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = bf16_round(xv[v][i] * rstd) * wv[v][i];
+        for (int i = 0; i < 8; ++i) o[i] = bf16_round(xv[v][i] * rstd) * wl[i];
         st16(y + row * H + idx, pack8(o));
       }
     }
   }
 }
 
+// Backward keeps x and dy as packed bf16 in registers (unpacked twice) and the weights in shared
+// memory, so that only the fp32 dW accumulators are long-lived: two CTAs fit per SM.
 template <int TPR, int NV>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 2)
     rms_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dres,
                    const bf16* __restrict__ xin, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, bf16* __restrict__ dx,
                    float* __restrict__ dw_partial, int N, int H, float w_off) {
   __shared__ float sred[8];
-  extern __shared__ float sdw[];
+  extern __shared__ float sdw[];  // [H] dW accumulator of the CTA, then [H] weights
+  float* sw = sdw + H;
   constexpr int ROWS = kRowThreads / TPR;
   const int t = threadIdx.x % TPR;
   const int r = threadIdx.x / TPR;
-  float wv[NV][8], dwacc[NV][8];
+  float dwacc[NV][8];
 #pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    const int idx = (v * TPR + t) * 8;
+  for (int v = 0; v < NV; ++v)
 #pragma unroll
     for (int i = 0; i < 8; ++i) dwacc[v][i] = 0.f;
-    if (idx < H) {
-      unpack8(ld16(w + idx), wv[v]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) wv[v][i] += w_off;
-    }
+  for (int i = threadIdx.x; i < H; i += kRowThreads) {
+    sdw[i] = 0.f;
+    sw[i] = __bfloat162float(w[i]) + w_off;
   }
-  for (int i = threadIdx.x; i < H; i += kRowThreads) sdw[i] = 0.f;
+  __syncthreads();
 
   for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
     const long long row = row0 + r;
     const bool valid = row < N;
     const float rstd = valid ? rstd_in[row] : 0.f;
-    float xh[NV][8], m[NV][8];
+    uint4 xq[NV], gq[NV];
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int idx = (v * TPR + t) * 8;
       if (valid && idx < H) {
-        float g[8];
-        unpack8(ld16(xin + row * H + idx), xh[v]);
-        unpack8(ld16(dy + row * H + idx), g);
+        xq[v] = ld16(xin + row * H + idx);
+        gq[v] = ld16(dy + row * H + idx);
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float xh[8], g[8];
+        unpack8(xq[v], xh);
+        unpack8(gq[v], g);
+        const float4 w0 = *reinterpret_cast<const float4*>(sw + idx);
+        const float4 w1 = *reinterpret_cast<const float4*>(sw + idx + 4);
+        const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          xh[v][i] *= rstd;
-          m[v][i] = g[i] * wv[v][i];
-          dot += m[v][i] * xh[v][i];
-          dwacc[v][i] += g[i] * bf16_round(xh[v][i]);
+          xh[i] *= rstd;
+          dot += g[i] * wl[i] * xh[i];
+          dwacc[v][i] += g[i] * bf16_round(xh[i]);
         }
       }
     }
@@ -125,9 +131,14 @@ __global__ void __launch_bounds__(kRowThreads)
     for (int v = 0; v < NV; ++v) {
       const int idx = (v * TPR + t) * 8;
       if (valid && idx < H) {
-        float o[8];
+        float xh[8], g[8], o[8];
+        unpack8(xq[v], xh);
+        unpack8(gq[v], g);
+        const float4 w0 = *reinterpret_cast<const float4*>(sw + idx);
+        const float4 w1 = *reinterpret_cast<const float4*>(sw + idx + 4);
+        const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = rstd * (m[v][i] - xh[v][i] * dot);
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[i] * wl[i] - xh[i] * rstd * dot);
         if (dres != nullptr) {
           float dr[8];
           unpack8(ld16(dres + row * H + idx), dr);
@@ -310,19 +321,30 @@ __global__ void __launch_bounds__(kRowThreads)
     dwb_partial[1LL * blockIdx.x * 2 * H + i] = sdw[i];
 }
 
-// out[c] (+)= sum_p partial[p, c]; one thread per column, coalesced across the warp.
-__global__ void colsum_kernel(const float* __restrict__ partial, int P, int C, void* out,
-                              int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// out[c] (+)= sum_p partial[p, c]. A CTA owns 32 columns; its 32 warps each sum a slice of the
+// partial rows (coalesced 128-byte reads), then the slices are combined in shared memory.
+__global__ void __launch_bounds__(1024)
+    colsum_kernel(const float* __restrict__ partial, int P, int C, void* out, int out_fp32,
+                  int accumulate) {
+  __shared__ float sm[32][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[1LL * p * C + c];
-  if (out_fp32) {
-    float* o = reinterpret_cast<float*>(out);
-    o[c] = accumulate ? o[c] + s : s;
-  } else {
-    bf16* o = reinterpret_cast<bf16*>(out);
-    o[c] = __float2bfloat16_rn(accumulate ? __bfloat162float(o[c]) + s : s);
+  if (c < C)
+    for (int p = grp; p < P; p += 32) s += partial[1LL * p * C + c];
+  sm[grp][lane] = s;
+  __syncthreads();
+  if (grp == 0 && c < C) {
+    float tot = 0.f;
+#pragma unroll
+    for (int g2 = 0; g2 < 32; ++g2) tot += sm[g2][lane];
+    if (out_fp32) {
+      float* o = reinterpret_cast<float*>(out);
+      o[c] = accumulate ? o[c] + tot : tot;
+    } else {
+      bf16* o = reinterpret_cast<bf16*>(out);
+      o[c] = __float2bfloat16_rn(accumulate ? __bfloat162float(o[c]) + tot : tot);
+    }
   }
 }
 
@@ -350,7 +372,7 @@ extern "C" int lb_rms_norm_fwd(const void* x, const void* res_in, const void* w,
   LB_ROW_DISPATCH(H, {
     constexpr int ROWS = kRowThreads / TPR;
     const int grid = (N + ROWS - 1) / ROWS;
-    rms_fwd_kernel<TPR, NV><<<grid, kRowThreads, 0, st>>>(
+    rms_fwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
         (const bf16*)x, (const bf16*)res_in, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, N, H,
         eps, w_off);
   });
@@ -369,12 +391,12 @@ extern "C" int lb_rms_norm_bwd(const void* dy, const void* dres, const void* xin
   LB_ROW_DISPATCH(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
-    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
+    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
         (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
         scratch, N, H, w_off);
   });
   if (dw_out != nullptr)
-    colsum_kernel<<<(H + 127) / 128, 128, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
+    colsum_kernel<<<(H + 31) / 32, 1024, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
   return launch_rc();
 }
 
@@ -411,7 +433,7 @@ extern "C" int lb_layer_norm_bwd(const void* dy, const void* dres, const void* x
         scratch, N, H);
   });
   if (dwb_out != nullptr)
-    colsum_kernel<<<(2 * H + 127) / 128, 128, 0, st>>>(scratch, grid, 2 * H, dwb_out, dw_fp32,
+    colsum_kernel<<<(2 * H + 31) / 32, 1024, 0, st>>>(scratch, grid, 2 * H, dwb_out, dw_fp32,
                                                        dw_accumulate);
   return launch_rc();
 }
@@ -419,7 +441,7 @@ extern "C" int lb_layer_norm_bwd(const void* dy, const void* dres, const void* x
 extern "C" int lb_colsum(const float* partial, int P, int C, void* out, int out_fp32,
                          int accumulate, void* stream) {
   if (C <= 0) return 0;
-  colsum_kernel<<<(C + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  colsum_kernel<<<(C + 31) / 32, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       partial, P, C, out, out_fp32, accumulate);
   return launch_rc();
 }
@@ -492,11 +514,11 @@ extern "C" int lb_rms_norm_bwd_noalloc(const void* dy, const void* dres, const v
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
     if (grid > LB_NOALLOC_MAX_PARTIAL_ROWS) grid = LB_NOALLOC_MAX_PARTIAL_ROWS;
-    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
+    rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
         (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
         scratch, N, H, w_off);
   });
   if (dw_out != nullptr)
-    colsum_kernel<<<(H + 127) / 128, 128, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
+    colsum_kernel<<<(H + 31) / 32, 1024, 0, st>>>(scratch, grid, H, dw_out, dw_fp32, dw_accumulate);
   return launch_rc();
 }

@@ -67,8 +67,10 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_fwd_kernel(RopeArgs a) {
   for (long long u0 = 1LL * blockIdx.x * UPB; u0 < units; u0 += 1LL * gridDim.x * UPB) {
     const long long u = u0 + u_in_block;
     const bool valid = u < units;
-    const long long tok = valid ? u / heads : 0;
-    const int h = valid ? int(u % heads) : 0;
+    // 32-bit index math: 64-bit division is many times slower and units fit in 32 bits
+    const unsigned u32 = unsigned(u);
+    const long long tok = valid ? u32 / unsigned(heads) : 0;
+    const int h = valid ? int(u32 % unsigned(heads)) : 0;
     const bool is_q = h < a.Hq;
     float x[8];
 #pragma unroll
@@ -172,8 +174,10 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_bwd_kernel(RopeBwdArgs a)
   for (long long u0 = 1LL * blockIdx.x * UPB; u0 < units; u0 += 1LL * gridDim.x * UPB) {
     const long long u = u0 + u_in_block;
     const bool valid = u < units;
-    const long long tok = valid ? u / heads : 0;
-    const int h = valid ? int(u % heads) : 0;
+    // 32-bit index math: 64-bit division is many times slower and units fit in 32 bits
+    const unsigned u32 = unsigned(u);
+    const long long tok = valid ? u32 / unsigned(heads) : 0;
+    const int h = valid ? int(u32 % unsigned(heads)) : 0;
     const bool is_q = h < a.Hq;
     float g[8];
 #pragma unroll
@@ -268,6 +272,7 @@ extern "C" int lb_qk_norm_rope_fwd(const void* q_in, long long ldq_in, const voi
                                    void* stream) {
   if (T <= 0) return 0;
   if ((ldq_in | ldk_in | ldq_out | ldk_out) & 7) return -3;
+  if (1LL * T * (Hq + Hk) >= (1LL << 32)) return -3;
   RopeArgs a{(const bf16*)q_in, (const bf16*)k_in, ldq_in, ldk_in, (const bf16*)qw, (const bf16*)kw,
              cos, sin, pos, pos_i64, pos_mod > 0 ? pos_mod : 1, (bf16*)q_out, (bf16*)k_out, ldq_out,
              ldk_out, q_rstd, k_rstd, T, Hq, Hk, eps, w_off, do_norm};
@@ -298,6 +303,7 @@ extern "C" int lb_qk_norm_rope_bwd(const void* dq, long long lddq, const void* d
                                    void* stream) {
   if (T <= 0) return 0;
   if ((lddq | lddk | ldq_in | ldk_in | lddq_in | lddk_in) & 7) return -3;
+  if (1LL * T * (Hq + Hk) >= (1LL << 32)) return -3;
   RopeBwdArgs a{(const bf16*)dq, (const bf16*)dk, lddq, lddk, (const bf16*)q_in, (const bf16*)k_in,
                 ldq_in, ldk_in, (const bf16*)qw, (const bf16*)kw, cos, sin, pos, pos_i64,
                 pos_mod > 0 ? pos_mod : 1, q_rstd, k_rstd, (bf16*)dq_in, (bf16*)dk_in, lddq_in,
