@@ -49,9 +49,10 @@ struct GemmArgs {
   float* pos;                 // [M] score of the target column (EPI_LSE output)
   const float* coef;          // device scalar multiplied into the probabilities' gradient
   long long target_offset;    // target column of row r is r + target_offset
-  // ---- peer gather of B (GATHER): rows of B live in `world` ranks' buffers, n_local rows each;
-  // two extra warps pull them into b_local ([world * n_local, K], the tensor map's base) and
-  // publish one flag per (rank, BN-row tile); tiles are visited in pull order, own rank first.
+  // ---- peer gather (GATHER 1: rows of B, GATHER 2: rows of A): the rows live in `world` ranks'
+  // buffers, n_local rows each; two extra warps pull them into b_local ([world * n_local, K], the
+  // base of that operand's tensor map) and publish one flag per (rank, row tile); tiles are
+  // visited in pull order, own rank first (its rows are placed by the host, no pull).
   const void* b_peers[8];
   void* b_local;
   long long ldb_peer;         // row stride (elements) of every rank's buffer and of b_local
@@ -133,19 +134,27 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + BN - 1) / BN : 0;
-  const int tiles_m = (g.M + BM - 1) / BM;
-  const int tiles_n = GATHER ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
+  // GATHER 1: rows of B come from the peers; GATHER 2: rows of A do. n_local = rows per rank.
+  constexpr int kGatherRows = GATHER == 2 ? BM : BN;
+  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 0;
+  const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
+  const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
   const int kb_total = (g.K + BK - 1) / BK;
   const int total = tiles_m * tiles_n * g.splits;
   // (m0, n0, flag index) of the `mn`-th output tile
   auto decode = [&](int mn, int& m0, int& n0, int& chunk) {
-    if constexpr (GATHER) {
+    if constexpr (GATHER == 1) {
       m0 = (mn % tiles_m) * BM;
       const int ni = mn / tiles_m;
       const int peer = (g.rank + ni / tiles_per_peer) % g.world;
       chunk = peer * tiles_per_peer + ni % tiles_per_peer;
       n0 = peer * g.n_local + (ni % tiles_per_peer) * BN;
+    } else if constexpr (GATHER == 2) {
+      n0 = (mn % tiles_n) * BN;
+      const int mi = mn / tiles_n;
+      const int peer = (g.rank + mi / tiles_per_peer) % g.world;
+      chunk = peer * tiles_per_peer + mi % tiles_per_peer;
+      m0 = peer * g.n_local + (mi % tiles_per_peer) * BM;
     } else {
       m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
       n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
@@ -280,7 +289,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         if (c >= unsigned(chunks)) break;
         const int peer = (g.rank + int(c) / tiles_per_peer) % g.world;
         const int t = int(c) % tiles_per_peer;
-        const int r0 = t * BN, r1 = peer == g.rank ? t * BN : min(r0 + BN, g.n_local);  // own rows are in place
+        const int r0 = t * kGatherRows;
+        const int r1 = peer == g.rank ? r0 : min(r0 + kGatherRows, g.n_local);  // own rows are in place
         const char* src = static_cast<const char*>(g.b_peers[peer]);
         char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
         const long long vec_per_row = row_bytes / 16;
@@ -322,7 +332,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       const int mn = tile - split * (tiles_m * tiles_n);
       int m0, n0, chunk;
       decode(mn, m0, n0, chunk);
-      const int n_limit = GATHER ? min(g.N, (n0 / g.n_local + 1) * g.n_local) : g.N;
+      const int n_limit = GATHER == 1 ? min(g.N, (n0 / g.n_local + 1) * g.n_local) : g.N;
+      const int m_limit = GATHER == 2 ? min(g.M, (m0 / g.n_local + 1) * g.n_local) : g.M;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aphase)) {
@@ -338,7 +349,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       [[maybe_unused]] const float s2 = g.scale * kLog2e;
       [[maybe_unused]] float lse2 = 0.f, cf = 0.f;
       if constexpr (EPI == EPI_PGRAD) {
-        lse2 = (row < g.M) ? g.lse[row] * kLog2e : 0.f;
+        lse2 = (row < m_limit) ? g.lse[row] * kLog2e : 0.f;
         cf = g.coef != nullptr ? g.coef[0] : 1.f;
       }
 #pragma unroll 1
@@ -347,7 +358,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row < g.M && col0 < g.N) {
+        if (row < m_limit && col0 < g.N) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -412,8 +423,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         }
       }
       if constexpr (EPI == EPI_LSE) {
-        if (row < g.M) {
-          const int part_idx = GATHER ? chunk : n0 / BN;
+        if (row < m_limit) {
+          const int part_idx = GATHER == 1 ? chunk : n0 / BN;
           float* pp = g.part + (static_cast<long long>(part_idx) * g.M + row) * 2;
           pp[0] = m_run;
           pp[1] = l_run;
@@ -752,4 +763,62 @@ extern "C" int lb_infonce_fwd_xrank(const void* q, long long ldq, const void* co
   if (rc) return rc;
   lse_merge_kernel<<<(M + 255) / 256, 256, 0, stream>>>(g.part, chunks, M, g.pos, lse, loss_sum);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// All-gather fused into a GEMM (tensor-parallel column layers and the input-gradient of row
+// layers): C[world * rows_local, N] = A_all · Bᵀ where A_all's rows are spread over `world` ranks
+// (a_peers[r]: rank r's [rows_local, K] bf16 slice in symmetric memory). Two extra warps per CTA
+// pull the peers' rows into a_all (local, [world * rows_local, K]; the caller has already copied
+// its own slice there) while the tensor-core tiles consume them in pull order, own rank first.
+// a_all is complete when the kernel ends, so the backward can reuse it. b_mn as in lb_gemm_bf16.
+// flags: [world * ceil(rows_local / 128)] u32, zero-initialised once; epoch must differ from every
+// earlier call that used these flags.
+extern "C" int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const void* B, void* C,
+                               int rows_local, int world, int rank, int N, int K, long long lda,
+                               long long ldb, long long ldc, int b_mn, const void* bias,
+                               unsigned* flags, unsigned* counter, unsigned epoch, int* status,
+                               void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > 8 || rows_local <= 0 || N <= 0 || K <= 0) return -3;
+  if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -3;
+  const int M = world * rows_local;
+  const int bn = N > 128 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, a_all, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true);
+  else
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, bn, true);
+  if (rc) return rc;
+  GemmArgs g{};
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.C = C;
+  g.ldc = ldc;
+  g.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  g.splits = 1;
+  g.kb_per_split = (K + BK - 1) / BK;
+  for (int i = 0; i < world; ++i) g.b_peers[i] = a_peers[i];
+  g.b_local = a_all;
+  g.ldb_peer = lda;
+  g.n_local = rows_local;
+  g.world = world;
+  g.rank = rank;
+  g.flags = flags;
+  g.chunk_counter = counter;
+  g.epoch = epoch;
+  g.status = status;
+  const int tiles_per_peer = (rows_local + BM - 1) / BM;
+  const long long total = 1LL * world * tiles_per_peer * ((N + bn - 1) / bn);
+  const int sms = num_sms();
+  const int grid = (int)(total < sms ? total : sms);
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), stream) != cudaSuccess) return -12;
+  if (b_mn)
+    return bn == 256 ? launch<0, 1, 256, __nv_bfloat16, EPI_STORE, 2>(tmA, tmB, g, grid, stream)
+                     : launch<0, 1, 128, __nv_bfloat16, EPI_STORE, 2>(tmA, tmB, g, grid, stream);
+  return bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_STORE, 2>(tmA, tmB, g, grid, stream)
+                   : launch<0, 0, 128, __nv_bfloat16, EPI_STORE, 2>(tmA, tmB, g, grid, stream);
 }

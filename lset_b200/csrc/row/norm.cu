@@ -391,6 +391,9 @@ extern "C" int lb_rms_norm_bwd(const void* dy, const void* dres, const void* xin
   LB_ROW_DISPATCH(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
+    if (2 * H * sizeof(float) > 48 * 1024)  // wide rows: opt in above the 48 KB default
+      cudaFuncSetAttribute(rms_bwd_kernel<TPR, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           2 * H * (int)sizeof(float));
     rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
         (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
         scratch, N, H, w_off);
@@ -428,6 +431,9 @@ extern "C" int lb_layer_norm_bwd(const void* dy, const void* dres, const void* x
   LB_ROW_DISPATCH(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
+    if (2 * H * sizeof(float) > 48 * 1024)
+      cudaFuncSetAttribute(ln_bwd_kernel<TPR, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           2 * H * (int)sizeof(float));
     ln_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
         (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, mean, rstd, (bf16*)dx,
         scratch, N, H);
@@ -514,6 +520,9 @@ extern "C" int lb_rms_norm_bwd_noalloc(const void* dy, const void* dres, const v
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
     if (grid > LB_NOALLOC_MAX_PARTIAL_ROWS) grid = LB_NOALLOC_MAX_PARTIAL_ROWS;
+    if (2 * H * sizeof(float) > 48 * 1024)  // wide rows: opt in above the 48 KB default
+      cudaFuncSetAttribute(rms_bwd_kernel<TPR, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           2 * H * (int)sizeof(float));
     rms_bwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
         (const bf16*)dy, (const bf16*)dres, (const bf16*)xin, (const bf16*)w, rstd, (bf16*)dx,
         scratch, N, H, w_off);

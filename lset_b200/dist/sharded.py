@@ -131,12 +131,20 @@ class ParamStore:
             # tensor-parallel shards and replicated parameters go to separate groups: their
             # squared norms are combined differently across the tensor-parallel ranks
             out = []
-            for tag, sel in (("", [p for p in ps if not getattr(p, "_tp_sharded", False)]),
-                             (".tp", [p for p in ps if getattr(p, "_tp_sharded", False)])):
+            def kind(p):
+                if getattr(p, "_tp_sharded", False):
+                    return ".tp"
+                return ".tpp" if getattr(p, "_tp_partial_grad", False) else ""
+
+            for tag in ("", ".tp", ".tpp"):
+                sel = [p for p in ps if kind(p) == tag]
                 if sel:
                     g = FlatGroup(name + tag, sel, self.world, self.rank, compute_dtype, self.device,
                                   dp_group, self.use_symm)
-                    g.tp_sharded = bool(tag)
+                    g.tp_sharded = tag == ".tp"
+                    # replicated parameter whose per-rank gradient is only a part of the total
+                    # (per-head norm weights; everything token-sharded under sequence parallelism)
+                    g.tp_partial = tag == ".tpp"
                     out.append(g)
             return out
 
@@ -162,7 +170,8 @@ class ParamStore:
         self.overlap = overlap and self.device.type == "cuda" and self.world > 1
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
         self._hooks = []
-        if self.world > 1:
+        self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+        if self.world > 1 or self.tp_world > 1:
             self._install_hooks()
 
     # ------------------------------------------------------------------ hooks
@@ -187,10 +196,14 @@ class ParamStore:
 
     # ------------------------------------------------------------------ collectives
     def _reduce_group(self, g: FlatGroup) -> None:
-        if g.reduced or self.world == 1:
-            g.reduced = True
+        if g.reduced:
             return
         g.collect_autograd_grads()
+        if getattr(g, "tp_partial", False) and self.tp_world > 1:
+            dist.all_reduce(g.flat_grad, op=dist.ReduceOp.SUM, group=self.tp_group)
+        if self.world == 1:
+            g.reduced = True
+            return
         if self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):

@@ -142,6 +142,10 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str]) -> nn.Module:
             _wrap_forward(module, "rowwise", tp_group)
             continue
         _wrap_forward(module, kind, tp_group)
+    # Per-head norm weights see only this rank's heads: their gradients are partial sums.
+    for name, p in model.named_parameters():
+        if name.endswith(("q_norm.weight", "k_norm.weight")):
+            p._tp_partial_grad = True
     model._tp_group = tp_group
     return model
 

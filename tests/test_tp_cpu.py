@@ -38,13 +38,24 @@ def _worker(rank, world, port, out_dir, fused):
     init_normal_(m, 0.05)
     full = {k: v.clone() for k, v in m.state_dict().items()}
     apply_tp(m, dist.group.WORLD, decoder_tp_plan(_cfg(), fused_projections=fused))
+    # data-parallel world of one per rank: the store only has to sum the partial gradients of the
+    # per-head norm weights over the tensor-parallel group
+    from lset_b200.dist.sharded import ParamStore
+
+    dp_groups = [dist.new_group([r]) for r in range(world)]
+    store = ParamStore(m, dp_group=dp_groups[rank], compute_dtype=torch.float32,
+                       device=torch.device("cpu"), tp_group=dist.group.WORLD)
     ids = torch.arange(14).reshape(2, 7) % 200
     out = m(ids)["hidden_states"]
     out.pow(2).sum().backward()
-    name = "layers.0.mlp.down_proj.weight"
-    g = dict(m.named_parameters())[name].grad
+    store.finish_backward()
+    params = dict(m.named_parameters())
+    g = params["layers.0.mlp.down_proj.weight"].main_grad.clone()
+    gq = params["layers.0.self_attn.q_norm.weight"].main_grad.clone()
+    gk = params["layers.1.self_attn.k_norm.weight"].main_grad.clone()
     if rank == 0:
-        torch.save({"out": out.detach(), "grad": g, "full": full}, os.path.join(out_dir, "tp.pt"))
+        torch.save({"out": out.detach(), "grad": g, "gq": gq, "gk": gk, "full": full},
+                   os.path.join(out_dir, "tp.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -62,6 +73,9 @@ def test_tp_matches_unsharded(fused):
     assert torch.allclose(out, got["out"], atol=1e-5), (out - got["out"]).abs().max()
     gfull = ref.layers[0].mlp.down_proj.weight.grad
     assert torch.allclose(gfull[:, :32], got["grad"], atol=1e-4)  # rank 0 owns the first half of the inputs
+    # per-head norm weights: each rank sees only its heads, the store sums the partial gradients
+    assert torch.allclose(ref.layers[0].self_attn.q_norm.weight.grad, got["gq"], atol=1e-4)
+    assert torch.allclose(ref.layers[1].self_attn.k_norm.weight.grad, got["gk"], atol=1e-4)
 
 
 def test_plans():
