@@ -38,6 +38,28 @@ MODEL = dict(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hi
              num_attention_heads=16, num_key_value_heads=8, head_dim=128,
              max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1_000_000.0,
              tie_word_embeddings=True, attention_bias=False)
+# The other training configurations of the comparison (selected with --config; the default is the
+# headline one). "pairs" are per data-parallel rank.
+MODEL_4B = dict(MODEL, hidden_size=2560, intermediate_size=9728, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8)
+MODEL_8B = dict(MODEL, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=False)
+PRESETS = {
+    "qwen3-0.6b": dict(
+        model=MODEL, pairs=64, tp=1, negs=0, lora_r=0,
+        metric="pairs/sec & tokens/sec, Qwen3-0.6B embed FSDP2 bf16, 1/2/4/8 B200, max over ranks",
+        label="Qwen3-0.6B (28L, H1024, 16q/8kv heads, hd128, FFN3072, vocab 151936), random init"),
+    "qwen3-4b-tp2": dict(
+        model=MODEL_4B, pairs=32, tp=2, negs=0, lora_r=0,
+        metric="pairs/sec & tokens/sec, Qwen3-4B embed TP2 x sharded DP bf16, max over ranks",
+        label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
+    "qwen3-8b-lora": dict(
+        model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16,
+        metric="pairs/sec & tokens/sec, Qwen3-8B embed + LoRA r16, sharded DP bf16, 3 hard negatives, "
+               "max over ranks",
+        label="Qwen3-8B (36L, H4096, 32q/8kv heads, hd128, FFN12288, vocab 151936), random init, "
+              "frozen base + LoRA r16 on q/k/v/o"),
+}
 PAIRS_PER_GPU = 64
 QUERY_LEN = (16, 64)
 DOC_LEN = (128, 512)
@@ -109,19 +131,25 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # data
 # ----------------------------------------------------------------------------------------------
-def make_samples(n_batches: int, rank: int, seed: int = 1234):
-    """Pre-tokenised samples: ``n_batches * PAIRS_PER_GPU`` (query, positive) dicts for one rank."""
+def make_samples(n_batches: int, rank: int, seed: int = 1234, pairs: int = PAIRS_PER_GPU,
+                 negs: int = 0):
+    """Pre-tokenised samples: ``n_batches * pairs`` (query, positive[, negatives]) dicts for one
+    data-parallel rank."""
     import torch
 
     gen = torch.Generator().manual_seed(seed + 7919 * rank)
+
+    def seq(lo, hi):
+        n = int(torch.randint(lo, hi + 1, (1,), generator=gen))
+        return {"input_ids": torch.randint(0, TOKEN_ID_MAX, (n,), generator=gen).tolist(),
+                "attention_mask": [1] * n}
+
     out = []
-    for _ in range(n_batches * PAIRS_PER_GPU):
-        ql = int(torch.randint(QUERY_LEN[0], QUERY_LEN[1] + 1, (1,), generator=gen))
-        dl = int(torch.randint(DOC_LEN[0], DOC_LEN[1] + 1, (1,), generator=gen))
-        q = torch.randint(0, TOKEN_ID_MAX, (ql,), generator=gen).tolist()
-        d = torch.randint(0, TOKEN_ID_MAX, (dl,), generator=gen).tolist()
-        out.append({"query": {"input_ids": q, "attention_mask": [1] * ql},
-                    "positive": {"input_ids": d, "attention_mask": [1] * dl}})
+    for _ in range(n_batches * pairs):
+        item = {"query": seq(*QUERY_LEN), "positive": seq(*DOC_LEN)}
+        if negs:
+            item["negatives"] = [seq(*DOC_LEN) for _ in range(negs)]
+        out.append(item)
     return out
 
 
@@ -172,20 +200,25 @@ def barrier_sync(device):
     torch.cuda.synchronize(device)
 
 
-def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, launches, extra_cfg):
+def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, launches, extra_cfg,
+                preset=None):
+    preset = preset or PRESETS["qwen3-0.6b"]
     pairs_s = pairs / (ms / 1e3)
+    tp = preset["tp"]
+    par = f"dp{n_gpus // tp}" + (f" x tp{tp}" if tp > 1 else "")
     line = {
-        "metric": "pairs/sec & tokens/sec, Qwen3-0.6B embed FSDP2 bf16, 1/2/4/8 B200, max over ranks",
+        "metric": preset["metric"],
         "value": pairs_s, "unit": "pairs/s", "tokens_per_sec": tokens / (ms / 1e3),
         "n_gpus": n_gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (pairs_s / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
         "dtype": "bf16", "data": "synthetic", "impl": impl,
         "config": dict({
-            "model": "Qwen3-0.6B (28L, H1024, 16q/8kv heads, hd128, FFN3072, vocab 151936), random init",
-            "global_batch": PAIRS_PER_GPU * n_gpus, "pairs_per_gpu": PAIRS_PER_GPU,
+            "model": preset["label"],
+            "global_batch": pairs, "pairs_per_dp_rank": preset["pairs"],
+            "hard_negatives_per_pair": preset["negs"],
             "seq_len": "query U[16,64], passage U[128,512], packed varlen stream (cu_seqlens)",
-            "parallelism": f"dp{n_gpus}" + (" (sharded optimizer/grad, ZeRO)" if n_gpus > 1 else ""),
+            "parallelism": par + (" (sharded optimizer/grad, ZeRO)" if n_gpus // tp > 1 else ""),
             "loss": "InfoNCE T=0.02, global in-batch negatives", "optimizer": "AdamW lr 2e-5, clip 1.0",
             "l2": "per-step working set (weights+optimizer+activations, several GB) exceeds the "
                   "126 MB L2; no explicit flush",
@@ -214,17 +247,36 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device")
     nv.load()
     K, W = args.steps, args.warmup
+    preset = PRESETS[args.config]
+    tp, P = preset["tp"], preset["pairs"]
+    if world % tp:
+        raise SystemExit(f"--config {args.config} needs a multiple of {tp} GPUs")
+    dp = world // tp
+
+    class BenchCollator(PackedCollator):
+        """Packed collator that also flattens a list of hard negatives per sample."""
+
+        def __call__(self, batch):
+            out = super().__call__(batch)
+            if "negatives" in batch[0]:
+                out["neg"] = self._batch([n for s in batch for n in s["negatives"]])
+            return out
+
     engine = TrainingEngine(
-        "qwen3", None, dataset=None, dp_size=world, tp_size=1, batch_size=PAIRS_PER_GPU, lr=LR,
+        "qwen3", None, dataset=None, dp_size=dp, tp_size=tp, batch_size=P, lr=LR,
         max_steps=10**9, grad_clip=1.0, temperature=TEMPERATURE, packed=True, log_interval=0,
-        scheduler_type="constant", model_config=Qwen3Config(**MODEL), fused_projections=True,
-        collator=PackedCollator())
+        scheduler_type="constant", model_config=Qwen3Config(**preset["model"]),
+        fused_projections=preset["lora_r"] == 0, collator=BenchCollator(), async_tp=tp > 1,
+        lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0)
     device = engine.device
     n_batches = W + 2 * K
-    samples = make_samples(n_batches, rank)
-    coll = PackedCollator()
-    host = [pin(coll(samples[i * PAIRS_PER_GPU:(i + 1) * PAIRS_PER_GPU])) for i in range(n_batches)]
-    tokens = [int(b["query"]["input_ids"].numel() + b["doc"]["input_ids"].numel()) for b in host]
+    # ranks of one tensor-parallel group see the same batch
+    samples = make_samples(n_batches, engine.dp_rank if tp > 1 else rank, pairs=P,
+                           negs=preset["negs"])
+    coll = BenchCollator()
+    host = [pin(coll(samples[i * P:(i + 1) * P])) for i in range(n_batches)]
+    tokens = [sum(int(b[k]["input_ids"].numel()) for k in ("query", "doc", "neg") if k in b)
+              for b in host]
 
     for i in range(W):
         engine.train_step(host[i]).item()
@@ -246,7 +298,7 @@ def run_ours(args):
     barrier_sync(device)
     ms_dev = max_over_ranks(e0.elapsed_time(e1) / K, device)
     launches = nv.launches()
-    tok_dev = sum_over_ranks(float(sum(tokens[W:W + K])) / K, device)
+    tok_dev = sum_over_ranks(float(sum(tokens[W:W + K])) / K, device) / tp
     del staged
 
     # ---- end-to-end region: pinned host batch -> H2D -> step -> loss read back, every step
@@ -262,14 +314,15 @@ def run_ours(args):
     ms_e2e = max_over_ranks(e2.elapsed_time(e3) / K, device)
     nv.check_status(device)
     h2d = sum(batch_bytes(b) for b in host[W + K:W + 2 * K]) / K
-    pairs = PAIRS_PER_GPU * world
+    pairs = P * dp
     e2e = {"value": pairs / (ms_e2e / 1e3), "unit": "pairs/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "last_loss": last,
            "api": "lset_b200.train.engine.TrainingEngine.train_step(pinned host batch) + loss.item()"}
     if rank == 0:
         print(json.dumps(result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e,
                                      launches,
-                                     {"fused_projections": True, "native_library": str(nv.lib_path().name)})))
+                                     {"fused_projections": preset["lora_r"] == 0,
+                                      "native_library": str(nv.lib_path().name)}, preset)))
     import torch.distributed as dist
 
     if dist.is_initialized():
@@ -281,6 +334,10 @@ def run_ours(args):
 # reference arm: the unmodified reference package from baseline/_ref, through its own engine
 # ----------------------------------------------------------------------------------------------
 def run_reference(args):
+    if args.config != "qwen3-0.6b":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference arm is wired for the headline config (qwen3-0.6b) only"}))
+        return
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "lset")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lset is not installed"}))
@@ -423,6 +480,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--config", choices=sorted(PRESETS), default="qwen3-0.6b")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -96,6 +96,36 @@ __device__ __forceinline__ float row_sum(float v, float* sred) {
     }                                                              \
   } while (0)
 
+// Narrow variant for kernels with long-lived per-column accumulators (backward passes): twice the
+// threads per row, half the vectors per thread, so that more CTAs fit per SM.
+#define LB_ROW_DISPATCH_NARROW(H, ...)                              \
+  do {                                                             \
+    if ((H) <= 128) {                                              \
+      constexpr int TPR = 16, NV = 1;                              \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 256) {                                       \
+      constexpr int TPR = 32, NV = 1;                              \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 512) {                                       \
+      constexpr int TPR = 64, NV = 1;                              \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 1024) {                                      \
+      constexpr int TPR = 64, NV = 2;                              \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 2048) {                                      \
+      constexpr int TPR = 128, NV = 2;                             \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 4096) {                                      \
+      constexpr int TPR = 256, NV = 2;                             \
+      __VA_ARGS__;                                                 \
+    } else if ((H) <= 8192) {                                      \
+      constexpr int TPR = 256, NV = 4;                             \
+      __VA_ARGS__;                                                 \
+    } else {                                                       \
+      return -3;                                                   \
+    }                                                              \
+  } while (0)
+
 inline int row_num_sms() {
   static int sms = 0;
   if (sms == 0) {

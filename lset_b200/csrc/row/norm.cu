@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kRowThreads)
 // Backward keeps x and dy as packed bf16 in registers (unpacked twice) and the weights in shared
 // memory, so that only the fp32 dW accumulators are long-lived: two CTAs fit per SM.
 template <int TPR, int NV>
-__global__ void __launch_bounds__(kRowThreads, 2)
+__global__ void __launch_bounds__(kRowThreads, 3)
     rms_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ dres,
                    const bf16* __restrict__ xin, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, bf16* __restrict__ dx,
@@ -98,14 +98,16 @@ __global__ void __launch_bounds__(kRowThreads, 2)
     const long long row = row0 + r;
     const bool valid = row < N;
     const float rstd = valid ? rstd_in[row] : 0.f;
-    uint4 xq[NV], gq[NV];
+    uint4 xq[NV], gq[NV], rq[NV];
     float dot = 0.f;
+    // every load of the row is requested before the first use
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int idx = (v * TPR + t) * 8;
       if (valid && idx < H) {
         xq[v] = ld16(xin + row * H + idx);
         gq[v] = ld16(dy + row * H + idx);
+        if (dres != nullptr) rq[v] = ld16(dres + row * H + idx);
       }
     }
 #pragma unroll
@@ -141,7 +143,7 @@ __global__ void __launch_bounds__(kRowThreads, 2)
         for (int i = 0; i < 8; ++i) o[i] = rstd * (g[i] * wl[i] - xh[i] * rstd * dot);
         if (dres != nullptr) {
           float dr[8];
-          unpack8(ld16(dres + row * H + idx), dr);
+          unpack8(rq[v], dr);
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] += dr[i];
         }
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(1024)
 
 int bwd_grid(int N, int rows_per_cta) {
   const int need = (N + rows_per_cta - 1) / rows_per_cta;
-  const int cap = row_num_sms() * 8;
+  const int cap = row_num_sms() * 6;  // two waves at three CTAs per SM
   return need < cap ? (need > 0 ? need : 1) : cap;
 }
 
@@ -388,7 +390,7 @@ extern "C" int lb_rms_norm_bwd(const void* dy, const void* dres, const void* xin
   if (H & 7) return -3;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = 1;
-  LB_ROW_DISPATCH(H, {
+  LB_ROW_DISPATCH_NARROW(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
     if (2 * H * sizeof(float) > 48 * 1024)  // wide rows: opt in above the 48 KB default
@@ -428,7 +430,7 @@ extern "C" int lb_layer_norm_bwd(const void* dy, const void* dres, const void* x
   if (H & 7) return -3;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = 1;
-  LB_ROW_DISPATCH(H, {
+  LB_ROW_DISPATCH_NARROW(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
     if (2 * H * sizeof(float) > 48 * 1024)
@@ -516,7 +518,7 @@ extern "C" int lb_rms_norm_bwd_noalloc(const void* dy, const void* dres, const v
   if (int rc = noalloc_scratch(&scratch)) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = 1;
-  LB_ROW_DISPATCH(H, {
+  LB_ROW_DISPATCH_NARROW(H, {
     constexpr int ROWS = kRowThreads / TPR;
     grid = bwd_grid(N, ROWS);
     if (grid > LB_NOALLOC_MAX_PARTIAL_ROWS) grid = LB_NOALLOC_MAX_PARTIAL_ROWS;

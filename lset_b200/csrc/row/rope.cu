@@ -43,14 +43,17 @@ __device__ __forceinline__ int token_pos(const RopeArgs& a, long long tok) {
                    : reinterpret_cast<const int*>(a.pos)[tok];
 }
 
+// A group of HD/8 lanes owns one token at a time and walks over its heads UB at a time: the cos/sin
+// row and the position are fetched once per token, and UB independent 16-byte loads are in flight
+// per thread before the first one is consumed (the kernel is bound by memory latency otherwise).
 template <int HD>
-__global__ void __launch_bounds__(kRowThreads) qk_rope_fwd_kernel(RopeArgs a) {
+__global__ void __launch_bounds__(kRowThreads, 2) qk_rope_fwd_kernel(RopeArgs a) {
   constexpr int LPH = HD / 8;  // lanes per head
-  constexpr int UPB = kRowThreads / LPH;
+  constexpr int TPB = kRowThreads / LPH;
+  constexpr int UB = 8;
   const int l = threadIdx.x % LPH;
-  const int u_in_block = threadIdx.x / LPH;
+  const int g = threadIdx.x / LPH;
   const int heads = a.Hq + a.Hk;
-  const long long units = 1LL * a.T * heads;
   const int e0 = l * 8;
   const int c0 = e0 % (HD / 2);
   const bool first_half = l < LPH / 2;
@@ -64,54 +67,66 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_fwd_kernel(RopeArgs a) {
       wk[i] += a.w_off;
     }
   }
-  for (long long u0 = 1LL * blockIdx.x * UPB; u0 < units; u0 += 1LL * gridDim.x * UPB) {
-    const long long u = u0 + u_in_block;
-    const bool valid = u < units;
-    // 32-bit index math: 64-bit division is many times slower and units fit in 32 bits
-    const unsigned u32 = unsigned(u);
-    const long long tok = valid ? u32 / unsigned(heads) : 0;
-    const int h = valid ? int(u32 % unsigned(heads)) : 0;
-    const bool is_q = h < a.Hq;
-    float x[8];
+  for (int tok0 = blockIdx.x * TPB; tok0 < a.T; tok0 += gridDim.x * TPB) {
+    const long long tok = tok0 + g;
+    const bool valid = tok < a.T;
+    float c[8], s[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = 0.f;
-    if (valid) {
-      const bf16* src = is_q ? a.q_in + tok * a.ldq_in + h * HD + e0
-                             : a.k_in + tok * a.ldk_in + (h - a.Hq) * HD + e0;
-      unpack8(ld16(src), x);
-    }
-    if (a.do_norm) {
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-#pragma unroll
-      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float rstd = rsqrtf(ss / float(HD) + a.eps);
-      if (valid && l == 0) {
-        if (is_q) a.q_rstd[tok * a.Hq + h] = rstd;
-        else a.k_rstd[tok * a.Hk + (h - a.Hq)] = rstd;
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = bf16_round(x[i] * rstd) * (is_q ? wq[i] : wk[i]);
-    }
-    float p[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) p[i] = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
+    for (int i = 0; i < 8; ++i) c[i] = s[i] = 0.f;
     if (valid) {
       const int pos = token_pos(a, tok);
       const float4* cp = reinterpret_cast<const float4*>(a.cos + 1LL * pos * (HD / 2) + c0);
       const float4* sp = reinterpret_cast<const float4*>(a.sin + 1LL * pos * (HD / 2) + c0);
-      float c[8], s[8];
       *reinterpret_cast<float4*>(c) = cp[0];
       *reinterpret_cast<float4*>(c + 4) = cp[1];
       *reinterpret_cast<float4*>(s) = sp[0];
       *reinterpret_cast<float4*>(s + 4) = sp[1];
-      float y[8];
+    }
+    if (!first_half) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = first_half ? x[i] * c[i] - p[i] * s[i] : x[i] * c[i] + p[i] * s[i];
-      bf16* dst = is_q ? a.q_out + tok * a.ldq_out + h * HD + e0
-                       : a.k_out + tok * a.ldk_out + (h - a.Hq) * HD + e0;
-      st16(dst, pack8(y));
+      for (int i = 0; i < 8; ++i) s[i] = -s[i];  // y = x*c - partner*s (first half), + (second)
+    }
+    const bf16* qrow = a.q_in + tok * a.ldq_in + e0;
+    const bf16* krow = a.k_in + tok * a.ldk_in + e0;
+    bf16* qdst = a.q_out + tok * a.ldq_out + e0;
+    bf16* kdst = a.k_out + tok * a.ldk_out + e0;
+    for (int h0 = 0; h0 < heads; h0 += UB) {
+      uint4 raw[UB];
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int h = h0 + j;
+        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (valid && h < heads) raw[j] = ld16(h < a.Hq ? qrow + h * HD : krow + (h - a.Hq) * HD);
+      }
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int h = h0 + j;
+        if (h >= heads) break;  // uniform over the CTA
+        const bool is_q = h < a.Hq;
+        float x[8];
+        unpack8(raw[j], x);
+        if (a.do_norm) {
+          float ss = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+          for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          const float rstd = rsqrtf(ss / float(HD) + a.eps);
+          if (valid && l == 0) {
+            if (is_q) a.q_rstd[tok * a.Hq + h] = rstd;
+            else a.k_rstd[tok * a.Hk + (h - a.Hq)] = rstd;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = bf16_round(x[i] * rstd) * (is_q ? wq[i] : wk[i]);
+        }
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float p = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
+          y[i] = x[i] * c[i] - p * s[i];
+        }
+        if (valid) st16(is_q ? qdst + h * HD : kdst + (h - a.Hq) * HD, pack8(y));
+      }
     }
   }
 }
@@ -141,110 +156,120 @@ struct RopeBwdArgs {
   int do_norm;
 };
 
+// Same token-per-lane-group walk as the forward kernel, UB heads at a time: the gradient rows, the
+// forward inputs and the saved rstd of UB heads are requested before any of them is used.
 template <int HD>
-__global__ void __launch_bounds__(kRowThreads) qk_rope_bwd_kernel(RopeBwdArgs a) {
+__global__ void __launch_bounds__(kRowThreads, 2) qk_rope_bwd_kernel(RopeBwdArgs a) {
   constexpr int LPH = HD / 8;
-  constexpr int UPB = kRowThreads / LPH;
+  constexpr int TPB = kRowThreads / LPH;
+  constexpr int UB = 4;
   __shared__ float sdw[2 * HD];
+  __shared__ float swt[2 * HD];  // q then k norm weights (+ offset)
   const int l = threadIdx.x % LPH;
-  const int u_in_block = threadIdx.x / LPH;
+  const int g = threadIdx.x / LPH;
   const int heads = a.Hq + a.Hk;
-  const long long units = 1LL * a.T * heads;
   const int e0 = l * 8;
   const int c0 = e0 % (HD / 2);
   const bool first_half = l < LPH / 2;
-  float wq[8], wk[8], dwq[8], dwk[8];
+  float dwq[8], dwk[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) dwq[i] = dwk[i] = 0.f;
-  if (a.do_norm) {
-    unpack8(ld16(a.qw + e0), wq);
-    unpack8(ld16(a.kw + e0), wk);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      wq[i] += a.w_off;
-      wk[i] += a.w_off;
-    }
+  for (int i = threadIdx.x; i < 2 * HD; i += kRowThreads) {
+    sdw[i] = 0.f;
+    swt[i] = a.do_norm ? __bfloat162float(i < HD ? a.qw[i] : a.kw[i - HD]) + a.w_off : 1.f;
   }
-  for (int i = threadIdx.x; i < 2 * HD; i += kRowThreads) sdw[i] = 0.f;
+  __syncthreads();
   RopeArgs pa;  // only the position fields are used by token_pos
   pa.pos = a.pos;
   pa.pos_i64 = a.pos_i64;
   pa.pos_mod = a.pos_mod;
 
-  for (long long u0 = 1LL * blockIdx.x * UPB; u0 < units; u0 += 1LL * gridDim.x * UPB) {
-    const long long u = u0 + u_in_block;
-    const bool valid = u < units;
-    // 32-bit index math: 64-bit division is many times slower and units fit in 32 bits
-    const unsigned u32 = unsigned(u);
-    const long long tok = valid ? u32 / unsigned(heads) : 0;
-    const int h = valid ? int(u32 % unsigned(heads)) : 0;
-    const bool is_q = h < a.Hq;
-    float g[8];
+  for (int tok0 = blockIdx.x * TPB; tok0 < a.T; tok0 += gridDim.x * TPB) {
+    const long long tok = tok0 + g;
+    const bool valid = tok < a.T;
+    float c[8], s[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] = 0.f;
-    if (valid) {
-      const bf16* src = is_q ? a.dq + tok * a.lddq + h * HD + e0
-                             : a.dk + tok * a.lddk + (h - a.Hq) * HD + e0;
-      unpack8(ld16(src), g);
-    }
-    float p[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) p[i] = __shfl_xor_sync(0xffffffffu, g[i], LPH / 2);
-    float gn[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) gn[i] = 0.f;
+    for (int i = 0; i < 8; ++i) c[i] = s[i] = 0.f;
     if (valid) {
       const int pos = token_pos(pa, tok);
       const float4* cp = reinterpret_cast<const float4*>(a.cos + 1LL * pos * (HD / 2) + c0);
       const float4* sp = reinterpret_cast<const float4*>(a.sin + 1LL * pos * (HD / 2) + c0);
-      float c[8], s[8];
       *reinterpret_cast<float4*>(c) = cp[0];
       *reinterpret_cast<float4*>(c + 4) = cp[1];
       *reinterpret_cast<float4*>(s) = sp[0];
       *reinterpret_cast<float4*>(s + 4) = sp[1];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) gn[i] = first_half ? g[i] * c[i] + p[i] * s[i] : g[i] * c[i] - p[i] * s[i];
     }
-    float o[8];
-    if (a.do_norm) {
-      float x[8];
+    if (!first_half) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = 0.f;
-      float rstd = 0.f;
-      if (valid) {
-        const bf16* src = is_q ? a.q_in + tok * a.ldq_in + h * HD + e0
-                               : a.k_in + tok * a.ldk_in + (h - a.Hq) * HD + e0;
-        unpack8(ld16(src), x);
-        rstd = is_q ? a.q_rstd[tok * a.Hq + h] : a.k_rstd[tok * a.Hk + (h - a.Hq)];
-      }
-      float m[8];
-      float dot = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        x[i] *= rstd;  // xhat
-        m[i] = gn[i] * (is_q ? wq[i] : wk[i]);
-        dot += m[i] * x[i];
-        const float dwv = gn[i] * bf16_round(x[i]);
-        if (is_q) dwq[i] += dwv;
-        else dwk[i] += dwv;
-      }
-#pragma unroll
-      for (int s = LPH / 2; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-      dot /= float(HD);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = rstd * (m[i] - x[i] * dot);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = gn[i];
+      for (int i = 0; i < 8; ++i) s[i] = -s[i];  // gn = g*c + partner*s (first half), - (second)
     }
-    if (valid) {
-      bf16* dst = is_q ? a.dq_in + tok * a.lddq_in + h * HD + e0
-                       : a.dk_in + tok * a.lddk_in + (h - a.Hq) * HD + e0;
-      st16(dst, pack8(o));
+    const bf16* gq = a.dq + tok * a.lddq + e0;
+    const bf16* gk = a.dk + tok * a.lddk + e0;
+    const bf16* xq = a.q_in + tok * a.ldq_in + e0;
+    const bf16* xk = a.k_in + tok * a.ldk_in + e0;
+    bf16* oq = a.dq_in + tok * a.lddq_in + e0;
+    bf16* ok = a.dk_in + tok * a.lddk_in + e0;
+    for (int h0 = 0; h0 < heads; h0 += UB) {
+      uint4 graw[UB], xraw[UB];
+      float rs[UB];
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int h = h0 + j;
+        graw[j] = xraw[j] = make_uint4(0u, 0u, 0u, 0u);
+        rs[j] = 0.f;
+        if (valid && h < heads) {
+          const bool is_q = h < a.Hq;
+          graw[j] = ld16(is_q ? gq + h * HD : gk + (h - a.Hq) * HD);
+          if (a.do_norm) {
+            xraw[j] = ld16(is_q ? xq + h * HD : xk + (h - a.Hq) * HD);
+            rs[j] = is_q ? a.q_rstd[tok * a.Hq + h] : a.k_rstd[tok * a.Hk + (h - a.Hq)];
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int h = h0 + j;
+        if (h >= heads) break;  // uniform over the CTA
+        const bool is_q = h < a.Hq;
+        float gv[8], gn[8], o[8];
+        unpack8(graw[j], gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float p = __shfl_xor_sync(0xffffffffu, gv[i], LPH / 2);
+          gn[i] = gv[i] * c[i] + p * s[i];
+        }
+        if (a.do_norm) {
+          float x[8], m[8];
+          unpack8(xraw[j], x);
+          const float rstd = rs[j];
+          const float* wt = swt + (is_q ? 0 : HD) + e0;
+          const float4 w0 = *reinterpret_cast<const float4*>(wt);
+          const float4 w1 = *reinterpret_cast<const float4*>(wt + 4);
+          const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          float dot = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x[i] *= rstd;  // xhat
+            m[i] = gn[i] * wl[i];
+            dot += m[i] * x[i];
+            const float dwv = gn[i] * bf16_round(x[i]);
+            if (is_q) dwq[i] += dwv;
+            else dwk[i] += dwv;
+          }
+#pragma unroll
+          for (int sh = LPH / 2; sh > 0; sh >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sh);
+          dot /= float(HD);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = rstd * (m[i] - x[i] * dot);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = gn[i];
+        }
+        if (valid) st16(is_q ? oq + h * HD : ok + (h - a.Hq) * HD, pack8(o));
+      }
     }
   }
   if (a.do_norm && a.dw_partial != nullptr) {
-    __syncthreads();
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       atomicAdd(&sdw[e0 + i], dwq[i]);
@@ -277,11 +302,10 @@ extern "C" int lb_qk_norm_rope_fwd(const void* q_in, long long ldq_in, const voi
              cos, sin, pos, pos_i64, pos_mod > 0 ? pos_mod : 1, (bf16*)q_out, (bf16*)k_out, ldq_out,
              ldk_out, q_rstd, k_rstd, T, Hq, Hk, eps, w_off, do_norm};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long units = 1LL * T * (Hq + Hk);
   auto grid_for = [&](int lph) {
-    const long long upb = kRowThreads / lph;
-    long long g = (units + upb - 1) / upb;
-    const long long cap = 1LL * row_num_sms() * 16;
+    const long long tpb = kRowThreads / lph;
+    long long g = (T + tpb - 1) / tpb;
+    const long long cap = 1LL * row_num_sms() * 8;
     return int(g < cap ? g : cap);
   };
   if (hd == 128) qk_rope_fwd_kernel<128><<<grid_for(16), kRowThreads, 0, st>>>(a);
@@ -309,11 +333,10 @@ extern "C" int lb_qk_norm_rope_bwd(const void* dq, long long lddq, const void* d
                 pos_mod > 0 ? pos_mod : 1, q_rstd, k_rstd, (bf16*)dq_in, (bf16*)dk_in, lddq_in,
                 lddk_in, scratch, T, Hq, Hk, w_off, do_norm};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long units = 1LL * T * (Hq + Hk);
   auto grid_for = [&](int lph) {
-    const long long upb = kRowThreads / lph;
-    long long g = (units + upb - 1) / upb;
-    const long long cap = 1LL * row_num_sms() * 8;
+    const long long tpb = kRowThreads / lph;
+    long long g = (T + tpb - 1) / tpb;
+    const long long cap = 1LL * row_num_sms() * 4;
     return int(g < cap ? (g > 0 ? g : 1) : cap);
   };
   int grid;

@@ -79,6 +79,21 @@ def _shard_rows(t: torch.Tensor, sections: Optional[List[int]], rank: int, world
     return torch.cat(parts, dim=0).contiguous()
 
 
+def _wrap_forward_sp(module: nn.Module, kind: str, st) -> None:
+    """Sequence-parallel variant: the collectives are part of the (fused) linear ops."""
+    from . import tp_fused
+
+    if kind == "colwise":
+        def forward(x):
+            return tp_fused.ag_linear(x, module.weight, module.bias, st)
+    else:
+        def forward(x):
+            return tp_fused.linear_rs(x, module.weight, module.bias, st)
+
+    module.forward = forward
+    module._tp_kind = kind
+
+
 def _wrap_forward(module: nn.Module, kind: str, group) -> None:
     inner = module.forward
 
@@ -103,10 +118,26 @@ def _wrap_forward(module: nn.Module, kind: str, group) -> None:
     module._tp_kind = kind
 
 
-def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str]) -> nn.Module:
+def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str],
+             sequence_parallel: Optional[bool] = None) -> nn.Module:
+    """``sequence_parallel`` (default: on when the plan marks the norms ``"sequence"``) shards the
+    residual stream by tokens between the blocks and swaps the all-reduces for all-gather /
+    reduce-scatter pairs fused into the GEMMs (``lset_b200.dist.tp_fused``)."""
     world, rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
     if world == 1:
         return model
+    if sequence_parallel is None:
+        sequence_parallel = any(v == "sequence" for v in plan.values())
+    sp_state = None
+    if sequence_parallel:
+        if not hasattr(model, "_sp"):
+            raise ValueError(f"{type(model).__name__} has no sequence-parallel forward")
+        if any(isinstance(m, nn.Linear) and n.rsplit(".", 1)[-1] in ("lora_A", "lora_B")
+               for n, m in model.named_modules()):
+            raise ValueError("sequence parallelism is not combined with LoRA adapters")
+        from .tp_fused import SPState
+
+        sp_state = SPState(tp_group)
     for name, module in list(model.named_modules()):
         kind = next((k for pat, k in plan.items() if fnmatch.fnmatchcase(name, pat)), None)
         if kind not in ("colwise", "rowwise") or not isinstance(module, nn.Linear):
@@ -141,11 +172,20 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str]) -> nn.Module:
         if leaf == "lora_A" and kind == "rowwise":
             _wrap_forward(module, "rowwise", tp_group)
             continue
-        _wrap_forward(module, kind, tp_group)
-    # Per-head norm weights see only this rank's heads: their gradients are partial sums.
+        if sp_state is not None:
+            _wrap_forward_sp(module, kind, sp_state)
+        else:
+            _wrap_forward(module, kind, tp_group)
+    # Per-head norm weights see only this rank's heads: their gradients are partial sums. Under
+    # sequence parallelism every replicated parameter inside the blocks sees only this rank's
+    # tokens; the embedding does not (the gradient of the token shard is gathered before it).
     for name, p in model.named_parameters():
         if name.endswith(("q_norm.weight", "k_norm.weight")):
             p._tp_partial_grad = True
+        elif sp_state is not None and not getattr(p, "_tp_sharded", False) \
+                and "embed" not in name:
+            p._tp_partial_grad = True
+    model._sp = sp_state
     model._tp_group = tp_group
     return model
 

@@ -124,8 +124,16 @@ class DecoderModel(nn.Module):
 
         return embedding(flat_ids, self.embed_tokens.weight, scale=self.traits.embed_scale)
 
+    _sp = None  # sequence-parallel state, set by ``lset_b200.dist.tp.apply_tp``
+
     def _run(self, flat_ids, ctx: StreamCtx):
         branch, residual = self._embed(flat_ids), None
+        sp = self._sp
+        if sp is not None:
+            from ..dist import tp_fused
+
+            T = branch.shape[0]
+            branch = tp_fused.shard_tokens(branch, sp)  # blocks see this rank's tokens only
         prev_post = None
         for layer in self.layers:
             branch, residual = layer(branch, residual, ctx, prev_post)
@@ -136,6 +144,8 @@ class DecoderModel(nn.Module):
                 residual, branch, prev_post.weight, n.weight, n.eps, n.w_off)
         else:
             hidden, _ = norm_ops.residual_rms_norm(residual, branch, n.weight, n.eps, n.w_off)
+        if sp is not None:
+            hidden = tp_fused.unshard_tokens(hidden, T, sp)
         return hidden
 
 

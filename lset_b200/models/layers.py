@@ -127,7 +127,10 @@ class Attention(nn.Module):
             self.q_norm = self.k_norm = None
 
     def forward(self, x, ctx: StreamCtx):
-        T, hd = x.shape[0], self.head_dim
+        # T is the full stream length: under sequence parallelism ``x`` holds only this rank's
+        # tokens, the projections return every token (padded to a multiple of the group size) and
+        # ``o_proj`` hands back a token shard again.
+        T, hd = int(ctx.pos.shape[0]), self.head_dim
         cos, sin = ctx.rope(hd, self.rope_theta, self.rope_scaling)
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
@@ -135,20 +138,26 @@ class Attention(nn.Module):
         w_off = self.q_norm.w_off if self.q_norm is not None else 0.0
         if self.fused_qkv:
             qkv = self.qkv_proj(x)
+            Tp = qkv.shape[0]
             # head counts come from the local weight shape so a tensor-parallel shard just works
             per = self.num_heads // self.num_kv_heads
             Hk = qkv.shape[-1] // ((per + 2) * hd)
             Hq = Hk * per
-            o = attn_ops.qkv_attention(qkv.view(T, Hq + 2 * Hk, hd), qw, kw, cos, sin, ctx.pos,
+            o = attn_ops.qkv_attention(qkv[:T].view(T, Hq + 2 * Hk, hd), qw, kw, cos, sin, ctx.pos,
                                        ctx.plan, Hq, Hk, self.causal, self.softmax_scale, eps, w_off)
         else:
-            q = self.q_proj(x).view(T, -1, hd)
-            k = self.k_proj(x).view(T, -1, hd)
-            v = self.v_proj(x).view(T, -1, hd)
+            q = self.q_proj(x)
+            Tp = q.shape[0]
+            q = q[:T].view(T, -1, hd)
+            k = self.k_proj(x)[:T].view(T, -1, hd)
+            v = self.v_proj(x)[:T].view(T, -1, hd)
             Hq = q.shape[1]
             q, k = rope_ops.qk_norm_rope(q, k, qw, kw, cos, sin, ctx.pos, eps, w_off)
             o = attn_ops.varlen_attention(q, k, v, ctx.plan, self.causal, self.softmax_scale)
-        return self.o_proj(o.reshape(T, Hq * hd))
+        o = o.reshape(T, Hq * hd)
+        if Tp != T:
+            o = torch.cat([o, o.new_zeros(Tp - T, o.shape[1])], dim=0)
+        return self.o_proj(o)
 
 
 class GatedMLP(nn.Module):

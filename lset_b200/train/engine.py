@@ -176,9 +176,13 @@ class TrainingEngine:
         if tp_size > 1:
             from ..dist.tp import apply_tp
 
+            # async_tp: token-sharded residual stream with the all-gather / reduce-scatter fused
+            # into the projection GEMMs over peer memory (decoder families, no LoRA adapters);
+            # otherwise the Megatron all-reduce scheme.
+            sp = bool(async_tp) and not self.use_lora and hasattr(model, "_sp")
             apply_tp(model, self.tp_group, spec.tp_plan_fn(
-                model_config, use_sequence_parallel=False, use_lora=self.use_lora,
-                fused_projections=fused_projections))
+                model_config, use_sequence_parallel=sp, use_lora=self.use_lora,
+                fused_projections=fused_projections), sequence_parallel=sp)
         if activation_checkpoint:
             from ..dist.activation_checkpoint import apply_activation_checkpointing
 

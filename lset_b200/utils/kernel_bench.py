@@ -8,8 +8,9 @@ captures under ``profiles/`` are taken from).
     python -m lset_b200.utils.kernel_bench glu   --rows 23040 --i 3072 [--bwd]
     python -m lset_b200.utils.kernel_bench loss  --q 8192 --k 8192 --d 1024
 
-Timing: CUDA events on the launching stream, 3 warm-up launches, a 256 MB buffer rewritten between
-timed launches (larger than the 126 MB L2). One JSON line per run.
+Timing: CUDA events on the launching stream, 3 warm-up launches, a 256 MB buffer rewritten and then
+read between timed launches (larger than the 126 MB L2; the read leaves no dirty lines whose
+write-back would be charged to the timed kernel). One JSON line per run.
 """
 from __future__ import annotations
 
@@ -28,7 +29,9 @@ def _time(fn, iters: int) -> float:
     torch.cuda.synchronize()
     total = 0.0
     for _ in range(iters):
-        flush.add_(1.0)
+        for _ in range(4):   # also gives the host time to enqueue fn() behind the flush
+            flush.add_(1.0)
+        flush.sum()   # the read pass pushes the dirty lines of the write pass out of L2
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()

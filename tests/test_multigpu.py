@@ -55,3 +55,23 @@ def test_cross_rank_infonce_matches_gather_path(tmp_path):
     for case in r["cases"]:
         assert case["loss_err"] < 2e-2, case
         assert case["dq_err"] < 3e-2 and case["dk_err"] < 3e-2, case
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_sequence_parallel_tp(tmp_path):
+    """All-gather fused into the GEMM, reduce-scatter fused into its epilogue, and a
+    sequence-parallel decoder built on both, against plain PyTorch."""
+    out = tmp_path / "tp.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29651",
+           os.path.join(HERE, "mgpu_tp_worker.py"), str(out)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    r = json.loads(out.read_text())
+    assert r["fused"] and r["model"]["sp_fused"], "peer-memory path not active on this box"
+    for case in r["cases"]:
+        for k in ("y", "dx", "dw", "db"):
+            if k in case:
+                assert case[k] < 2e-2, case
+    assert r["model"]["hidden"] < 5e-2 and r["model"]["down_proj_grad"] < 5e-2, r["model"]

@@ -27,7 +27,7 @@ def _port():
     return p
 
 
-def _worker(rank, world, port, out_dir, fused):
+def _worker(rank, world, port, out_dir, fused, sp=False):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -37,7 +37,8 @@ def _worker(rank, world, port, out_dir, fused):
     m = Qwen3Decoder(_cfg(), fused_projections=fused)
     init_normal_(m, 0.05)
     full = {k: v.clone() for k, v in m.state_dict().items()}
-    apply_tp(m, dist.group.WORLD, decoder_tp_plan(_cfg(), fused_projections=fused))
+    apply_tp(m, dist.group.WORLD, decoder_tp_plan(_cfg(), fused_projections=fused,
+                                                  use_sequence_parallel=sp))
     # data-parallel world of one per rank: the store only has to sum the partial gradients of the
     # per-head norm weights over the tensor-parallel group
     from lset_b200.dist.sharded import ParamStore
@@ -45,7 +46,7 @@ def _worker(rank, world, port, out_dir, fused):
     dp_groups = [dist.new_group([r]) for r in range(world)]
     store = ParamStore(m, dp_group=dp_groups[rank], compute_dtype=torch.float32,
                        device=torch.device("cpu"), tp_group=dist.group.WORLD)
-    ids = torch.arange(14).reshape(2, 7) % 200
+    ids = _ids(sp)
     out = m(ids)["hidden_states"]
     out.pow(2).sum().backward()
     store.finish_backward()
@@ -53,21 +54,29 @@ def _worker(rank, world, port, out_dir, fused):
     g = params["layers.0.mlp.down_proj.weight"].main_grad.clone()
     gq = params["layers.0.self_attn.q_norm.weight"].main_grad.clone()
     gk = params["layers.1.self_attn.k_norm.weight"].main_grad.clone()
+    gn = params["layers.1.input_layernorm.weight"].main_grad.clone()
+    ge = params["embed_tokens.weight"].main_grad.clone()
     if rank == 0:
-        torch.save({"out": out.detach(), "grad": g, "gq": gq, "gk": gk, "full": full},
+        torch.save({"out": out.detach(), "grad": g, "gq": gq, "gk": gk, "gn": gn, "ge": ge,
+                    "full": full},
                    os.path.join(out_dir, "tp.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_tp_matches_unsharded(fused):
+def _ids(sp):
+    # 15 tokens under sequence parallelism: not a multiple of the group size, so padding is covered
+    return (torch.arange(15).reshape(3, 5) if sp else torch.arange(14).reshape(2, 7)) % 200
+
+
+@pytest.mark.parametrize("fused,sp", [(False, False), (True, False), (False, True), (True, True)])
+def test_tp_matches_unsharded(fused, sp):
     out_dir = tempfile.mkdtemp()
-    mp.spawn(_worker, args=(2, _port(), out_dir, fused), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _port(), out_dir, fused, sp), nprocs=2, join=True)
     got = torch.load(os.path.join(out_dir, "tp.pt"), weights_only=False)
     ref = Qwen3Decoder(_cfg(), fused_projections=fused)
     ref.load_state_dict(got["full"])
-    ids = torch.arange(14).reshape(2, 7) % 200
+    ids = _ids(sp)
     out = ref(ids)["hidden_states"]
     out.pow(2).sum().backward()
     assert torch.allclose(out, got["out"], atol=1e-5), (out - got["out"]).abs().max()
@@ -76,6 +85,9 @@ def test_tp_matches_unsharded(fused):
     # per-head norm weights: each rank sees only its heads, the store sums the partial gradients
     assert torch.allclose(ref.layers[0].self_attn.q_norm.weight.grad, got["gq"], atol=1e-4)
     assert torch.allclose(ref.layers[1].self_attn.k_norm.weight.grad, got["gk"], atol=1e-4)
+    # token-sharded norms (sequence parallelism) and the embedding see the full gradient too
+    assert torch.allclose(ref.layers[1].input_layernorm.weight.grad, got["gn"], atol=1e-4)
+    assert torch.allclose(ref.embed_tokens.weight.grad, got["ge"], atol=1e-4)
 
 
 def test_plans():
