@@ -49,6 +49,21 @@ struct GemmArgs {
   float* pos;                 // [M] score of the target column (EPI_LSE output)
   const float* coef;          // device scalar multiplied into the probabilities' gradient
   long long target_offset;    // target column of row r is r + target_offset
+  // label-matrix losses (labels != nullptr): int8 labels [M, ld_labels] (1 positive, 0 negative,
+  // < 0 ignored; ld_labels a multiple of 32 and >= N, padding = ignored), optional target weights
+  // tw [M, ld_tw] fp32 (soft labels; zero where ignored), row_scale [M] (1 / number of positives,
+  // or 1 / sum of the target weights) and row_w [M] (weight of the row in the mean; 0 = skipped).
+  const signed char* labels;
+  long long ld_labels;
+  const float* tw;
+  long long ld_tw;
+  const float* row_scale;
+  const float* row_w;
+  // 0: LSE over label >= 0, target t = tw or max(label, 0) (weighted cross-entropy family);
+  // 1: multi-positive NCE: LSE over label == 0 only; the gradient of a positive is
+  //    sigmoid(s - lse) - 1, of a negative exp(s - lse) * row_scale (row_scale = sum over the
+  //    row's positives of sigmoid(lse - s_p)).
+  int loss_mode;
   // ---- peer gather (GATHER 1: rows of B, GATHER 2: rows of A): the rows live in `world` ranks'
   // buffers, n_local rows each; two extra warps pull them into b_local ([world * n_local, K], the
   // base of that operand's tensor map) and publish one flag per (rank, row tile); tiles are
@@ -76,7 +91,12 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // per epilogue warp: a 32 x 32 fp32 block (row stride 33 words, conflict-free both ways) that
+  // turns "one row per lane" into "one 128-byte row segment per 8 lanes" for the fp32 reductions
+  static constexpr int EPI_STAGE_WORDS = 32 * 33;
+  static constexpr int EPI_STAGE_BYTES = 4 * EPI_STAGE_WORDS * 4;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -108,6 +128,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   uint64_t* tfull = empty + C::STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  [[maybe_unused]] float* epi_stage =
+      reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -136,6 +158,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
 
   // GATHER 1: rows of B come from the peers; GATHER 2: rows of A do. n_local = rows per rank.
   constexpr int kGatherRows = GATHER == 2 ? BM : BN;
+  constexpr int kPullRows = 16;  // rows per pull item (one warp); divides BM and BN
   [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 0;
   const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
   const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
@@ -162,6 +185,15 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     }
   };
 
+  // The rows of a chunk (one row tile of one rank) are pulled as items of kPullRows rows by
+  // different warps; flags[chunk] counts completed items and only ever grows: after the call with
+  // epoch e it holds e * items_of_chunk(chunk).
+  [[maybe_unused]] auto items_of_chunk = [&](int chunk) {
+    const int t = chunk % tiles_per_peer;
+    const int rows = min(kGatherRows, g.n_local - t * kGatherRows);
+    return (rows + kPullRows - 1) / kPullRows;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -180,7 +212,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           for (unsigned it2 = 0;; ++it2) {
             unsigned v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(g.flags + chunk) : "memory");
-            if (v == g.epoch) {
+            if (v >= g.epoch * unsigned(items_of_chunk(chunk))) {
               landed = true;
               break;
             }
@@ -280,45 +312,51 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   } else if (GATHER && warp >= 6) {
     // ------------------------------------------------------------------ pull warps (6, 7)
     if constexpr (GATHER) {
-      const int chunks = g.world * tiles_per_peer;
-      const long long row_bytes = 2LL * g.K;
+      constexpr int kItemsPerTile = kGatherRows / kPullRows;
+      const int items_total = g.world * tiles_per_peer * kItemsPerTile;
+      const long long vec_per_row = (2LL * g.K) / 16;
       for (;;) {
         unsigned c = 0;
         if (lane == 0) c = atomicAdd(g.chunk_counter, 1u);
         c = __shfl_sync(0xffffffffu, c, 0);
-        if (c >= unsigned(chunks)) break;
-        const int peer = (g.rank + int(c) / tiles_per_peer) % g.world;
-        const int t = int(c) % tiles_per_peer;
-        const int r0 = t * kGatherRows;
-        const int r1 = peer == g.rank ? r0 : min(r0 + kGatherRows, g.n_local);  // own rows are in place
-        const char* src = static_cast<const char*>(g.b_peers[peer]);
-        char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
-        const long long vec_per_row = row_bytes / 16;
-        const long long total_vec = vec_per_row * (r1 - r0);
-        for (long long i0 = 0; i0 < total_vec; i0 += 32 * 8) {
-          uint4 buf[8];
+        if (c >= unsigned(items_total)) break;
+        const int tile_i = int(c) / kItemsPerTile;      // tiles in consumption order
+        const int sub = int(c) % kItemsPerTile;
+        const int peer = (g.rank + tile_i / tiles_per_peer) % g.world;
+        const int t = tile_i % tiles_per_peer;
+        const int r0 = t * kGatherRows + sub * kPullRows;
+        const int tile_end = min((t + 1) * kGatherRows, g.n_local);
+        if (r0 >= tile_end) continue;                   // short last tile: no such item
+        const int r1 = min(r0 + kPullRows, tile_end);
+        if (peer != g.rank) {                           // own rows are in place already
+          const char* src = static_cast<const char*>(g.b_peers[peer]);
+          char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
+          const long long total_vec = vec_per_row * (r1 - r0);
+          for (long long i0 = 0; i0 < total_vec; i0 += 32 * 8) {
+            uint4 buf[8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const long long i = i0 + u * 32 + lane;
-            if (i < total_vec) {
-              const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
-              buf[u] = *reinterpret_cast<const uint4*>(src + 2LL * rr * g.ldb_peer + cc * 16);
+            for (int u = 0; u < 8; ++u) {
+              const long long i = i0 + u * 32 + lane;
+              if (i < total_vec) {
+                const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+                buf[u] = *reinterpret_cast<const uint4*>(src + 2LL * rr * g.ldb_peer + cc * 16);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const long long i = i0 + u * 32 + lane;
+              if (i < total_vec) {
+                const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+                *reinterpret_cast<uint4*>(dst + 2LL * rr * g.ldb_peer + cc * 16) = buf[u];
+              }
             }
           }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const long long i = i0 + u * 32 + lane;
-            if (i < total_vec) {
-              const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
-              *reinterpret_cast<uint4*>(dst + 2LL * rr * g.ldb_peer + cc * 16) = buf[u];
-            }
-          }
+          __threadfence();
         }
-        __threadfence();
         __syncwarp();
         if (lane == 0) {
-          const unsigned* fp = g.flags + (peer * tiles_per_peer + t);
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(fp), "r"(g.epoch) : "memory");
+          unsigned* fp = g.flags + (peer * tiles_per_peer + t);
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(fp) : "memory");
         }
       }
     }
@@ -348,9 +386,15 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       [[maybe_unused]] const long long target = row + g.target_offset;
       [[maybe_unused]] const float s2 = g.scale * kLog2e;
       [[maybe_unused]] float lse2 = 0.f, cf = 0.f;
+      [[maybe_unused]] const bool lbl = g.labels != nullptr;
+      [[maybe_unused]] float rscale = 0.f;
       if constexpr (EPI == EPI_PGRAD) {
         lse2 = (row < m_limit) ? g.lse[row] * kLog2e : 0.f;
         cf = g.coef != nullptr ? g.coef[0] : 1.f;
+        if (lbl && row < m_limit) {
+          cf *= g.row_w[row];
+          rscale = g.row_scale[row];
+        }
       }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -362,30 +406,81 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          [[maybe_unused]] uint32_t lab[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+          if constexpr (EPI != EPI_STORE) {
+            if (lbl) {
+              const uint4* lp = reinterpret_cast<const uint4*>(
+                  g.labels + static_cast<long long>(row) * g.ld_labels + col0);
+              const uint4 l0 = lp[0], l1 = lp[1];
+              lab[0] = l0.x; lab[1] = l0.y; lab[2] = l0.z; lab[3] = l0.w;
+              lab[4] = l1.x; lab[5] = l1.y; lab[6] = l1.z; lab[7] = l1.w;
+            }
+          }
+          // label of column j of this chunk, sign-extended
+          [[maybe_unused]] auto label_at = [&](int j) {
+            return static_cast<int>(static_cast<signed char>((lab[j >> 2] >> ((j & 3) * 8)) & 0xffu));
+          };
           if constexpr (EPI == EPI_LSE) {
             float cm = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const bool in = col0 + j < n_limit;
-              if (in && col0 + j == target) {
-                pos_val = v[j] * g.scale;
-                pos_here = true;
-              }
-              v[j] = in ? v[j] * s2 : -INFINITY;
-              cm = fmaxf(cm, v[j]);
-            }
-            const float m_new = fmaxf(m_run, cm);
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) sum += exp2f(v[j] - m_new);
-            l_run = l_run * exp2f(m_run - m_new) + sum;
-            m_run = m_new;
-          } else {
-            if constexpr (EPI == EPI_PGRAD) {
+            if (lbl) {
+              const float* twp =
+                  g.tw != nullptr ? g.tw + static_cast<long long>(row) * g.ld_tw + col0 : nullptr;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
-                const float p = exp2f(v[j] * s2 - lse2);
-                v[j] = (p - ((col0 + j == target) ? 1.f : 0.f)) * cf;
+                const int l = label_at(j);
+                const bool in = (col0 + j < n_limit) && (g.loss_mode == 1 ? l == 0 : l >= 0);
+                if (in) {
+                  if (twp != nullptr) pos_val += twp[j] * v[j] * g.scale;
+                  else if (l > 0) pos_val += float(l) * v[j] * g.scale;
+                }
+                v[j] = in ? v[j] * s2 : -INFINITY;
+                cm = fmaxf(cm, v[j]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const bool in = col0 + j < n_limit;
+                if (in && col0 + j == target) {
+                  pos_val = v[j] * g.scale;
+                  pos_here = true;
+                }
+                v[j] = in ? v[j] * s2 : -INFINITY;
+                cm = fmaxf(cm, v[j]);
+              }
+            }
+            const float m_new = fmaxf(m_run, cm);
+            if (m_new > -INFINITY) {  // a chunk of ignored columns leaves the running pair alone
+              float sum = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) sum += exp2f(v[j] - m_new);
+              l_run = l_run * exp2f(m_run - m_new) + sum;
+              m_run = m_new;
+            }
+          } else {
+            if constexpr (EPI == EPI_PGRAD) {
+              if (lbl) {
+                const float* twp =
+                    g.tw != nullptr ? g.tw + static_cast<long long>(row) * g.ld_tw + col0 : nullptr;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int l = label_at(j);
+                  const bool in = (col0 + j < g.N) && l >= 0;
+                  const float e = in ? exp2f(v[j] * s2 - lse2) : 0.f;  // exp(s - lse)
+                  if (g.loss_mode == 1) {
+                    // positives: sigmoid(s - lse) - 1 = -1 / (1 + e); negatives: e * row_scale
+                    v[j] = (!in || cf == 0.f) ? 0.f : (l > 0 ? -cf / (1.f + e) : e * rscale * cf);
+                  } else {
+                    const float t =
+                        !in ? 0.f : (twp != nullptr ? twp[j] * rscale : (l > 0 ? float(l) * rscale : 0.f));
+                    v[j] = cf == 0.f ? 0.f : (e - t) * cf;  // skipped rows: no inf * 0
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float p = exp2f(v[j] * s2 - lse2);
+                  v[j] = (p - ((col0 + j == target) ? 1.f : 0.f)) * cf;
+                }
               }
             }
             if (add_bias) {
@@ -407,10 +502,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
             } else {
               float* fd = reinterpret_cast<float*>(dst);
               if (g.accumulate) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (col0 + 4 * j < g.N)
-                    red_add4(fd + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                // handled below by the whole warp (row-coalesced reductions)
               } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
@@ -421,6 +513,41 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
             }
           }
         }
+        if constexpr (sizeof(OutT) == 4 && EPI == EPI_STORE) {
+          if (g.accumulate && col0 < g.N) {
+            // Transpose through shared memory: lane = row on the way in, 8 lanes = one 128-byte
+            // row segment on the way out, so every reduction instruction covers 4 full lines
+            // (local L2 atomics and, for peer-owned rows, NVLink reductions both want whole lines).
+            float* st = epi_stage + (warp - 2) * C::EPI_STAGE_WORDS;
+            const bool add_b = add_bias;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __uint_as_float(r[j]);
+              if (add_b && col0 + j < g.N) x += __bfloat162float(g.bias[col0 + j]);
+              st[lane * 33 + j] = x;
+            }
+            __syncwarp();
+            const int rr = lane >> 3, cc = (lane & 7) * 4;
+            if (col0 + cc < g.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int lr = i * 4 + rr;
+                const int grow = m0 + q * 32 + lr;
+                if (grow < m_limit) {
+                  const float* sp = st + lr * 33 + cc;
+                  float* base;
+                  if (g.c_rows_per_peer > 0)
+                    base = reinterpret_cast<float*>(g.c_peers[grow / g.c_rows_per_peer]) +
+                           static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
+                  else
+                    base = reinterpret_cast<float*>(g.C) + static_cast<long long>(grow) * g.ldc;
+                  red_add4(base + col0 + cc, sp[0], sp[1], sp[2], sp[3]);
+                }
+              }
+            }
+            __syncwarp();
+          }
+        }
       }
       if constexpr (EPI == EPI_LSE) {
         if (row < m_limit) {
@@ -428,7 +555,11 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           float* pp = g.part + (static_cast<long long>(part_idx) * g.M + row) * 2;
           pp[0] = m_run;
           pp[1] = l_run;
-          if (pos_here) g.pos[row] = pos_val;
+          if (lbl) {
+            if (pos_val != 0.f) atomicAdd(&g.pos[row], pos_val);  // several column tiles add up
+          } else if (pos_here) {
+            g.pos[row] = pos_val;
+          }
         }
       }
       tc_fence_before();
@@ -626,6 +757,40 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Label-matrix variant: per_q = lse − row_scale · pos; loss_sum += sum_r row_w[r] · per_q. Rows
+// without a valid column get lse = 0 (their row_w is 0).
+__global__ void __launch_bounds__(256)
+    lse_merge_label_kernel(const float* __restrict__ part, int tiles_n, int M,
+                           const float* __restrict__ pos, const float* __restrict__ row_scale,
+                           const float* __restrict__ row_w, float* __restrict__ lse,
+                           float* __restrict__ loss_sum) {
+  __shared__ float sred[8];
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  float contrib = 0.f;
+  if (r < M) {
+    float m = -INFINITY, l = 0.f;
+    for (int t = 0; t < tiles_n; ++t) {
+      const float mt = part[(1LL * t * M + r) * 2], lt = part[(1LL * t * M + r) * 2 + 1];
+      const float mn = fmaxf(m, mt);
+      if (mn > -INFINITY) l = l * exp2f(m - mn) + lt * exp2f(mt - mn);
+      m = mn;
+    }
+    const float v = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : 0.f;
+    lse[r] = v;
+    const float w = row_w[r];
+    if (w != 0.f) contrib = w * (v - row_scale[r] * pos[r]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
+  if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = contrib;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < 8; ++i) s += sred[i];
+    atomicAdd(loss_sum, s);
+  }
+}
+
 int loss_tile_bn(int M, int N) {
   (void)M;
   return N > 128 ? 256 : 128;
@@ -714,14 +879,92 @@ extern "C" int lb_infonce_pgrad(const void* q, long long ldq, const void* k, lon
                    : launch<0, 0, 128, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream);
 }
 
+// Label-matrix contrastive loss (multi-positive NCE and soft-label cross-entropy) on the same
+// streaming kernels: loss_sum += sum_r row_w[r] · (LSE_{valid c} s_rc − row_scale[r] · sum_c t_rc s_rc)
+// with t = max(label, 0) (tw == nullptr) or t = tw. labels: int8 [M, ld_labels], ld_labels % 32 == 0,
+// >= N, padded with a negative value; tw: fp32 [M, ld_tw] or nullptr, same padding rule (zeros).
+// loss_mode 1 (multi-positive NCE): lse[r] is the LSE over the negatives (label == 0) only and
+// loss_sum is not meaningful; the caller forms the loss from lse and the positives' scores.
+// scratch: lb_infonce_scratch_floats(M, N) floats.
+extern "C" int lb_label_loss_fwd(const void* q, long long ldq, const void* k, long long ldk, int M,
+                                 int N, int D, float inv_temperature, const void* labels,
+                                 long long ld_labels, const float* tw, long long ld_tw,
+                                 const float* row_scale, const float* row_w, int loss_mode,
+                                 float* scratch, float* lse, float* loss_sum, int* status,
+                                 void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (labels == nullptr || (ld_labels & 31) || ld_labels < N) return -3;
+  if (tw != nullptr && ((ld_tw & 31) || ld_tw < N)) return -3;
+  const int bn = loss_tile_bn(M, N);
+  CUtensorMap tmA, tmB;
+  GemmArgs g;
+  int grid;
+  if (int rc = prep_loss(q, k, M, N, D, ldq, ldk, bn, &tmA, &tmB, &g, &grid)) return rc;
+  const int tiles_n = (N + bn - 1) / bn;
+  g.scale = inv_temperature;
+  g.part = scratch;
+  g.pos = scratch + 2LL * tiles_n * M;
+  g.labels = static_cast<const signed char*>(labels);
+  g.ld_labels = ld_labels;
+  g.tw = tw;
+  g.ld_tw = ld_tw;
+  g.row_scale = row_scale;
+  g.row_w = row_w;
+  g.loss_mode = loss_mode;
+  g.status = status;
+  if (cudaMemsetAsync(g.pos, 0, sizeof(float) * M, stream) != cudaSuccess) return -12;
+  int rc = bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_LSE>(tmA, tmB, g, grid, stream)
+                     : launch<0, 0, 128, __nv_bfloat16, EPI_LSE>(tmA, tmB, g, grid, stream);
+  if (rc) return rc;
+  lse_merge_label_kernel<<<(M + 255) / 256, 256, 0, stream>>>(g.part, tiles_n, M, g.pos, row_scale,
+                                                             row_w, lse, loss_sum);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// W[r, c] = ([label_rc >= 0] · exp(s_rc − lse[r]) − row_scale[r] · t_rc) · row_w[r] · coef[0], bf16
+// (loss_mode 0); loss_mode 1: positives (sigmoid(s − lse) − 1) · row_w · coef, negatives
+// exp(s − lse) · row_scale · row_w · coef.
+extern "C" int lb_label_loss_pgrad(const void* q, long long ldq, const void* k, long long ldk, int M,
+                                   int N, int D, float inv_temperature, const void* labels,
+                                   long long ld_labels, const float* tw, long long ld_tw,
+                                   const float* row_scale, const float* row_w, int loss_mode,
+                                   const float* lse, const float* coef, void* W, long long ldw,
+                                   int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if ((N & 7) || (ldw & 7)) return -3;
+  if (labels == nullptr || (ld_labels & 31) || ld_labels < N) return -3;
+  if (tw != nullptr && ((ld_tw & 31) || ld_tw < N)) return -3;
+  const int bn = loss_tile_bn(M, N);
+  CUtensorMap tmA, tmB;
+  GemmArgs g;
+  int grid;
+  if (int rc = prep_loss(q, k, M, N, D, ldq, ldk, bn, &tmA, &tmB, &g, &grid)) return rc;
+  g.scale = inv_temperature;
+  g.lse = lse;
+  g.coef = coef;
+  g.C = W;
+  g.ldc = ldw;
+  g.labels = static_cast<const signed char*>(labels);
+  g.ld_labels = ld_labels;
+  g.tw = tw;
+  g.ld_tw = ld_tw;
+  g.row_scale = row_scale;
+  g.row_w = row_w;
+  g.loss_mode = loss_mode;
+  g.status = status;
+  return bn == 256 ? launch<0, 0, 256, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream)
+                   : launch<0, 0, 128, __nv_bfloat16, EPI_PGRAD>(tmA, tmB, g, grid, stream);
+}
 
 // Cross-rank InfoNCE forward: the passages of all `world` ranks (n_local rows each, in symmetric
 // buffers k_peers[r]) are pulled into k_all ([world * n_local, D], local) by two extra warps per
 // CTA while the tensor-core tiles consume them in pull order, own rank first. The caller orders
 // the launch after every rank has written its passages and keeps k_all for the backward.
-// flags: [world * ceil(n_local / 256)] zero-initialised once; counter: one u32; epoch: a value
-// that differs from every earlier call on these flags. part/lse layout as in lb_infonce_fwd with
-// tiles = world * ceil(n_local / 256).
+// flags: [world * ceil(n_local / 256)] zero-initialised once; counter: one u32; epoch: 1, 2, 3, …
+// on successive calls that use these flags (a flag counts the 16-row items pulled so far).
+// part/lse layout as in lb_infonce_fwd with tiles = world * ceil(n_local / 256).
 extern "C" long long lb_infonce_xrank_scratch_floats(int M, int n_local, int world) {
   return 2LL * world * ((n_local + 255) / 256) * M + M;
 }
@@ -771,8 +1014,8 @@ extern "C" int lb_infonce_fwd_xrank(const void* q, long long ldq, const void* co
 // pull the peers' rows into a_all (local, [world * rows_local, K]; the caller has already copied
 // its own slice there) while the tensor-core tiles consume them in pull order, own rank first.
 // a_all is complete when the kernel ends, so the backward can reuse it. b_mn as in lb_gemm_bf16.
-// flags: [world * ceil(rows_local / 128)] u32, zero-initialised once; epoch must differ from every
-// earlier call that used these flags.
+// flags: [world * ceil(rows_local / 128)] u32, zero-initialised once; epoch: 1, 2, 3, … on
+// successive calls that use these flags (a flag counts the 16-row items pulled so far).
 extern "C" int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const void* B, void* C,
                                int rows_local, int world, int rank, int N, int K, long long lda,
                                long long ldb, long long ldc, int b_mn, const void* bias,

@@ -69,6 +69,79 @@ __global__ void __launch_bounds__(kRowThreads)
   }
 }
 
+// Gemma's post-norm pair in one pass: z = bf16(bf16(a·rstd1)·w1); nr = bf16(residual + z);
+// y = bf16(nr·rstd2)·w2. The row stays in registers between the two norms; a, rstd1, nr and rstd2
+// are what the two backward launches need.
+template <int TPR, int NV>
+__global__ void __launch_bounds__(kRowThreads)
+    rms_double_fwd_kernel(const bf16* __restrict__ a, const bf16* __restrict__ res_in,
+                          const bf16* __restrict__ w1, const bf16* __restrict__ w2,
+                          bf16* __restrict__ y, bf16* __restrict__ res_out,
+                          float* __restrict__ rstd1_out, float* __restrict__ rstd2_out, int N, int H,
+                          float eps, float w_off) {
+  __shared__ float sred[8];
+  extern __shared__ float sw[];  // [H] first weights, [H] second weights (+ offset)
+  const int t = threadIdx.x % TPR;
+  const int r = threadIdx.x / TPR;
+  constexpr int ROWS = kRowThreads / TPR;
+  for (int i = threadIdx.x; i < H; i += kRowThreads) {
+    sw[i] = __bfloat162float(w1[i]) + w_off;
+    sw[H + i] = __bfloat162float(w2[i]) + w_off;
+  }
+  __syncthreads();
+  for (long long row0 = 1LL * blockIdx.x * ROWS; row0 < N; row0 += 1LL * gridDim.x * ROWS) {
+    const long long row = row0 + r;
+    const bool valid = row < N;
+    float xv[NV][8];
+    uint4 rq[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        unpack8(ld16(a + row * H + idx), xv[v]);
+        rq[v] = ld16(res_in + row * H + idx);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += xv[v][i] * xv[v][i];
+      }
+    }
+    ss = row_sum<TPR>(ss, sred);
+    const float rstd1 = rsqrtf(ss / float(H) + eps);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float rv[8];
+        unpack8(rq[v], rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float z = bf16_round(bf16_round(xv[v][i] * rstd1) * sw[idx + i]);
+          xv[v][i] = bf16_round(rv[i] + z);
+          ss2 += xv[v][i] * xv[v][i];
+        }
+        st16(res_out + row * H + idx, pack8(xv[v]));
+      }
+    }
+    ss2 = row_sum<TPR>(ss2, sred);
+    const float rstd2 = rsqrtf(ss2 / float(H) + eps);
+    if (valid && t == 0) {
+      rstd1_out[row] = rstd1;
+      rstd2_out[row] = rstd2;
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int idx = (v * TPR + t) * 8;
+      if (valid && idx < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = bf16_round(xv[v][i] * rstd2) * sw[H + idx + i];
+        st16(y + row * H + idx, pack8(o));
+      }
+    }
+  }
+}
+
 // Backward keeps x and dy as packed bf16 in registers (unpacked twice) and the weights in shared
 // memory, so that only the fp32 dW accumulators are long-lived: two CTAs fit per SM.
 template <int TPR, int NV>
@@ -377,6 +450,25 @@ extern "C" int lb_rms_norm_fwd(const void* x, const void* res_in, const void* w,
     rms_fwd_kernel<TPR, NV><<<grid, kRowThreads, H * sizeof(float), st>>>(
         (const bf16*)x, (const bf16*)res_in, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, N, H,
         eps, w_off);
+  });
+  return launch_rc();
+}
+
+// Fused forward of rmsnorm(a)·w1 → + residual → rmsnorm(·)·w2. Outputs y, res_out (the new
+// residual stream), rstd1 (of a) and rstd2 (of res_out).
+extern "C" int lb_rms_norm_double_fwd(const void* a, const void* res_in, const void* w1,
+                                      const void* w2, void* y, void* res_out, float* rstd1,
+                                      float* rstd2, int N, int H, float eps, float w_off,
+                                      void* stream) {
+  if (N <= 0) return 0;
+  if ((H & 7) || 2 * H * sizeof(float) > 48 * 1024) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  LB_ROW_DISPATCH(H, {
+    constexpr int ROWS = kRowThreads / TPR;
+    const int grid = (N + ROWS - 1) / ROWS;
+    rms_double_fwd_kernel<TPR, NV><<<grid, kRowThreads, 2 * H * sizeof(float), st>>>(
+        (const bf16*)a, (const bf16*)res_in, (const bf16*)w1, (const bf16*)w2, (bf16*)y,
+        (bf16*)res_out, rstd1, rstd2, N, H, eps, w_off);
   });
   return launch_rc();
 }

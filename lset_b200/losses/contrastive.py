@@ -2,15 +2,17 @@
 (semantics of lset/losses/contrastive.py:14-53). Labels: 1 = positive, 0 = negative, -1 = ignore.
 
 * multi-positive: ``mean_q( -mean_{p in pos(q)} sim[q,p] + logsumexp_{valid} sim[q,:] )``
-* soft labels (``scores`` given): targets are the row-normalised softmax of the teacher scores over
-  valid entries; loss is the cross-entropy against the log-softmax over valid entries.
-Queries without a positive (or without a valid column) are skipped; with none left the result is a
-zero that still carries gradient."""
+* soft labels (``scores`` given): targets are the teacher scores over the non-ignored columns,
+  normalised to sum to one; loss is ``logsumexp_{valid} sim[q,:] - sum_k target[q,k] sim[q,k]``.
+Queries without a positive (resp. with a zero score sum) or without a valid column are skipped;
+with none left the result is a zero that still carries gradient. bf16 CUDA inputs with a Python
+float temperature run on the streaming tensor-core kernels (``ops.loss.fused_label_loss``), which
+never materialise the score matrix."""
 from __future__ import annotations
 
 import torch
 
-from ..ops.loss import similarity
+from ..ops.loss import fused_label_loss, fused_label_loss_supported, similarity
 
 
 def _zero_with_grad(*tensors):
@@ -18,20 +20,23 @@ def _zero_with_grad(*tensors):
 
 
 def contrastive_loss(query_embeds, doc_embeds, labels, temperature=0.02, scores=None, scale=None):
+    if (scale is None and isinstance(temperature, (int, float))
+            and fused_label_loss_supported(query_embeds, doc_embeds)):
+        return fused_label_loss(query_embeds, doc_embeds, labels, float(temperature), scores)
     s = (1.0 / temperature) if scale is None else scale
     sim = similarity(query_embeds, doc_embeds) * s
     labels = labels.to(sim.device)
     valid = labels >= 0
     masked = sim.masked_fill(~valid, float("-inf"))
     if scores is not None:
-        sc = scores.to(sim.device).float().masked_fill(~valid, float("-inf"))
-        keep = valid.any(dim=1)
+        target = scores.to(sim.device).float().masked_fill(~valid, 0.0)
+        tsum = target.sum(dim=1)
+        keep = (tsum > 0) & valid.any(dim=1)
         if not keep.any():
             return _zero_with_grad(query_embeds, doc_embeds)
-        target = torch.softmax(sc[keep], dim=1)
-        logp = torch.log_softmax(masked[keep], dim=1)
-        per_q = -(target * logp.masked_fill(~valid[keep], 0.0)).sum(dim=1)
-        return per_q.mean()
+        target = target / tsum.clamp(min=1e-12).unsqueeze(1)
+        per_q = torch.logsumexp(masked, dim=1) - (target * sim).sum(dim=1)
+        return per_q[keep].mean()
     pos = labels > 0
     n_pos = pos.sum(dim=1)
     keep = n_pos > 0

@@ -114,38 +114,80 @@ class _RmsNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dres):
         xin, w, rstd = ctx.saved_tensors
-        N, H = xin.shape
-        dy2 = dy.reshape(N, H)
-        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
-        dr2 = None
-        if dres is not None and ctx.has_res:
-            dr2 = dres.reshape(N, H)
-            dr2 = dr2 if dr2.is_contiguous() else dr2.contiguous()
-        dx = torch.empty_like(xin)
-        lib = nv.load()
-        rows = lib.lb_norm_bwd_partial_rows()
-        scr = scratch("norm_bwd", rows * H, xin.device)
-        need_dw = ctx.needs_input_grad[2]
-
-        def call(out_ptr, out_fp32, accumulate):
-            rc = lib.lb_rms_norm_bwd(
-                nv.c_void_p(dy2.data_ptr()), nv.c_void_p(nv.ptr(dr2)), nv.c_void_p(xin.data_ptr()),
-                nv.c_void_p(w.data_ptr()), nv.c_void_p(rstd.data_ptr()), nv.c_void_p(dx.data_ptr()),
-                nv.c_void_p(scr.data_ptr()), nv.c_void_p(out_ptr), nv.c_int(out_fp32),
-                nv.c_int(accumulate), nv.c_int(N), nv.c_int(H), nv.c_float(ctx.w_off),
-                nv.c_void_p(nv.stream_ptr()))
-            nv.check_rc(rc, "lb_rms_norm_bwd")
-            nv.count_launch(2 if out_ptr else 1)
-
-        dw = None
-        if need_dw:
-            dw = deliver_wgrad(w, H, xin.device, call)
-            if dw is not None:
-                dw = dw.to(w.dtype)
-        else:
-            call(0, 1, 0)
+        dx, dw = _rms_bwd(dy, dres if ctx.has_res else None, xin, w, rstd, ctx.w_off,
+                          ctx.needs_input_grad[2])
         dxv = dx.view(ctx.shape)
         return dxv, (dxv if ctx.has_res else None), dw, None, None
+
+
+def _rms_bwd(dy, dres, xin, w, rstd, w_off, need_dw):
+    """One RMSNorm backward launch: ``dx`` (plus ``dres`` when given) and the weight gradient,
+    which lands in ``w.main_grad`` when the sharding runtime provides one (then ``dw`` is None)."""
+    N, H = xin.shape
+    dy2 = dy.reshape(N, H)
+    dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+    dr2 = None
+    if dres is not None:
+        dr2 = dres.reshape(N, H)
+        dr2 = dr2 if dr2.is_contiguous() else dr2.contiguous()
+    dx = torch.empty_like(xin)
+    lib = nv.load()
+    rows = lib.lb_norm_bwd_partial_rows()
+    scr = scratch("norm_bwd", rows * H, xin.device)
+
+    def call(out_ptr, out_fp32, accumulate):
+        rc = lib.lb_rms_norm_bwd(
+            nv.c_void_p(dy2.data_ptr()), nv.c_void_p(nv.ptr(dr2)), nv.c_void_p(xin.data_ptr()),
+            nv.c_void_p(w.data_ptr()), nv.c_void_p(rstd.data_ptr()), nv.c_void_p(dx.data_ptr()),
+            nv.c_void_p(scr.data_ptr()), nv.c_void_p(out_ptr), nv.c_int(out_fp32),
+            nv.c_int(accumulate), nv.c_int(N), nv.c_int(H), nv.c_float(w_off),
+            nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_rms_norm_bwd")
+        nv.count_launch(2 if out_ptr else 1)
+
+    dw = None
+    if need_dw:
+        dw = deliver_wgrad(w, H, xin.device, call)
+        if dw is not None:
+            dw = dw.to(w.dtype)
+    else:
+        call(0, 1, 0)
+    return dx, dw
+
+
+class _RmsNormDouble(torch.autograd.Function):
+    """``z = rmsnorm(a)·w1; nr = residual + z; y = rmsnorm(nr)·w2`` in one forward launch; the
+    backward is the two single-norm launches."""
+
+    @staticmethod
+    def forward(ctx, residual, a, w1, w2, eps, w_off):
+        shape = a.shape
+        H = shape[-1]
+        a2 = a.reshape(-1, H)
+        a2 = a2 if a2.is_contiguous() else a2.contiguous()
+        r2 = residual.reshape(-1, H)
+        r2 = r2 if r2.is_contiguous() else r2.contiguous()
+        N = a2.shape[0]
+        y, nr = torch.empty_like(a2), torch.empty_like(a2)
+        rstd1 = torch.empty(N, dtype=torch.float32, device=a.device)
+        rstd2 = torch.empty(N, dtype=torch.float32, device=a.device)
+        rc = nv.load().lb_rms_norm_double_fwd(
+            nv.c_void_p(a2.data_ptr()), nv.c_void_p(r2.data_ptr()), nv.c_void_p(w1.data_ptr()),
+            nv.c_void_p(w2.data_ptr()), nv.c_void_p(y.data_ptr()), nv.c_void_p(nr.data_ptr()),
+            nv.c_void_p(rstd1.data_ptr()), nv.c_void_p(rstd2.data_ptr()), nv.c_int(N), nv.c_int(H),
+            nv.c_float(eps), nv.c_float(w_off), nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_rms_norm_double_fwd")
+        nv.count_launch()
+        ctx.save_for_backward(a2, nr, w1, w2, rstd1, rstd2)
+        ctx.w_off, ctx.shape = w_off, shape
+        return y.view(shape), nr.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy, dnr):
+        a2, nr, w1, w2, rstd1, rstd2 = ctx.saved_tensors
+        d_nr, dw2 = _rms_bwd(dy, dnr, nr, w2, rstd2, ctx.w_off, ctx.needs_input_grad[3])
+        d_a, dw1 = _rms_bwd(d_nr, None, a2, w1, rstd1, ctx.w_off, ctx.needs_input_grad[2])
+        return d_nr.view(ctx.shape), d_a.view(ctx.shape), dw1, dw2, None, None
 
 
 def rms_norm(x, w, eps=1e-6, w_off=0.0):
@@ -164,11 +206,14 @@ def residual_rms_norm(residual, x, w, eps=1e-6, w_off=0.0):
 
 def double_residual_rms_norm(residual, a, w1, w2, eps=1e-6, w_off=0.0):
     """Gemma post-norm pair: ``z = rmsnorm(a)·w1; nr = residual + z; out = rmsnorm(nr)·w2``;
-    returns ``(out, nr)``. Runs as two native launches (norm, then residual-add + norm)."""
+    returns ``(out, nr)``. One forward launch (the row never leaves the registers between the two
+    norms); rows wider than 6144 take the two-launch route."""
     if not (_native_ok(residual, a, w1, w2) and enabled("fused_double_rmsnorm")):
         return double_residual_rms_norm_ref(residual, a, w1, w2, eps, w_off)
-    z = rms_norm(a, w1, eps, w_off)
-    return residual_rms_norm(residual, z, w2, eps, w_off)
+    if a.shape[-1] * 8 > 48 * 1024:
+        z = rms_norm(a, w1, eps, w_off)
+        return residual_rms_norm(residual, z, w2, eps, w_off)
+    return _RmsNormDouble.apply(residual, a, w1, w2, eps, w_off)
 
 
 # --------------------------------------------------------------------------- LayerNorm

@@ -24,6 +24,7 @@ import torch.nn as nn
 from ..dist.gather import gather_for_local_rows
 from ..losses.base import LogitScale
 from ..losses.contrastive import contrastive_loss
+from ..losses.fused_contrastive import fused_contrastive_loss
 from ..losses.infonce import infonce_loss
 from ..losses.matryoshka import matryoshka_loss
 from ..ops.pooling import packed_pool, pool
@@ -96,7 +97,8 @@ class BiEncoderTask(nn.Module):
             return 1.0 / self.logit_scale()
         return self.temperature
 
-    def loss_from_embeddings(self, q_emb, d_emb, n_emb=None, labels=None, scores=None):
+    def loss_from_embeddings(self, q_emb, d_emb, n_emb=None, labels=None, scores=None,
+                             pos_qi=None, pos_di=None, pos_counts=None):
         """Loss for local query rows against globally gathered documents (+ negatives).
         Returns the rank's share of the global mean (the shares sum to the global loss)."""
         W, rank = self._dp()
@@ -131,6 +133,18 @@ class BiEncoderTask(nn.Module):
                 labels_full, s_full = labels, (scores.to(q_emb.device) if scores is not None else None)
             if self.matryoshka_dims:
                 local = matryoshka_loss(q_emb, docs, self.matryoshka_dims, temperature, labels_full)
+            elif isinstance(temperature, (int, float)):
+                pdi = None
+                if pos_qi is not None and pos_di is not None:
+                    # local document indices -> columns of the gathered [docs | negatives] matrix
+                    pdi = pos_di.to(q_emb.device).long()
+                    if W > 1:
+                        Bn = n_emb.shape[0] if n_emb is not None else 0
+                        pdi = torch.where(pdi < Bd, pdi + rank * Bd, pdi - Bd + W * Bd + rank * Bn)
+                local = fused_contrastive_loss(
+                    q_emb, docs, labels_full, temperature, s_full,
+                    pos_qi=pos_qi.to(q_emb.device) if pos_qi is not None and pdi is not None else None,
+                    pos_di=pdi, pos_counts=pos_counts, num_queries=W * Bq)
             else:
                 local = contrastive_loss(q_emb, docs, labels_full, temperature, s_full)
             return local / W if W > 1 else local
@@ -147,7 +161,8 @@ class BiEncoderTask(nn.Module):
         embs = self.encode_many(model, [query_batch, doc_batch, neg_batch])
         q_emb, d_emb = embs[0], embs[1]
         n_emb = embs[2] if len(embs) > 2 else None
-        loss = self.loss_from_embeddings(q_emb, d_emb, n_emb, labels, scores)
+        loss = self.loss_from_embeddings(q_emb, d_emb, n_emb, labels, scores, pos_qi, pos_di,
+                                         pos_counts)
         return {"loss": loss, "query_embeds": q_emb.detach(), "doc_embeds": d_emb.detach()}
 
 

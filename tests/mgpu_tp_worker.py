@@ -13,6 +13,8 @@ import sys
 import torch
 import torch.distributed as dist
 
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 
 def rel(a, b):
     return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
@@ -102,11 +104,32 @@ def main():
         h = model.forward_packed(ids, pos, cu, max(lens))["hidden_states"]
         h.float().pow(2).mean().backward()
         outs.append(h.detach())
-    g_ref = ref.layers[0].mlp.down_proj.weight.grad
-    g_tp = m.layers[0].mlp.down_proj.weight.grad
-    per = g_ref.shape[1] // world
-    res["model"] = {"hidden": rel(outs[1], outs[0]),
-                    "down_proj_grad": rel(g_tp, g_ref[:, rank * per:(rank + 1) * per]),
+    # every parameter gradient of the sharded model against the matching slice of the reference
+    from lset_b200.dist.tp import _section_sizes, _shard_rows
+
+    ref_params = dict(ref.named_parameters())
+    grads = {}
+    for name, p in m.named_parameters():
+        g_ref = ref_params[name].grad
+        g_tp = p.grad
+        if g_tp is None or g_ref is None:
+            grads[name] = None
+            continue
+        if getattr(p, "_tp_sharded", False):
+            mod_name = name.rsplit(".", 1)[0]
+            mod = ref.get_submodule(mod_name)
+            owner = ref.get_submodule(mod_name.rsplit(".", 1)[0])
+            if g_tp.shape[0] != g_ref.shape[0]:      # column-parallel: rows sharded by section
+                g_ref = _shard_rows(g_ref, _section_sizes(mod_name, mod, owner), rank, world)
+            else:                                     # row-parallel: input features sharded
+                per = g_ref.shape[1] // world
+                g_ref = g_ref[:, rank * per:(rank + 1) * per]
+        elif getattr(p, "_tp_partial_grad", False):
+            g_tp = g_tp.float().clone()
+            dist.all_reduce(g_tp)                    # the sharding runtime sums these over the group
+        grads[name] = rel(g_tp, g_ref)
+    res["model"] = {"hidden": rel(outs[1], outs[0]), "grads": grads,
+                    "worst_grad": max(v for v in grads.values() if v is not None),
                     "sp_fused": bool(m._sp.fused)}
     nv.check_status()
     dist.barrier()

@@ -48,3 +48,122 @@ def test_no_score_matrix_in_fp32():
     fused_infonce(q, k, 0.02).backward()
     torch.cuda.synchronize()
     assert torch.cuda.max_memory_allocated() - base < M * N * 4  # below one fp32 score matrix
+
+
+def _eager_label_loss(q, k, labels, T, scores=None):
+    """fp32 oracle: the formulas of the label-matrix loss written out with plain torch ops."""
+    sim = q @ k.t() / T
+    valid = labels >= 0
+    lse = torch.logsumexp(sim.masked_fill(~valid, float("-inf")), dim=1)
+    if scores is None:
+        pos = (labels == 1).float()
+        n = pos.sum(1)
+        keep = (n > 0) & valid.any(1)
+        per_q = lse - (sim * pos).sum(1) / n.clamp(min=1)
+    else:
+        t = scores.masked_fill(~valid, 0.0)
+        ts = t.sum(1)
+        keep = (ts > 0) & valid.any(1)
+        per_q = lse - (t / ts.clamp(min=1e-12).unsqueeze(1) * sim).sum(1)
+    return per_q[keep].mean()
+
+
+@pytest.mark.parametrize("Q,K,D", [(64, 200, 256), (300, 1000, 1024), (128, 4096, 768), (40, 72, 128)])
+@pytest.mark.parametrize("soft", [False, True])
+def test_fused_label_loss_matches_eager(Q, K, D, soft):
+    from lset_b200.ops.loss import fused_label_loss
+
+    q, k = _emb(Q, D, 6).requires_grad_(), _emb(K, D, 7).requires_grad_()
+    g = torch.Generator(device="cuda").manual_seed(Q + K)
+    r = torch.rand(Q, K, device="cuda", generator=g)
+    labels = torch.zeros(Q, K, device="cuda")
+    labels[r < 0.02] = 1.0           # several positives per row
+    labels[r > 0.9] = -1.0           # ignored columns
+    labels[1] = 0.0                  # a query without positives is skipped
+    labels[2] = -1.0                 # a query without any valid column too
+    scores = torch.rand(Q, K, device="cuda", generator=g) * 4 if soft else None
+    if soft:
+        scores[3] = 0.0              # zero score sum: skipped
+    loss = fused_label_loss(q, k, labels, 0.05, scores)
+    loss.backward()
+    nv.check_status()
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    ref = _eager_label_loss(qr, kr, labels, 0.05, scores)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
+    for a, b, name in ((q.grad, qr.grad, "dq"), (k.grad, kr.grad, "dk")):
+        err = (a.float() - b).abs().max().item()
+        assert err < 3e-2 * (b.abs().max().item() + 1e-6), (name, err, b.abs().max().item())
+    for row in ((2, 3) if soft else (1, 2)):   # the skipped queries get no gradient
+        assert q.grad[row].abs().max().item() == 0.0
+
+
+def test_label_loss_dispatches_to_streaming_kernels():
+    from lset_b200.losses.contrastive import contrastive_loss
+
+    Q, K = 2048, 4096
+    q, k = _emb(Q, 256, 8).requires_grad_(), _emb(K, 256, 9).requires_grad_()
+    labels = torch.zeros(Q, K, device="cuda")
+    labels[torch.arange(Q), torch.arange(Q)] = 1.0
+    before = nv.launches()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    contrastive_loss(q, k, labels, 0.02).backward()
+    torch.cuda.synchronize()
+    assert nv.launches() > before
+    # int8 labels, masks and the bf16 probability gradient, but never fp32 score-sized temporaries
+    # (the eager formulation holds at least three of them)
+    assert torch.cuda.max_memory_allocated() - base < 2 * Q * K * 4
+
+
+def _eager_dense_loss(q, k, labels, scale, loss_type):
+    """fp32 oracle of the three fused loss types, written from their definitions."""
+    s = q @ k.t() * scale
+    lab = labels.float()
+    pos, neg, valid = lab > 0, lab == 0, lab >= 0
+    if loss_type == "multi":
+        neg_lse = torch.logsumexp(s.masked_fill(~neg, float("-inf")), dim=1, keepdim=True)
+        per = F.softplus(neg_lse - s) * pos
+        n_pos = pos.sum(1)
+        keep = (n_pos > 0) & neg.any(1)
+        per_q = per.sum(1) / n_pos.clamp(min=1)
+        return per_q[keep].sum() / keep.sum().clamp(min=1)
+    lse = torch.logsumexp(s.masked_fill(~valid, float("-inf")), dim=1)
+    l = lab.clamp(min=0)
+    lsum = l.sum(1)
+    keep = lsum > 0
+    if loss_type == "soft":
+        per_q = lse - (l / lsum.clamp(min=1e-9).unsqueeze(1) * s).sum(1)
+    else:
+        per_q = lsum * lse - (l * s).sum(1)
+    return per_q[keep].sum() / keep.sum().clamp(min=1)
+
+
+@pytest.mark.parametrize("loss_type", ["multi", "soft", "cross"])
+@pytest.mark.parametrize("Q,K,D,give_idx", [(96, 300, 256, True), (512, 2048, 1024, False)])
+def test_fused_dense_loss_types(loss_type, Q, K, D, give_idx):
+    from lset_b200.ops.loss import fused_dense_loss
+
+    q, k = _emb(Q, D, 10).requires_grad_(), _emb(K, D, 11).requires_grad_()
+    g = torch.Generator(device="cuda").manual_seed(3 * Q + K)
+    r = torch.rand(Q, K, device="cuda", generator=g)
+    labels = torch.zeros(Q, K, device="cuda", dtype=torch.int8)
+    labels[r < 0.02] = 1
+    if loss_type != "multi":
+        labels[r < 0.01] = 3          # soft label values
+    labels[r > 0.9] = -1
+    labels[4] = 0                     # no positive: skipped
+    labels[5] = torch.where(labels[5] == 0, torch.full_like(labels[5], -1), labels[5])  # no negative
+    idx = (labels > 0).nonzero(as_tuple=True) if give_idx else (None, None)
+    loss = fused_dense_loss(q, k, labels, 20.0, loss_type, pos_qi=idx[0], pos_di=idx[1])
+    loss.backward()
+    nv.check_status()
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    ref = _eager_dense_loss(qr, kr, labels, 20.0, loss_type)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item())), (loss.item(), ref.item())
+    for a, b, name in ((q.grad, qr.grad, "dq"), (k.grad, kr.grad, "dk")):
+        err = (a.float() - b).abs().max().item()
+        assert err < 3e-2 * (b.abs().max().item() + 1e-6), (name, err, b.abs().max().item())
+    assert q.grad[4].abs().max().item() == 0.0

@@ -53,12 +53,13 @@ def test_multi_positive_ignore_and_grads():
 def test_soft_labels():
     q, d = _emb(2, 8, 8), _emb(3, 8, 9)
     labels = torch.tensor([[1., 0, 0], [0, 1, 0]])
-    scores = torch.tensor([[3., 1, float("-inf")], [0., 2, 1]])
-    labels[0, 2] = -1
+    scores = torch.tensor([[3., 1, 5.0], [0., 2, 1]])
+    labels[0, 2] = -1   # ignored column: its score does not count and it leaves the denominator
     loss = contrastive_loss(q, d, labels, 0.1, scores=scores)
     sim = (q @ d.t()) / 0.1
-    t0, lp0 = torch.softmax(scores[0, :2], 0), torch.log_softmax(sim[0, :2], 0)
-    t1, lp1 = torch.softmax(scores[1], 0), torch.log_softmax(sim[1], 0)
+    # targets are the scores normalised to sum to one (lset/losses/contrastive.py:27-38)
+    t0, lp0 = scores[0, :2] / scores[0, :2].sum(), torch.log_softmax(sim[0, :2], 0)
+    t1, lp1 = scores[1] / scores[1].sum(), torch.log_softmax(sim[1], 0)
     assert torch.allclose(loss, (-(t0 * lp0).sum() - (t1 * lp1).sum()) / 2, atol=1e-6)
 
 

@@ -61,11 +61,17 @@ def test_residual_rms_norm(N_, H):
     _close(gr[0], grr[0], name="dr"); _close(gr[1], grr[1], name="dx"); _close(gr[2], grr[2], 3e-2, name="dw")
 
 
-def test_double_residual_rms_norm():
-    r, a, w1, w2 = _r(200, 768), _r(200, 768), _r(768, scale=0.3), _r(768, scale=0.3)
-    out, nr = N.double_residual_rms_norm(r, a, w1, w2, 1e-6, 1.0)
-    outr, nrr = N.double_residual_rms_norm_ref(r.float(), a.float(), w1.float(), w2.float(), 1e-6, 1.0)
-    _close(out, outr); _close(nr, nrr)
+@pytest.mark.parametrize("N_,H", [(200, 768), (1000, 1024), (33, 2560)])
+def test_double_residual_rms_norm(N_, H):
+    r, a, w1, w2 = _r(N_, H), _r(N_, H), _r(H, scale=0.3), _r(H, scale=0.3)
+    g1, g2 = _r(N_, H), _r(N_, H)
+    (out, nr), gr = _grads(lambda p, q, u, v: N.double_residual_rms_norm(p, q, u, v, 1e-6, 1.0),
+                           [r, a, w1, w2], (g1, g2))
+    (outr, nrr), grr = _grads(lambda p, q, u, v: N.double_residual_rms_norm_ref(p, q, u, v, 1e-6, 1.0),
+                              [t.float() for t in (r, a, w1, w2)], (g1.float(), g2.float()))
+    _close(out, outr, name="y"); _close(nr, nrr, name="nr")
+    _close(gr[0], grr[0], name="dr"); _close(gr[1], grr[1], 3e-2, name="da")
+    _close(gr[2], grr[2], 4e-2, name="dw1"); _close(gr[3], grr[3], 4e-2, name="dw2")
 
 
 @pytest.mark.parametrize("N_,H", [(300, 768), (1000, 1024), (64, 384)])
