@@ -193,18 +193,18 @@ def fused_label_loss(q, k, labels, temperature: float, scores=None):
     lab8 = torch.full((Q, Kp), -1, dtype=torch.int8, device=dev)
     lab8[:, :K].copy_(labels)           # converts in the copy: no fp32 [Q, K] temporary
     labels = lab8[:, :K]
-    valid = labels >= 0
+    any_valid = labels.max(dim=1).values >= 0      # row statistics without [Q, K] temporaries
     tw = None
     if scores is not None:
-        target = scores.to(dev, torch.float32).masked_fill(~valid, 0.0)
-        tsum = target.sum(dim=1)
-        keep = (tsum > 0) & valid.any(dim=1)
-        row_scale = 1.0 / tsum.clamp(min=1e-12)
         tw = torch.zeros(Q, Kp, dtype=torch.float32, device=dev)
-        tw[:, :K] = target
+        tw[:, :K] = scores.to(dev, torch.float32)
+        tw[:, :K].masked_fill_(labels < 0, 0.0)
+        tsum = tw.sum(dim=1)
+        keep = (tsum > 0) & any_valid
+        row_scale = 1.0 / tsum.clamp(min=1e-12)
     else:
-        n_pos = (labels == 1).sum(dim=1)
-        keep = (n_pos > 0) & valid.any(dim=1)
+        n_pos = labels.clamp(min=0).sum(dim=1, dtype=torch.int32)   # labels are -1 / 0 / 1 here
+        keep = (n_pos > 0) & any_valid
         row_scale = 1.0 / n_pos.clamp(min=1).float()
     keepf = keep.float()
     row_w = keepf / keepf.sum().clamp(min=1.0)

@@ -37,7 +37,8 @@ def main():
         dist.all_gather(parts, t.contiguous())
         return parts
 
-    for rows, K, N in ((192, 256, 512), (300, 1024, 384), (64, 128, 128)):
+    for rows, K, N in ((192, 256, 512), (300, 1024, 384), (64, 128, 128), (86, 256, 256),
+                       (86, 128, 256), (45, 256, 512)):
         for it in range(3):  # three uses: both halves of the double buffers and a reuse
             torch.manual_seed(100 * it + rank)
             x = (torch.randn(rows, K, device=dev) * 0.5).to(torch.bfloat16).requires_grad_()
@@ -89,47 +90,72 @@ def main():
     init_normal_(ref, 0.05)
     full = {k: v.clone() for k, v in ref.state_dict().items()}
     ref = ref.to(dev, torch.bfloat16)
-    m = Qwen3Decoder(cfg, fused_projections=True)
-    m.load_state_dict(full)
-    apply_tp(m, dist.group.WORLD, decoder_tp_plan(cfg, fused_projections=True,
-                                                  use_sequence_parallel=True))
-    m = m.to(dev, torch.bfloat16)
     lens = [37, 64, 50, 21]
     T = sum(lens)
     ids = torch.arange(T, device=dev) % 512
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
     pos = torch.cat([torch.arange(n, device=dev) for n in lens])
-    outs = []
-    for model in (ref, m):
+
+    # A fixed random projection as the loss: sum(h²) after the final RMSNorm is (almost) constant,
+    # its gradient is rounding noise and would compare nothing.
+    torch.manual_seed(11)
+    proj = torch.randn(T, cfg.hidden_size, device=dev) / T
+
+    def run(model):
         h = model.forward_packed(ids, pos, cu, max(lens))["hidden_states"]
-        h.float().pow(2).mean().backward()
-        outs.append(h.detach())
-    # every parameter gradient of the sharded model against the matching slice of the reference
+        (h.float() * proj).sum().backward()
+        return h.detach()
+
+    def sharded_model(fused):
+        mm = Qwen3Decoder(cfg, fused_projections=True)
+        mm.load_state_dict(full)
+        apply_tp(mm, dist.group.WORLD, decoder_tp_plan(cfg, fused_projections=True,
+                                                       use_sequence_parallel=True))
+        mm = mm.to(dev, torch.bfloat16)
+        mm._sp.bind(dev)
+        if not fused:
+            mm._sp.fused = False   # plain all-gather / reduce-scatter around local GEMMs
+        return mm
+
+    outs = [run(ref)]
+    m_plain = sharded_model(False)
+    h_plain = run(m_plain)
+    m = sharded_model(True)
+    outs.append(run(m))
+    res["plain_vs_fused"] = {
+        "hidden": rel(outs[1], h_plain),
+        "worst_grad": max(rel(a.grad, b.grad) for a, b in zip(m.parameters(), m_plain.parameters())
+                          if a.grad is not None)}
+    # every parameter gradient of the sharded models against the matching slice of the reference
     from lset_b200.dist.tp import _section_sizes, _shard_rows
 
     ref_params = dict(ref.named_parameters())
-    grads = {}
-    for name, p in m.named_parameters():
-        g_ref = ref_params[name].grad
-        g_tp = p.grad
-        if g_tp is None or g_ref is None:
-            grads[name] = None
-            continue
-        if getattr(p, "_tp_sharded", False):
-            mod_name = name.rsplit(".", 1)[0]
-            mod = ref.get_submodule(mod_name)
-            owner = ref.get_submodule(mod_name.rsplit(".", 1)[0])
-            if g_tp.shape[0] != g_ref.shape[0]:      # column-parallel: rows sharded by section
-                g_ref = _shard_rows(g_ref, _section_sizes(mod_name, mod, owner), rank, world)
-            else:                                     # row-parallel: input features sharded
-                per = g_ref.shape[1] // world
-                g_ref = g_ref[:, rank * per:(rank + 1) * per]
-        elif getattr(p, "_tp_partial_grad", False):
-            g_tp = g_tp.float().clone()
-            dist.all_reduce(g_tp)                    # the sharding runtime sums these over the group
-        grads[name] = rel(g_tp, g_ref)
-    res["model"] = {"hidden": rel(outs[1], outs[0]), "grads": grads,
-                    "worst_grad": max(v for v in grads.values() if v is not None),
+
+    def grad_errors(model):
+        grads = {}
+        for name, p in model.named_parameters():
+            g_ref = ref_params[name].grad
+            g_tp = p.grad
+            if g_tp is None or g_ref is None:
+                continue
+            if getattr(p, "_tp_sharded", False):
+                mod_name = name.rsplit(".", 1)[0]
+                mod = ref.get_submodule(mod_name)
+                owner = ref.get_submodule(mod_name.rsplit(".", 1)[0])
+                if g_tp.shape[0] != g_ref.shape[0]:      # column-parallel: rows sharded by section
+                    g_ref = _shard_rows(g_ref, _section_sizes(mod_name, mod, owner), rank, world)
+                else:                                     # row-parallel: input features sharded
+                    per = g_ref.shape[1] // world
+                    g_ref = g_ref[:, rank * per:(rank + 1) * per]
+            elif getattr(p, "_tp_partial_grad", False):
+                g_tp = g_tp.float().clone()
+                dist.all_reduce(g_tp)                    # the sharding runtime sums these over the group
+            grads[name] = rel(g_tp, g_ref)
+        return grads
+
+    grads, grads_plain = grad_errors(m), grad_errors(m_plain)
+    res["model"] = {"hidden": rel(outs[1], outs[0]), "grads": grads, "grads_plain": grads_plain,
+                    "worst_grad": max(grads.values()), "worst_grad_plain": max(grads_plain.values()),
                     "sp_fused": bool(m._sp.fused)}
     nv.check_status()
     dist.barrier()
