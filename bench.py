@@ -290,10 +290,12 @@ def run_ours(args):
     nv.reset_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_host = time.perf_counter()
     for i in range(K):
         engine.forward_backward(staged[i], True)
         engine.optimizer_step()
         engine.micro_step += 1
+    host_ms = (time.perf_counter() - t_host) * 1e3 / K   # time the host needs to enqueue a step
     e1.record()
     barrier_sync(device)
     ms_dev = max_over_ranks(e0.elapsed_time(e1) / K, device)
@@ -321,7 +323,8 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e,
                                      launches,
-                                     {"fused_projections": preset["lora_r"] == 0,
+                                     {"host_enqueue_ms_per_step": round(host_ms, 2),
+                                      "fused_projections": preset["lora_r"] == 0,
                                       "native_library": str(nv.lib_path().name)}, preset)))
     import torch.distributed as dist
 

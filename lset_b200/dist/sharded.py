@@ -217,8 +217,8 @@ class ParamStore:
     def _reduce_scatter(self, g: FlatGroup) -> None:
         if self.use_symm:
             # All ranks' gradients for this group must be complete before anyone reads them: a
-            # one-element all-reduce on this (side) stream orders the kernels across ranks.
-            dist.all_reduce(self._token(), group=self.dp_group)
+            # device barrier on this (side) stream orders the kernels across ranks.
+            self._barrier("reduce").sync()
             lib = nv.load()
             scr = scratch("reduce_shard", lib.lb_reduce_shard_partial_rows(), self.device)
             rc = lib.lb_reduce_shard_f32(
@@ -236,6 +236,16 @@ class ParamStore:
         else:  # gloo: no reduce-scatter
             dist.all_reduce(g.flat_grad, op=dist.ReduceOp.SUM, group=self.dp_group)
             g.grad_shard.copy_(g.flat_grad[g.lo:g.hi]).div_(self.world)
+
+    def _barrier(self, name: str):
+        """Device barrier (flags in symmetric memory) per use site: the sites run on different
+        streams, so each keeps its own epoch sequence."""
+        bars = self.__dict__.setdefault("_barriers", {})
+        if name not in bars:
+            from . import symm as _symm
+
+            bars[name] = _symm.DeviceBarrier(self.device, self.dp_group)
+        return bars[name]
 
     def _token(self) -> torch.Tensor:
         if getattr(self, "_tok", None) is None:
@@ -264,9 +274,9 @@ class ParamStore:
         if self.world == 1:
             return
         if self.use_symm:
-            # adamw_push already stored the new shards into every rank's buffer; one collective
+            # adamw_push already stored the new shards into every rank's buffer; one barrier
             # orders "all pushes done" before the next forward on every rank.
-            dist.all_reduce(self._token(), group=self.dp_group)
+            self._barrier("gather").sync()
             return
         for g in self.groups:
             if self.comm_stream is not None:

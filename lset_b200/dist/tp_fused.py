@@ -12,8 +12,8 @@ sums for every token (GEMM → reduce-scatter). On NVLink-connected GPUs both pa
 
 Their backward passes are each other's mirror image (the gradient of an all-gather is a
 reduce-scatter and vice versa), so the same two kernels serve forward and backward. Ranks are
-ordered by one one-element all-reduce per op, enqueued on the compute stream: no kernel ever spins
-on another GPU. Buffers are double-buffered by an epoch counter, which removes the need for a
+ordered by one device barrier per op (``symm.DeviceBarrier``: flags in symmetric memory, bounded
+wait), enqueued on the compute stream; the GEMM kernels themselves never wait on another GPU. Buffers are double-buffered by an epoch counter, which removes the need for a
 second "done reading" collective (see ``SPState``).
 
 Without symmetric memory (CPU / gloo, or a GPU pair without peer access) the same functions fall
@@ -86,8 +86,8 @@ class SPState:
 
     def barrier(self):
         if self._token is None:
-            self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
-        dist.all_reduce(self._token, group=self.group)
+            self._token = symm.DeviceBarrier(self.device, self.group)
+        self._token.sync()
 
     def ag_buf(self, rows, K) -> _AGBuf:
         b = self._ag.get((rows, K))

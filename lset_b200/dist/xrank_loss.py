@@ -8,9 +8,9 @@ recomputed as a bf16 ``W``, ``dQ = W · K`` stays local, and ``dK = Wᵀ · Q`` 
 whose epilogue adds every row straight into its *owner's* fp32 buffer with ``red.global.add`` over
 NVLink — the reduce-scatter is fused into the GEMM.
 
-Ranks are ordered on the host side with two one-element all-reduces per step (passages published
-and accumulators cleared; all dK contributions landed); they are stream-ordered, so no kernel ever
-spins on another GPU. Same value and gradients as
+Ranks are ordered with two device barriers per step (passages published and accumulators cleared;
+all dK contributions landed): one-warp kernels with a bounded wait on flags in symmetric memory,
+enqueued on the compute stream, so the GEMM kernels themselves never wait on another GPU. Same value and gradients as
 ``gather_for_local_rows`` + ``infonce_loss``; replaces the reference's ``all_gather`` + loss kernel
 (lset/distributed/gather.py:7-35, lset/kernels/loss.py).
 """
@@ -43,11 +43,11 @@ class _Buffers:
         tiles = self.world * ((n_local + 255) // 256)
         self.flags = torch.zeros(tiles, dtype=torch.int32, device=device)
         self.counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.barrier = symm.DeviceBarrier(device, group)
         self.epoch = 0
 
     def order_ranks(self):
-        dist.all_reduce(self.token, group=self.group)
+        self.barrier.sync()
 
 
 def _buffers(n_local, D, device, group) -> _Buffers:

@@ -178,7 +178,15 @@ class _FusedLabelLoss(torch.autograd.Function):
 
 
 def fused_label_loss_supported(q, k) -> bool:
-    return fused_infonce_supported(q, k)
+    return (nv.use_native(q, k) and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and q.shape[1] % 8 == 0 and q.shape[1] == k.shape[1])
+
+
+def _pad_rows8(k):
+    """Passages padded with zero rows to a multiple of 8 (the kernels' granularity); the label
+    padding marks those columns as ignored, and autograd drops their gradient rows."""
+    extra = (-k.shape[0]) % 8
+    return k if extra == 0 else torch.cat([k, k.new_zeros(extra, k.shape[1])], dim=0)
 
 
 def fused_label_loss(q, k, labels, temperature: float, scores=None):
@@ -208,8 +216,9 @@ def fused_label_loss(q, k, labels, temperature: float, scores=None):
         row_scale = 1.0 / n_pos.clamp(min=1).float()
     keepf = keep.float()
     row_w = keepf / keepf.sum().clamp(min=1.0)
-    return _FusedLabelLoss.apply(q.contiguous(), k.contiguous(), lab8, tw, row_scale.contiguous(),
-                                 row_w.contiguous(), 1.0 / float(temperature))
+    return _FusedLabelLoss.apply(q.contiguous(), _pad_rows8(k).contiguous(), lab8, tw,
+                                 row_scale.contiguous(), row_w.contiguous(),
+                                 1.0 / float(temperature))
 
 
 # ------------------------------------------------------------------------------------------------
@@ -325,7 +334,7 @@ def fused_dense_loss(q, k, labels, scale: float, loss_type: str = "multi", pos_q
         raise ValueError(f"unknown loss_type {loss_type!r}")
     lab8 = _pad_labels_int8(labels.to(q.device))
     K = labels.shape[1]
-    q, k = q.contiguous(), k.contiguous()
+    q, k = q.contiguous(), _pad_rows8(k).contiguous()
     if loss_type == "multi":
         if pos_qi is None or pos_di is None:
             pos_qi, pos_di = (lab8[:, :K] > 0).nonzero(as_tuple=True)

@@ -153,12 +153,17 @@ class TrainingEngine:
         if model_config is None:
             model_config = spec.config_cls.from_hf_json(str(Path(model_path) / "config.json"))
         self.model_config = model_config
-        model = spec.model_cls(model_config, fused_projections=fused_projections)
-        if model_path is not None and any(Path(model_path).glob("*.safetensors")) or (
-                model_path is not None and any(Path(model_path).glob("pytorch_model*.bin"))):
+        has_weights = model_path is not None and (
+            any(Path(model_path).glob("*.safetensors")) or any(Path(model_path).glob("pytorch_model*.bin")))
+        if has_weights:
+            model = spec.model_cls(model_config, fused_projections=fused_projections)
             state = spec.weight_converter(model_path, fused_projections=fused_projections)
             model.load_state_dict(state, strict=True)
         else:
+            # random initialisation happens on the target device: building and filling a
+            # multi-billion-parameter model in host memory takes minutes per rank
+            with torch.device(self.device):
+                model = spec.model_cls(model_config, fused_projections=fused_projections)
             init_normal_(model, init_std)
         if self.use_lora:
             from .lora import apply_lora, apply_qlora

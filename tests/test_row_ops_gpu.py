@@ -195,3 +195,40 @@ def test_bounded_wait_times_out_with_status_and_context_survives():
     torch.cuda.synchronize()
     assert status.item() == 0 and waited.item() < 50_000_000
     assert torch.ones(4, device="cuda").sum().item() == 4.0       # the context is still usable
+
+
+def test_device_barrier_single_gpu_forms():
+    """The device barrier on one GPU: a one-rank group passes at once; a two-rank group whose peer
+    never announces runs into the bounded wait and reports the peer-timeout status (nothing hangs,
+    the context stays usable). The peer's pad is a second local buffer, so no other GPU is involved."""
+    import ctypes
+
+    lib = nv.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peer = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pads1 = (ctypes.c_void_p * 1)(mine.data_ptr())
+    for epoch in (1, 2, 3):
+        rc = lib.lb_device_barrier(pads1, ctypes.c_int(1), ctypes.c_int(0), ctypes.c_uint(epoch),
+                                   ctypes.c_ulonglong(200_000_000),
+                                   ctypes.c_void_p(status.data_ptr()), stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0 and mine[0].item() == 3
+    pads2 = (ctypes.c_void_p * 2)(mine.data_ptr(), peer.data_ptr())
+    mine.zero_()
+    rc = lib.lb_device_barrier(pads2, ctypes.c_int(2), ctypes.c_int(0), ctypes.c_uint(1),
+                               ctypes.c_ulonglong(200_000_000), ctypes.c_void_p(status.data_ptr()),
+                               stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 4                      # kStatusTimeoutPeer
+    assert mine[0].item() == 1 and peer[0].item() == 1   # this rank did announce to both pads
+    mine[1] = 2                                    # the "peer" is already one barrier ahead
+    status.zero_()
+    lib.lb_device_barrier(pads2, ctypes.c_int(2), ctypes.c_int(0), ctypes.c_uint(2),
+                          ctypes.c_ulonglong(200_000_000), ctypes.c_void_p(status.data_ptr()), stream)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
