@@ -42,6 +42,8 @@ struct GemmArgs {
   int splits;                 // >= 1, split of the K range
   int kb_per_split;
   int raster_m_fast;          // tile order: consecutive tiles walk M first (B tile shared in L2)
+  int kb_ext;                 // extra k-blocks read through the second tensor-map pair (A2, B2):
+                              // C = A·Bᵀ + A2·B2ᵀ in one accumulator pass (LoRA: A2 = x·A_loraᵀ)
   // contrastive-loss epilogues (EPI_LSE / EPI_PGRAD): scores s = acc * scale
   float scale;                // 1 / temperature
   const float* lse;           // [M] natural-log LSE (EPI_PGRAD input)
@@ -118,7 +120,8 @@ __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, 
 template <int A_MN, int B_MN, int BN, typename OutT, int EPI, int GATHER = 0>
 __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tmA2,
+                     const __grid_constant__ CUtensorMap tmB2, GemmArgs g) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -146,6 +149,10 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (g.kb_ext > 0) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -162,7 +169,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 0;
   const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
   const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
-  const int kb_total = (g.K + BK - 1) / BK;
+  const int kb_main = (g.K + BK - 1) / BK;
+  const int kb_total = kb_main + g.kb_ext;
   const int total = tiles_m * tiles_n * g.splits;
   // (m0, n0, flag index) of the `mn`-th output tile
   auto decode = [&](int mn, int& m0, int& n0, int& chunk) {
@@ -236,19 +244,24 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           mbar_expect_tx(&full[stage], C::STAGE_BYTES);
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
+          // k-blocks past the main contraction come from the second operand pair
+          const bool ext = kb >= kb_main;
+          const CUtensorMap* ta = ext ? &tmA2 : &tmA;
+          const CUtensorMap* tb = ext ? &tmB2 : &tmB;
+          const int kc = (ext ? kb - kb_main : kb) * BK;
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
-              tma_load_2d(sa + c * (BK * 128), &tmA, &full[stage], m0 + 64 * c, kb * BK);
+              tma_load_2d(sa + c * (BK * 128), ta, &full[stage], m0 + 64 * c, kc);
           } else {
-            tma_load_2d(sa, &tmA, &full[stage], kb * BK, m0);
+            tma_load_2d(sa, ta, &full[stage], kc, m0);
           }
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (BK * 128), &tmB, &full[stage], n0 + 64 * c, kb * BK);
+              tma_load_2d(sb + c * (BK * 128), tb, &full[stage], n0 + 64 * c, kc);
           } else {
-            tma_load_2d(sb, &tmB, &full[stage], kb * BK, n0);
+            tma_load_2d(sb, tb, &full[stage], kc, n0);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -586,7 +599,8 @@ int num_sms() {
 
 template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE, int GATHER = 0>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
-           cudaStream_t stream) {
+           cudaStream_t stream, const CUtensorMap* tmA2 = nullptr,
+           const CUtensorMap* tmB2 = nullptr) {
   using C = Cfg<BN>;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI, GATHER>;
   static bool configured = false;
@@ -596,7 +610,8 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, in
       return -10;
     configured = true;
   }
-  kern<<<grid, GATHER ? kGatherThreads : kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, g);
+  kern<<<grid, GATHER ? kGatherThreads : kGemmThreads, C::SMEM_BYTES, stream>>>(
+      tmA, tmB, tmA2 != nullptr ? *tmA2 : tmA, tmB2 != nullptr ? *tmB2 : tmB, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -822,6 +837,61 @@ int prep_loss(const void* Q, const void* Kd, int M, int N, int D, long long ldq,
 }  // namespace lb
 
 // Number of floats of scratch that lb_infonce_fwd needs for M queries against N passages.
+// C[M, N] (bf16) = A · op(B) + A2 · op(B2) (+ bias) in one pass over the accumulator: the k-blocks
+// of the second pair are appended to the contraction. A [M, K] and A2 [M, K2] are K-major;
+// op(B) = Bᵀ for B [N, K], B2 [N, K2] (b_mn = 0) or B for B [K, N], B2 [K2, N] (b_mn = 1).
+// K2 is a multiple of 8 (a LoRA rank); its k-block is zero-filled by TMA up to 64.
+extern "C" int lb_gemm_bf16_ext(const void* A, const void* B, const void* A2, const void* B2,
+                                void* C, int M, int N, int K, int K2, long long lda,
+                                long long ldb, long long lda2, long long ldb2, long long ldc,
+                                int b_mn, const void* bias, int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K2 <= 0) return -4;
+  if ((N & 7) || (K2 & 7) || (lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7) || (ldc & 7))
+    return -3;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int bn = N > 128 ? 256 : 128;
+  const int tiles_n = (N + bn - 1) / bn;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  int rc = make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmA2, A2, 2, (uint64_t)K2, (uint64_t)M, (uint64_t)lda2 * 2, BK, BM, true);
+  if (rc) return rc;
+  if (b_mn) {
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)N, (uint64_t)K2, (uint64_t)ldb2 * 2, 64, BK, true);
+  } else {
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, bn, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)K2, (uint64_t)N, (uint64_t)ldb2 * 2, BK, bn, true);
+  }
+  if (rc) return rc;
+  GemmArgs g{};
+  g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.C = C;
+  g.ldc = ldc;
+  g.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  g.splits = 1;
+  g.kb_ext = (K2 + BK - 1) / BK;
+  g.kb_per_split = (K + BK - 1) / BK + g.kb_ext;
+  g.status = status;
+  const long long total = 1LL * tiles_m * tiles_n;
+  const int sms = num_sms();
+  const int grid = (int)(total < sms ? total : sms);
+  if (b_mn)
+    return bn == 256
+               ? launch<0, 1, 256, __nv_bfloat16>(tmA, tmB, g, grid, stream, &tmA2, &tmB2)
+               : launch<0, 1, 128, __nv_bfloat16>(tmA, tmB, g, grid, stream, &tmA2, &tmB2);
+  return bn == 256 ? launch<0, 0, 256, __nv_bfloat16>(tmA, tmB, g, grid, stream, &tmA2, &tmB2)
+                   : launch<0, 0, 128, __nv_bfloat16>(tmA, tmB, g, grid, stream, &tmA2, &tmB2);
+}
+
 extern "C" long long lb_infonce_scratch_floats(int M, int N) {
   const int bn = lb::loss_tile_bn(M, N);
   return 2LL * ((N + bn - 1) / bn) * M + M;

@@ -13,8 +13,9 @@ sums for every token (GEMM → reduce-scatter). On NVLink-connected GPUs both pa
 Their backward passes are each other's mirror image (the gradient of an all-gather is a
 reduce-scatter and vice versa), so the same two kernels serve forward and backward. Ranks are
 ordered by one device barrier per op (``symm.DeviceBarrier``: flags in symmetric memory, bounded
-wait), enqueued on the compute stream; the GEMM kernels themselves never wait on another GPU. Buffers are double-buffered by an epoch counter, which removes the need for a
-second "done reading" collective (see ``SPState``).
+wait), enqueued on the compute stream; the GEMM kernels themselves never wait on another GPU.
+Buffers are double-buffered by an epoch counter, which removes the need for a second "done
+reading" barrier (see ``SPState``).
 
 Without symmetric memory (CPU / gloo, or a GPU pair without peer access) the same functions fall
 back to an explicit all-gather / reduce-scatter around a local GEMM, so the model plumbing is
@@ -34,18 +35,38 @@ from ..ops.gemm import matmul_abt, wgrad_splits
 from . import symm
 
 
+def _capacity(rows: int) -> int:
+    """Row capacity for ``rows``: headroom of a quarter, rounded up to 1024, so that batches of
+    varying token counts reuse one allocation (symmetric allocations need a rendezvous)."""
+    return ((rows + rows // 4 + 1023) // 1024) * 1024
+
+
 class _AGBuf:
-    def __init__(self, rows, K, world, device, group):
-        self.x_sym = [symm.SymmBuffer(rows * K, torch.bfloat16, device, group) for _ in range(2)]
-        tiles = world * ((rows + 127) // 128)
-        self.flags = torch.zeros(tiles, dtype=torch.int32, device=device)
+    """Double-buffered publication area for token shards of width K (any row count up to cap)."""
+
+    def __init__(self, cap, K, world, device, group):
+        self.cap = cap
+        self.x_sym = [symm.SymmBuffer(cap * K, torch.bfloat16, device, group) for _ in range(2)]
         self.counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
+        self.device, self.world = device, world
+        self._flags = {}   # rows -> (flags, epoch): the flag counts depend on the tile split
+
+    def flags(self, rows):
+        """Flag words and call count for this row count. A flag accumulates the items pulled over
+        all calls that used it, so every row count keeps its own words and its own epoch."""
+        ent = self._flags.get(rows)
+        if ent is None:
+            tiles = self.world * ((rows + 127) // 128)
+            ent = self._flags[rows] = [torch.zeros(tiles, dtype=torch.int32, device=self.device), 0]
+        return ent
 
 
 class _RSBuf:
-    def __init__(self, rows, N, device, group):
-        self.acc = [symm.SymmBuffer(rows * N, torch.float32, device, group) for _ in range(2)]
+    """Double-buffered fp32 accumulators of width N (any row count up to cap)."""
+
+    def __init__(self, cap, N, device, group):
+        self.cap = cap
+        self.acc = [symm.SymmBuffer(cap * N, torch.float32, device, group) for _ in range(2)]
         for a in self.acc:
             a.local.zero_()
         self.epoch = 0
@@ -71,7 +92,7 @@ class SPState:
         self._token = None
         if device is not None:
             self.bind(device)
-        self._ag, self._rs = {}, {}
+        self._ag, self._rs, self._ag_epoch, self._retired = {}, {}, {}, []
         self._last_gather = None  # (x_shard, x_all) of the latest all-gather (q/k/v share it)
 
     def bind(self, device) -> None:
@@ -90,15 +111,24 @@ class SPState:
         self._token.sync()
 
     def ag_buf(self, rows, K) -> _AGBuf:
-        b = self._ag.get((rows, K))
-        if b is None:
-            b = self._ag[(rows, K)] = _AGBuf(rows, K, self.world, self.device, self.group)
+        b = self._ag.get(K)
+        if b is None or b.cap < rows:
+            # a larger batch than ever seen: new buffers (every rank takes this branch together,
+            # the token count is the same on all ranks of the group). The old ones are kept: a
+            # slower peer may still be reading them, and memory a peer maps must not be freed
+            # under it.
+            if b is not None:
+                self._retired.append(b)
+            b = self._ag[K] = _AGBuf(_capacity(rows), K, self.world, self.device, self.group)
+            self._ag_epoch[K] = 0
         return b
 
     def rs_buf(self, rows, N) -> _RSBuf:
-        b = self._rs.get((rows, N))
-        if b is None:
-            b = self._rs[(rows, N)] = _RSBuf(rows, N, self.device, self.group)
+        b = self._rs.get(N)
+        if b is None or b.cap < rows:
+            if b is not None:
+                self._retired.append(b)
+            b = self._rs[N] = _RSBuf(_capacity(rows), N, self.device, self.group)
             self.barrier()  # every rank's accumulators are cleared before anyone adds into them
         return b
 
@@ -131,9 +161,11 @@ def _ag_gemm(st: SPState, x_shard, w, bias, b_mn: bool):
     W, rank = st.world, st.rank
     N = w.shape[1] if b_mn else w.shape[0]
     buf = st.ag_buf(rows, K)
-    buf.epoch += 1
-    xs = buf.x_sym[buf.epoch & 1]
-    xs.local.view(rows, K).copy_(x_shard)
+    st._ag_epoch[K] += 1                       # which half of the publication area this use takes
+    xs = buf.x_sym[st._ag_epoch[K] & 1]
+    fl = buf.flags(rows)
+    fl[1] += 1                                 # call count of these flag words
+    xs.local[:rows * K].view(rows, K).copy_(x_shard)
     x_all = torch.empty(W * rows, K, dtype=torch.bfloat16, device=x_shard.device)
     x_all[rank * rows:(rank + 1) * rows].copy_(x_shard)  # own rows need no pull
     st.barrier()                                          # every shard is published
@@ -144,8 +176,8 @@ def _ag_gemm(st: SPState, x_shard, w, bias, b_mn: bool):
         nv.c_void_p(y.data_ptr()), nv.c_int(rows), nv.c_int(W), nv.c_int(rank), nv.c_int(N),
         nv.c_int(K), nv.c_ll(K), nv.c_ll(w.stride(0)), nv.c_ll(N), nv.c_int(1 if b_mn else 0),
         nv.c_void_p(bias.data_ptr() if bias is not None else None),
-        nv.c_void_p(buf.flags.data_ptr()), nv.c_void_p(buf.counter.data_ptr()),
-        ctypes.c_uint(buf.epoch), nv.c_void_p(nv.status_word(x_shard.device).data_ptr()),
+        nv.c_void_p(fl[0].data_ptr()), nv.c_void_p(buf.counter.data_ptr()),
+        ctypes.c_uint(fl[1]), nv.c_void_p(nv.status_word(x_shard.device).data_ptr()),
         nv.c_void_p(nv.stream_ptr()))
     nv.check_rc(rc, "lb_gemm_bf16_ag")
     nv.count_launch(1)
@@ -170,8 +202,9 @@ def _gemm_rs(st: SPState, a, w, b_mn: bool):
     nv.check_rc(rc, "lb_gemm_bf16_scatter")
     nv.count_launch(1)
     st.barrier()                                          # every contribution has landed
-    out = acc.local.view(rows, N).to(torch.bfloat16)
-    acc.local.zero_()
+    used = acc.local[:rows * N]
+    out = used.view(rows, N).to(torch.bfloat16)
+    used.zero_()
     return out
 
 

@@ -60,7 +60,15 @@ def use_native(*tensors) -> bool:
     return all(t is None or t.is_cuda for t in tensors) and any(t is not None for t in tensors)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream_ptr() -> int:
+    """Raw handle of the current CUDA stream of the current device (the C-level lookup: this is
+    called once per kernel launch)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -73,12 +81,17 @@ _status = {}
 
 def status_word(device=None) -> torch.Tensor:
     """Per-device int32 word that kernels with bounded waits write their status code into."""
+    t = _status.get(device)          # hot path: the same torch.device object / value every call
+    if t is not None:
+        return t
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
     t = _status.get(key)
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=dev)
         _status[key] = t
+    if device is not None:
+        _status[device] = t
     return t
 
 

@@ -86,7 +86,8 @@ def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat
         nv.c_int(bn), nv.c_void_p(nv.status_word(a.device).data_ptr()),
         nv.c_void_p(nv.stream_ptr()),
     )
-    nv.check_rc(rc, f"lb_gemm_bf16(M={M},N={N},K={K})")
+    if rc != 0:
+        nv.check_rc(rc, f"lb_gemm_bf16(M={M},N={N},K={K})")
     nv.count_launch()
     return out
 
@@ -140,3 +141,83 @@ def linear(x, w, bias=None):
     if not nv.use_native(x, w) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return torch.nn.functional.linear(x, w, bias)
     return _Linear.apply(x, w, bias)
+
+
+def matmul_ext(a, b, a2, b2, *, b_mn=False, bias=None):
+    """``A · op(B) + A2 · op(B2)`` (bf16 out) in one pass over the accumulator: the second pair's
+    k-blocks are appended to the contraction (``lb_gemm_bf16_ext``). ``op`` as in ``matmul_abt``;
+    ``a2`` is ``[M, K2]`` with K2 a multiple of 8 (a LoRA rank)."""
+    M, K = a.shape
+    K2 = a2.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if not nv.use_native(a, b, a2, b2):
+        bf = b.float() if b_mn else b.float().t()
+        b2f = b2.float() if b_mn else b2.float().t()
+        c = a.float() @ bf + a2.float() @ b2f
+        if bias is not None:
+            c = c + bias.float()
+        return c.to(a.dtype)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if M == 0 or N == 0:
+        return out
+    rc = nv.load().lb_gemm_bf16_ext(
+        nv.c_void_p(a.data_ptr()), nv.c_void_p(b.data_ptr()), nv.c_void_p(a2.data_ptr()),
+        nv.c_void_p(b2.data_ptr()), nv.c_void_p(out.data_ptr()), nv.c_int(M), nv.c_int(N),
+        nv.c_int(K), nv.c_int(K2), nv.c_ll(a.stride(0)), nv.c_ll(b.stride(0)),
+        nv.c_ll(a2.stride(0)), nv.c_ll(b2.stride(0)), nv.c_ll(N), nv.c_int(int(b_mn)),
+        nv.c_void_p(nv.ptr(bias)), nv.c_void_p(nv.status_word(a.device).data_ptr()),
+        nv.c_void_p(nv.stream_ptr()))
+    if rc != 0:
+        nv.check_rc(rc, f"lb_gemm_bf16_ext(M={M},N={N},K={K},K2={K2})")
+    nv.count_launch()
+    return out
+
+
+def _accumulate_wgrad(w, dy2, x2):
+    """``dW = dy2ᵀ · x2`` into ``w.main_grad`` (returns None) or as a tensor of ``w``'s dtype."""
+    splits = wgrad_splits(w.shape[0], w.shape[1], x2.shape[0]) if dy2.is_cuda else 1
+    main = getattr(w, "main_grad", None)
+    if main is not None and dy2.is_cuda:
+        matmul_abt(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True, splits=splits)
+        return None
+    return matmul_abt(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32,
+                      splits=splits).to(w.dtype)
+
+
+class _LoRALinear(torch.autograd.Function):
+    """``y = x Wᵀ + s · (x Aᵀ) Bᵀ (+ bias)`` with a frozen ``W``: the rank-r update rides along in
+    the base GEMM's accumulator (forward) and in the input-gradient GEMM (backward), so the
+    ``[T, N]`` output is written once and never re-read. No weight gradient for ``W``."""
+
+    @staticmethod
+    def forward(ctx, x, w, lora_a, lora_b, bias, scale):
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        t = matmul_abt(x2, lora_a)                       # [T, r]
+        ts = t * scale
+        y = matmul_ext(x2, w, ts, lora_b, bias=bias)      # x·Wᵀ + ts·Bᵀ
+        ctx.save_for_backward(x2, ts, w, lora_a, lora_b)
+        ctx.scale = scale
+        ctx.has_bias = bias is not None
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, ts, w, lora_a, lora_b = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16 and dy2.is_cuda:
+            dy2 = dy2.to(torch.bfloat16)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        us = matmul_abt(dy2, lora_b, b_mn=True) * ctx.scale          # [T, r] = s · dy · B
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_ext(dy2, w, us, lora_a, b_mn=True).view(ctx.shape)   # dy·W + us·A
+        da = _accumulate_wgrad(lora_a, us, x2) if ctx.needs_input_grad[2] else None   # usᵀ · x
+        db = _accumulate_wgrad(lora_b, dy2, ts) if ctx.needs_input_grad[3] else None  # dyᵀ · ts
+        dbias = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[4] else None
+        return dx, None, da, db, dbias, None
+
+
+def lora_linear(x, w, lora_a, lora_b, bias, scale: float):
+    return _LoRALinear.apply(x, w, lora_a, lora_b, bias, float(scale))

@@ -3,9 +3,11 @@
 ``LoRALinear`` wraps a frozen linear layer: ``y = base(x) + lora_B(lora_A(dropout(x))) * alpha / r``
 with ``lora_A`` Kaiming-uniform(a=sqrt(5)) and ``lora_B`` zero, so training starts at the base
 model. State-dict keys under a wrapped layer are ``base_linear.weight``, ``lora_A.weight``,
-``lora_B.weight`` as in the reference (lset/train/lora.py:24-170). All three products run on the
-tcgen05 GEMM for bf16 CUDA tensors; the base weight gets no weight-gradient GEMM because it does
-not require grad.
+``lora_B.weight`` as in the reference (lset/train/lora.py:24-170). For bf16 CUDA tensors the
+rank-r update is folded into the base GEMM (``ops.gemm.lora_linear``: the k-blocks of
+``(s·x·Aᵀ, B)`` are appended to the contraction of ``(x, W)``), forward and input-gradient alike;
+the base weight gets no weight-gradient GEMM because it does not require grad. Quantised bases,
+dropout in training mode and tensor-parallel wrappers use the three-product composition.
 """
 from __future__ import annotations
 
@@ -49,7 +51,21 @@ class LoRALinear(nn.Module):
     def bias(self):
         return self.base_linear.bias
 
+    def _fusable(self, x) -> bool:
+        """One-GEMM path: plain bf16 base on the GPU, no dropout mask to apply, no tensor-parallel
+        wrappers around the three linears, rank a multiple of 8."""
+        b = self.base_linear
+        return (type(b) is Linear and x.is_cuda and x.dtype == torch.bfloat16
+                and b.weight.dtype == torch.bfloat16 and self.r % 8 == 0
+                and (isinstance(self.dropout, nn.Identity) or not self.training)
+                and not any(hasattr(m, "_tp_kind") for m in (b, self.lora_A, self.lora_B)))
+
     def forward(self, x):
+        if self._fusable(x):
+            from ..ops.gemm import lora_linear
+
+            return lora_linear(x, self.base_linear.weight, self.lora_A.weight, self.lora_B.weight,
+                               self.base_linear.bias, self.scale)
         return self.base_linear(x) + self.lora_B(self.lora_A(self.dropout(x))) * self.scale
 
     def merged_weight(self) -> torch.Tensor:

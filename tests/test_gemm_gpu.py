@@ -85,3 +85,49 @@ def test_linear_autograd():
     _check(x.grad, xr.grad)
     _check(w.grad, wr.grad)
     _check(bias.grad, br.grad)
+
+
+@pytest.mark.parametrize("M,N,K,K2", [(300, 512, 256, 16), (1000, 4096, 1024, 16), (64, 128, 128, 8),
+                                      (513, 1024, 2560, 64)])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_matmul_ext_second_operand_pair(M, N, K, K2, b_mn):
+    """C = A·op(B) + A2·op(B2) in one accumulator pass (the LoRA forward / input-gradient form)."""
+    from lset_b200.ops.gemm import matmul_ext
+
+    torch.manual_seed(0)
+    r = lambda *s: (torch.randn(*s, device="cuda") * 0.3).to(torch.bfloat16)  # noqa: E731
+    a, a2 = r(M, K), r(M, K2)
+    b, b2 = (r(K, N), r(K2, N)) if b_mn else (r(N, K), r(N, K2))
+    bias = None if b_mn else r(N)
+    c = matmul_ext(a, b, a2, b2, b_mn=b_mn, bias=bias)
+    nv.check_status()
+    bf, b2f = (b.float(), b2.float()) if b_mn else (b.float().t(), b2.float().t())
+    ref = a.float() @ bf + a2.float() @ b2f + (bias.float() if bias is not None else 0.0)
+    err = (c.float() - ref).abs().max().item()
+    assert err < 2e-2 * ref.abs().max().item(), (err, ref.abs().max().item())
+
+
+def test_lora_linear_matches_three_products():
+    from lset_b200.models.layers import Linear
+    from lset_b200.train.lora import LoRALinear
+
+    torch.manual_seed(1)
+    base = Linear(512, 768, bias=False, device="cuda", dtype=torch.bfloat16)
+    lora = LoRALinear(base, r=16, alpha=32.0).to("cuda")
+    torch.nn.init.normal_(lora.lora_B.weight, std=0.05)      # away from the zero initialisation
+    x = (torch.randn(3, 100, 512, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    g = (torch.randn(3, 100, 768, device="cuda") * 0.5).to(torch.bfloat16)
+    assert lora._fusable(x)
+    y = lora(x)
+    y.backward(g)
+    nv.check_status()
+    got = (y.detach(), x.grad, lora.lora_A.weight.grad, lora.lora_B.weight.grad)
+    xr = x.detach().float().requires_grad_()
+    W, A, B = (t.detach().float().requires_grad_() for t in
+               (base.weight, lora.lora_A.weight, lora.lora_B.weight))
+    yr = xr @ W.t() + (xr @ A.t()) @ B.t() * lora.scale
+    yr.backward(g.float())
+    for a, b, name in zip(got, (yr.detach(), xr.grad, A.grad, B.grad), ("y", "dx", "dA", "dB")):
+        err = (a.float() - b).abs().max().item()
+        assert err < 3e-2 * b.abs().max().item(), (name, err, b.abs().max().item())
+    assert base.weight.grad is None
