@@ -267,7 +267,8 @@ def run_ours(args):
         max_steps=10**9, grad_clip=1.0, temperature=TEMPERATURE, packed=True, log_interval=0,
         scheduler_type="constant", model_config=Qwen3Config(**preset["model"]),
         fused_projections=preset["lora_r"] == 0, collator=BenchCollator(), async_tp=tp > 1,
-        lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0)
+        lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0,
+        init_on_device=args.config != "qwen3-0.6b")
     device = engine.device
     n_batches = W + 2 * K
     # ranks of one tensor-parallel group see the same batch

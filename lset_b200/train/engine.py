@@ -95,7 +95,7 @@ class TrainingEngine:
                  learnable_temperature: bool = False, weight_decay: float = 0.01,
                  step_timeout_s: float = 0.0, device: Optional[str] = None, seed: int = 42,
                  max_seq_length: int = 512, tokenizer=None, num_workers: int = 0,
-                 jsonl_log: bool = False, init_std: float = 0.02):
+                 jsonl_log: bool = False, init_std: float = 0.02, init_on_device: bool = False):
         if cuda_graph:
             from .cuda_graph import validate_cuda_graph_config
 
@@ -160,9 +160,10 @@ class TrainingEngine:
             state = spec.weight_converter(model_path, fused_projections=fused_projections)
             model.load_state_dict(state, strict=True)
         else:
-            # random initialisation happens on the target device: building and filling a
-            # multi-billion-parameter model in host memory takes minutes per rank
-            with torch.device(self.device):
+            # Random initialisation: on the host by default (bit-identical start on CPU and GPU
+            # runs); init_on_device builds and fills the model on the target device, which is what
+            # multi-billion-parameter models need (host-side init takes minutes per rank).
+            with torch.device(self.device if init_on_device else "cpu"):
                 model = spec.model_cls(model_config, fused_projections=fused_projections)
             init_normal_(model, init_std)
         if self.use_lora:

@@ -7,6 +7,9 @@ captures under ``profiles/`` are taken from).
     python -m lset_b200.utils.kernel_bench rope  --rows 23040 --hq 16 --hk 8 --hd 128 [--bwd]
     python -m lset_b200.utils.kernel_bench glu   --rows 23040 --i 3072 [--bwd]
     python -m lset_b200.utils.kernel_bench loss  --q 8192 --k 8192 --d 1024
+    python -m lset_b200.utils.kernel_bench pool  --seqs 4096 --len 64 --h 1024 [--bwd]
+    python -m lset_b200.utils.kernel_bench embed --rows 131072 --h 1024 [--bwd]
+    python -m lset_b200.utils.kernel_bench adamw --n 268435456
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, a 256 MB buffer rewritten and then
 read between timed launches (larger than the 126 MB L2; the read leaves no dirty lines whose
@@ -165,6 +168,64 @@ def bench_loss(a):
                 **roofline(ms, 8.0 * a.q * a.k * a.d, 0.0))
 
 
+def bench_pool(a):
+    from ..ops.pooling import packed_pool
+
+    T = a.seqs * a.len
+    h = _r(T, a.h)
+    cu = torch.arange(a.seqs + 1, device="cuda", dtype=torch.int32) * a.len
+    if a.bwd:
+        h.requires_grad_()
+        y = packed_pool(h, cu, "mean", True)
+        g = _r(a.seqs, a.h)
+        fn = lambda: torch.autograd.grad(y, h, g, retain_graph=True)  # noqa: E731
+        byt = 2.0 * T * a.h
+    else:
+        fn = lambda: packed_pool(h, cu, "mean", True)  # noqa: E731
+        byt = 2.0 * T * a.h
+    ms = _time(fn, a.iters)
+    return dict(kernel="segment_mean_l2norm_" + ("bwd" if a.bwd else "fwd"), seqs=a.seqs, len=a.len,
+                H=a.h, ms=ms, **roofline(ms, 0.0, byt))
+
+
+def bench_embed(a):
+    from ..ops.embedding import embedding
+
+    table = _r(151936, a.h)
+    ids = torch.randint(0, 151936, (a.rows,), device="cuda")
+    if a.bwd:
+        table.requires_grad_()
+        y = embedding(ids, table)
+        g = _r(a.rows, a.h)
+        fn = lambda: torch.autograd.grad(y, table, g, retain_graph=True)  # noqa: E731
+        byt = a.rows * a.h * (2.0 + 8.0)      # read bf16 grads, fp32 read-modify-write of the rows
+    else:
+        fn = lambda: embedding(ids, table)  # noqa: E731
+        byt = a.rows * a.h * 4.0
+    ms = _time(fn, a.iters)
+    return dict(kernel="embedding_" + ("bwd" if a.bwd else "fwd"), rows=a.rows, H=a.h, ms=ms,
+                **roofline(ms, 0.0, byt))
+
+
+def bench_adamw(a):
+    from ..dist.sharded import ParamStore, ShardedAdamW
+
+    lin = torch.nn.Linear(16384, a.n // 16384, bias=False)
+    store = ParamStore(lin, layer_modules=[lin], compute_dtype=torch.bfloat16,
+                       device=torch.device("cuda"))
+    opt = ShardedAdamW(store, lr=1e-4, grad_clip=1.0)
+    store.groups[0].flat_grad.normal_(0.0, 1e-3)
+
+    def fn():
+        store.sumsq.zero_()
+        opt.step()
+
+    ms = _time(fn, a.iters)
+    # grad read twice (norm, update), master + two moments read and written, bf16 copy written
+    byt = a.n * (4.0 * 2 + 4.0 * 6 + 2.0)
+    return dict(kernel="sumsq+clip+adamw", n=a.n, ms=ms, **roofline(ms, 0.0, byt))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="which", required=True)
@@ -190,13 +251,22 @@ def main(argv=None):
     l = sub.add_parser("loss")
     l.add_argument("--q", type=int, default=8192); l.add_argument("--k", type=int, default=8192)
     l.add_argument("--d", type=int, default=1024)
-    for p in (g, t, n, r, u, l):
+    po = sub.add_parser("pool")
+    po.add_argument("--seqs", type=int, default=4096); po.add_argument("--len", type=int, default=64)
+    po.add_argument("--h", type=int, default=1024); po.add_argument("--bwd", action="store_true")
+    em = sub.add_parser("embed")
+    em.add_argument("--rows", type=int, default=131072); em.add_argument("--h", type=int, default=1024)
+    em.add_argument("--bwd", action="store_true")
+    ad = sub.add_parser("adamw")
+    ad.add_argument("--n", type=int, default=268435456)
+    for p in (g, t, n, r, u, l, po, em, ad):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     from ..ops import _native as nv
 
     out = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "rope": bench_rope,
-           "glu": bench_glu, "loss": bench_loss}[a.which](a)
+           "glu": bench_glu, "loss": bench_loss, "pool": bench_pool, "embed": bench_embed,
+           "adamw": bench_adamw}[a.which](a)
     nv.check_status()
     print(json.dumps(out))
 
