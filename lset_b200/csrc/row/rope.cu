@@ -44,32 +44,41 @@ __device__ __forceinline__ int token_pos(const RopeArgs& a, long long tok) {
 }
 
 // A group of HD/8 lanes owns one token at a time and walks over its heads UB at a time: the cos/sin
-// row and the position are fetched once per token, and UB independent 16-byte loads are in flight
-// per thread before the first one is consumed (the kernel is bound by memory latency otherwise).
+// row and the position are fetched once per token, and the 16-byte loads of the next UB heads are
+// already in flight while the current UB heads are normalised, rotated and stored (the kernel is
+// bound by memory latency otherwise).
 template <int HD>
-__global__ void __launch_bounds__(kRowThreads, 2) qk_rope_fwd_kernel(RopeArgs a) {
+__global__ void __launch_bounds__(kRowThreads, 3) qk_rope_fwd_kernel(RopeArgs a) {
   constexpr int LPH = HD / 8;  // lanes per head
   constexpr int TPB = kRowThreads / LPH;
-  constexpr int UB = 8;
+  constexpr int UB = 4;
+  __shared__ float swt[2 * HD];  // q then k norm weights (+ offset)
   const int l = threadIdx.x % LPH;
   const int g = threadIdx.x / LPH;
   const int heads = a.Hq + a.Hk;
   const int e0 = l * 8;
   const int c0 = e0 % (HD / 2);
   const bool first_half = l < LPH / 2;
-  float wq[8], wk[8];
-  if (a.do_norm) {
-    unpack8(ld16(a.qw + e0), wq);
-    unpack8(ld16(a.kw + e0), wk);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      wq[i] += a.w_off;
-      wk[i] += a.w_off;
-    }
-  }
+  for (int i = threadIdx.x; i < 2 * HD; i += kRowThreads)
+    swt[i] = a.do_norm ? __bfloat162float(i < HD ? a.qw[i] : a.kw[i - HD]) + a.w_off : 1.f;
+  __syncthreads();
   for (int tok0 = blockIdx.x * TPB; tok0 < a.T; tok0 += gridDim.x * TPB) {
     const long long tok = tok0 + g;
     const bool valid = tok < a.T;
+    const bf16* qrow = a.q_in + tok * a.ldq_in + e0;
+    const bf16* krow = a.k_in + tok * a.ldk_in + e0;
+    bf16* qdst = a.q_out + tok * a.ldq_out + e0;
+    bf16* kdst = a.k_out + tok * a.ldk_out + e0;
+    auto load_batch = [&](int h0, uint4 (&raw)[UB]) {
+#pragma unroll
+      for (int j = 0; j < UB; ++j) {
+        const int h = h0 + j;
+        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (valid && h < heads) raw[j] = ld16(h < a.Hq ? qrow + h * HD : krow + (h - a.Hq) * HD);
+      }
+    };
+    uint4 cur[UB], nxt[UB];
+    load_batch(0, cur);
     float c[8], s[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) c[i] = s[i] = 0.f;
@@ -86,25 +95,15 @@ __global__ void __launch_bounds__(kRowThreads, 2) qk_rope_fwd_kernel(RopeArgs a)
 #pragma unroll
       for (int i = 0; i < 8; ++i) s[i] = -s[i];  // y = x*c - partner*s (first half), + (second)
     }
-    const bf16* qrow = a.q_in + tok * a.ldq_in + e0;
-    const bf16* krow = a.k_in + tok * a.ldk_in + e0;
-    bf16* qdst = a.q_out + tok * a.ldq_out + e0;
-    bf16* kdst = a.k_out + tok * a.ldk_out + e0;
     for (int h0 = 0; h0 < heads; h0 += UB) {
-      uint4 raw[UB];
-#pragma unroll
-      for (int j = 0; j < UB; ++j) {
-        const int h = h0 + j;
-        raw[j] = make_uint4(0u, 0u, 0u, 0u);
-        if (valid && h < heads) raw[j] = ld16(h < a.Hq ? qrow + h * HD : krow + (h - a.Hq) * HD);
-      }
+      if (h0 + UB < heads) load_batch(h0 + UB, nxt);
 #pragma unroll
       for (int j = 0; j < UB; ++j) {
         const int h = h0 + j;
         if (h >= heads) break;  // uniform over the CTA
         const bool is_q = h < a.Hq;
         float x[8];
-        unpack8(raw[j], x);
+        unpack8(cur[j], x);
         if (a.do_norm) {
           float ss = 0.f;
 #pragma unroll
@@ -116,8 +115,12 @@ __global__ void __launch_bounds__(kRowThreads, 2) qk_rope_fwd_kernel(RopeArgs a)
             if (is_q) a.q_rstd[tok * a.Hq + h] = rstd;
             else a.k_rstd[tok * a.Hk + (h - a.Hq)] = rstd;
           }
+          const float* wt = swt + (is_q ? 0 : HD) + e0;
+          const float4 w0 = *reinterpret_cast<const float4*>(wt);
+          const float4 w1 = *reinterpret_cast<const float4*>(wt + 4);
+          const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = bf16_round(x[i] * rstd) * (is_q ? wq[i] : wk[i]);
+          for (int i = 0; i < 8; ++i) x[i] = bf16_round(x[i] * rstd) * wl[i];
         }
         float y[8];
 #pragma unroll
@@ -127,6 +130,8 @@ __global__ void __launch_bounds__(kRowThreads, 2) qk_rope_fwd_kernel(RopeArgs a)
         }
         if (valid) st16(is_q ? qdst + h * HD : kdst + (h - a.Hq) * HD, pack8(y));
       }
+#pragma unroll
+      for (int j = 0; j < UB; ++j) cur[j] = nxt[j];
     }
   }
 }
@@ -305,7 +310,7 @@ extern "C" int lb_qk_norm_rope_fwd(const void* q_in, long long ldq_in, const voi
   auto grid_for = [&](int lph) {
     const long long tpb = kRowThreads / lph;
     long long g = (T + tpb - 1) / tpb;
-    const long long cap = 1LL * row_num_sms() * 8;
+    const long long cap = 1LL * row_num_sms() * 6;  // two waves at three CTAs per SM
     return int(g < cap ? g : cap);
   };
   if (hd == 128) qk_rope_fwd_kernel<128><<<grid_for(16), kRowThreads, 0, st>>>(a);
