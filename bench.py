@@ -54,7 +54,7 @@ PRESETS = {
         metric="pairs/sec & tokens/sec, Qwen3-4B embed TP2 x sharded DP bf16, max over ranks",
         label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
     "qwen3-8b-lora": dict(
-        model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16,
+        model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16, ac=True,
         metric="pairs/sec & tokens/sec, Qwen3-8B embed + LoRA r16, sharded DP bf16, 3 hard negatives, "
                "max over ranks",
         label="Qwen3-8B (36L, H4096, 32q/8kv heads, hd128, FFN12288, vocab 151936), random init, "
@@ -268,7 +268,9 @@ def run_ours(args):
         scheduler_type="constant", model_config=Qwen3Config(**preset["model"]),
         fused_projections=preset["lora_r"] == 0, collator=BenchCollator(), async_tp=tp > 1,
         lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0,
-        init_on_device=args.config != "qwen3-0.6b")
+        init_on_device=args.config != "qwen3-0.6b",
+        # the 8B model keeps ~3 GB of activations per layer at this batch: recompute the cheap ops
+        activation_checkpoint=bool(preset.get("ac", False)))
     device = engine.device
     n_batches = W + 2 * K
     # ranks of one tensor-parallel group see the same batch

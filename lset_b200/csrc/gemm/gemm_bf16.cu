@@ -93,9 +93,11 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  // per epilogue warp: a 32 x 32 fp32 block (row stride 33 words, conflict-free both ways) that
-  // turns "one row per lane" into "one 128-byte row segment per 8 lanes" for the fp32 reductions
-  static constexpr int EPI_STAGE_WORDS = 32 * 33;
+  // per epilogue warp: a staging block that turns "one row per lane" (the TMEM load layout) into
+  // "one 128-byte row segment per 8 lanes" for global memory: 32 x 32 fp32 (row stride 33 words)
+  // for the fp32 reductions, 32 rows x 64 bf16 columns (row stride 144 bytes) for bf16 stores;
+  // both strides are conflict-free for the lane-per-row writes and the 8-lanes-per-row reads
+  static constexpr int EPI_STAGE_WORDS = 32 * 36;
   static constexpr int EPI_STAGE_BYTES = 4 * EPI_STAGE_WORDS * 4;
   static constexpr int SMEM_BYTES =
       STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
@@ -114,6 +116,13 @@ __device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) 
 __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
                "f"(d)
+               : "memory");
+}
+
+// 8 bf16 values added into memory in one 16-byte reduction (packed bf16x2 lanes)
+__device__ __forceinline__ void red_add8_bf16(void* dst, const uint4& v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 
@@ -508,10 +517,19 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
                       static_cast<long long>(row % g.c_rows_per_peer) * g.ldc + col0;
             }
             if constexpr (sizeof(OutT) == 2) {
+              // this lane's 32 columns go to its row of the staging block (flushed below)
+              uint8_t* srow = reinterpret_cast<uint8_t*>(epi_stage + (warp - 2) * C::EPI_STAGE_WORDS) +
+                              lane * 144 + (c & 1) * 64;
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (col0 + 8 * j < g.N)
-                  store8_bf16(reinterpret_cast<__nv_bfloat16*>(dst) + 8 * j, v + 8 * j);
+              for (int j = 0; j < 4; ++j) {
+                uint4 pk;
+                pk.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+                pk.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                pk.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                pk.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                *reinterpret_cast<uint4*>(srow + 16 * j) = pk;
+              }
+              (void)dst;
             } else {
               float* fd = reinterpret_cast<float*>(dst);
               if (g.accumulate) {
@@ -524,6 +542,36 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
                         make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
               }
             }
+          }
+        }
+        if constexpr (sizeof(OutT) == 2 && EPI != EPI_LSE) {
+          // After every second 32-column chunk the warp writes its 32 x 64 block out: 8 lanes cover
+          // one 128-byte row segment, so each store instruction fills four whole lines.
+          if (c & 1) {
+            __syncwarp();
+            const uint8_t* sblk =
+                reinterpret_cast<const uint8_t*>(epi_stage + (warp - 2) * C::EPI_STAGE_WORDS);
+            const int rr = lane >> 3, cc = lane & 7;
+            const int colb = n0 + (c - 1) * 32 + cc * 8;
+            if (colb < g.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int lr = i * 4 + rr;
+                const int grow = m0 + q * 32 + lr;
+                if (grow < m_limit) {
+                  const uint4 pk = *reinterpret_cast<const uint4*>(sblk + lr * 144 + cc * 16);
+                  if (g.c_rows_per_peer > 0) {
+                    // reduce-scatter in bf16: the row's owner accumulates over NVLink
+                    OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
+                                 static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
+                    red_add8_bf16(base + colb, pk);
+                  } else {
+                    *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
+                  }
+                }
+              }
+            }
+            __syncwarp();
           }
         }
         if constexpr (sizeof(OutT) == 4 && EPI == EPI_STORE) {
@@ -643,7 +691,9 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   if (K <= 0) return -4;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -3;
   if (!out_fp32 && (ldc & 7)) return -3;
-  if (!out_fp32 && (accumulate || splits > 1)) return -5;
+  const bool scatter = c_peers != nullptr && c_rows_per_peer > 0;
+  if (!out_fp32 && !scatter && (accumulate || splits > 1)) return -5;
+  if (!out_fp32 && scatter) splits = 1;  // bf16 reduce-scatter: one pass over the contraction
 
   const int tiles_m = (M + BM - 1) / BM;
   const int sms = num_sms();
@@ -689,7 +739,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   g.kb_per_split = kb_per;
   g.status = status;
   if (c_peers != nullptr && c_rows_per_peer > 0) {
-    if (!out_fp32 || c_world > 8) return -3;
+    if (c_world > 8) return -3;
     for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);
     g.c_rows_per_peer = c_rows_per_peer;
     g.accumulate = 1;
@@ -837,6 +887,17 @@ int prep_loss(const void* Q, const void* Kd, int M, int N, int D, long long ldq,
 }  // namespace lb
 
 // Number of floats of scratch that lb_infonce_fwd needs for M queries against N passages.
+// Same with bf16 accumulators in the owners' buffers (red.global.add on packed bf16x2): half the
+// NVLink bytes of the fp32 form, for activations whose reduce-scatter would be bf16 anyway.
+extern "C" int lb_gemm_bf16_scatter16(const void* A, const void* B, const void* const* c_peers,
+                                      int world, int rows_per_peer, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int a_mn,
+                                      int b_mn, int bn, int* status, void* stream_) {
+  if (M != world * rows_per_peer) return -3;
+  return gemm_bf16_impl(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, 1, bn,
+                        status, stream_, c_peers, world, rows_per_peer);
+}
+
 // C[M, N] (bf16) = A · op(B) + A2 · op(B2) (+ bias) in one pass over the accumulator: the k-blocks
 // of the second pair are appended to the contraction. A [M, K] and A2 [M, K2] are K-major;
 // op(B) = Bᵀ for B [N, K], B2 [N, K2] (b_mn = 0) or B for B [K, N], B2 [K2, N] (b_mn = 1).

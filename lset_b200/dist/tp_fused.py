@@ -25,6 +25,7 @@ styles (lset/distributed/tp.py:9-11, lset/models/decoder/qwen3/parallel_plan.py:
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -62,11 +63,12 @@ class _AGBuf:
 
 
 class _RSBuf:
-    """Double-buffered fp32 accumulators of width N (any row count up to cap)."""
+    """Double-buffered accumulators of width N (any row count up to cap), fp32 or bf16."""
 
-    def __init__(self, cap, N, device, group):
+    def __init__(self, cap, N, device, group, dtype=torch.float32):
         self.cap = cap
-        self.acc = [symm.SymmBuffer(cap * N, torch.float32, device, group) for _ in range(2)]
+        self.dtype = dtype
+        self.acc = [symm.SymmBuffer(cap * N, dtype, device, group) for _ in range(2)]
         for a in self.acc:
             a.local.zero_()
         self.epoch = 0
@@ -90,6 +92,9 @@ class SPState:
         self.device = None
         self.fused = False
         self._token = None
+        # Reduce-scatter accumulators in bf16 (packed bf16x2 reductions over NVLink, half the bytes
+        # of fp32; the same precision as a bf16 reduce-scatter of a collective library) or fp32.
+        self.rs_bf16 = os.environ.get("LSET_B200_TP_RS_FP32", "0") != "1"
         if device is not None:
             self.bind(device)
         self._ag, self._rs, self._ag_epoch, self._retired = {}, {}, {}, []
@@ -124,11 +129,12 @@ class SPState:
         return b
 
     def rs_buf(self, rows, N) -> _RSBuf:
+        dtype = torch.bfloat16 if self.rs_bf16 else torch.float32
         b = self._rs.get(N)
-        if b is None or b.cap < rows:
+        if b is None or b.cap < rows or b.dtype != dtype:
             if b is not None:
                 self._retired.append(b)
-            b = self._rs[N] = _RSBuf(_capacity(rows), N, self.device, self.group)
+            b = self._rs[N] = _RSBuf(_capacity(rows), N, self.device, self.group, dtype)
             self.barrier()  # every rank's accumulators are cleared before anyone adds into them
         return b
 
@@ -194,16 +200,24 @@ def _gemm_rs(st: SPState, a, w, b_mn: bool):
     buf.epoch += 1
     acc = buf.acc[buf.epoch & 1]
     lib = nv.load()
-    rc = lib.lb_gemm_bf16_scatter(
-        nv.c_void_p(a.data_ptr()), nv.c_void_p(w.data_ptr()), acc.c_ptr_array(), nv.c_int(W),
-        nv.c_int(rows), nv.c_int(T), nv.c_int(N), nv.c_int(K), nv.c_ll(a.stride(0)),
-        nv.c_ll(w.stride(0)), nv.c_ll(N), nv.c_int(0), nv.c_int(1 if b_mn else 0), nv.c_int(1),
-        nv.c_int(0), nv.c_void_p(nv.status_word(a.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
+    if buf.dtype == torch.bfloat16:
+        rc = lib.lb_gemm_bf16_scatter16(
+            nv.c_void_p(a.data_ptr()), nv.c_void_p(w.data_ptr()), acc.c_ptr_array(), nv.c_int(W),
+            nv.c_int(rows), nv.c_int(T), nv.c_int(N), nv.c_int(K), nv.c_ll(a.stride(0)),
+            nv.c_ll(w.stride(0)), nv.c_ll(N), nv.c_int(0), nv.c_int(1 if b_mn else 0), nv.c_int(0),
+            nv.c_void_p(nv.status_word(a.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
+    else:
+        rc = lib.lb_gemm_bf16_scatter(
+            nv.c_void_p(a.data_ptr()), nv.c_void_p(w.data_ptr()), acc.c_ptr_array(), nv.c_int(W),
+            nv.c_int(rows), nv.c_int(T), nv.c_int(N), nv.c_int(K), nv.c_ll(a.stride(0)),
+            nv.c_ll(w.stride(0)), nv.c_ll(N), nv.c_int(0), nv.c_int(1 if b_mn else 0), nv.c_int(1),
+            nv.c_int(0), nv.c_void_p(nv.status_word(a.device).data_ptr()),
+            nv.c_void_p(nv.stream_ptr()))
     nv.check_rc(rc, "lb_gemm_bf16_scatter")
     nv.count_launch(1)
     st.barrier()                                          # every contribution has landed
     used = acc.local[:rows * N]
-    out = used.view(rows, N).to(torch.bfloat16)
+    out = used.view(rows, N).to(torch.bfloat16, copy=True)
     used.zero_()
     return out
 

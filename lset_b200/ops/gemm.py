@@ -195,7 +195,8 @@ class _LoRALinear(torch.autograd.Function):
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
         t = matmul_abt(x2, lora_a)                       # [T, r]
         ts = t * scale
-        y = matmul_ext(x2, w, ts, lora_b, bias=bias)      # x·Wᵀ + ts·Bᵀ
+        # kept across selective activation checkpointing like every other big GEMM output
+        y = run_expensive(lambda: matmul_ext(x2, w, ts, lora_b, bias=bias))   # x·Wᵀ + ts·Bᵀ
         ctx.save_for_backward(x2, ts, w, lora_a, lora_b)
         ctx.scale = scale
         ctx.has_bias = bias is not None
