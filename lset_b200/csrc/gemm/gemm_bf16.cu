@@ -354,10 +354,13 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           const char* src = static_cast<const char*>(g.b_peers[peer]);
           char* dst = static_cast<char*>(g.b_local) + 2LL * peer * g.n_local * g.ldb_peer;
           const long long total_vec = vec_per_row * (r1 - r0);
-          for (long long i0 = 0; i0 < total_vec; i0 += 32 * 8) {
-            uint4 buf[8];
+          // 16 x 16 bytes per lane in flight: a warp keeps 8 KB on the wire, which is what the
+          // NVLink round trip needs for two pull warps per SM to reach the link rate
+          constexpr int kPullDepth = 16;
+          for (long long i0 = 0; i0 < total_vec; i0 += 32 * kPullDepth) {
+            uint4 buf[kPullDepth];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < kPullDepth; ++u) {
               const long long i = i0 + u * 32 + lane;
               if (i < total_vec) {
                 const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
@@ -365,7 +368,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
               }
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < kPullDepth; ++u) {
               const long long i = i0 + u * 32 + lane;
               if (i < total_vec) {
                 const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;

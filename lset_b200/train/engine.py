@@ -95,7 +95,8 @@ class TrainingEngine:
                  learnable_temperature: bool = False, weight_decay: float = 0.01,
                  step_timeout_s: float = 0.0, device: Optional[str] = None, seed: int = 42,
                  max_seq_length: int = 512, tokenizer=None, num_workers: int = 0,
-                 jsonl_log: bool = False, init_std: float = 0.02, init_on_device: bool = False):
+                 jsonl_log: bool = False, init_std: float = 0.02, init_on_device: bool = False,
+                 max_inflight_steps: int = 2):
         if cuda_graph:
             from .cuda_graph import validate_cuda_graph_config
 
@@ -250,6 +251,8 @@ class TrainingEngine:
                 shuffle=self.sampler is None, collate_fn=self.collator, drop_last=True,
                 num_workers=num_workers, pin_memory=use_cuda, generator=gen)
         self.micro_step = 0
+        self.max_inflight_steps = max_inflight_steps
+        self._inflight = []
         self.epoch = 0
         # per-phase device timing (h2d / forward_backward / optimizer); LSET_B200_PROFILE=1 enables it
         self.timer = PhaseTimer(enabled=os.environ.get("LSET_B200_PROFILE", "0") == "1")
@@ -321,6 +324,21 @@ class TrainingEngine:
             self.task_optimizer.zero_grad()
         self.scheduler.step()
         self.optimizer.zero_grad()
+        self._limit_run_ahead()
+
+    def _limit_run_ahead(self) -> None:
+        """Keep the host at most ``max_inflight_steps`` optimizer steps ahead of the GPU. A host
+        that queues many steps ahead makes the caching allocator hold the blocks of all of them
+        (side-stream frees are deferred until their events complete) and fall back to fresh device
+        allocations, which are slow once peer access to many GPUs is enabled. Waiting on the event
+        of an older step costs nothing while the GPU is the bottleneck."""
+        if self.device.type != "cuda" or self.max_inflight_steps <= 0:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self._inflight.append(ev)
+        while len(self._inflight) > self.max_inflight_steps:
+            self._inflight.pop(0).synchronize()
 
     def train_step(self, batch: dict):
         """One micro-step from a host batch: H2D copy, forward/backward and, on the accumulation
