@@ -9,7 +9,8 @@ between iterations):
   ag_gemm      all-gather of token shards fused into the column-parallel GEMM (lb_gemm_bf16_ag)
                vs NCCL all_gather_into_tensor + the same GEMM kernel on local memory
   gemm_rs      row-parallel GEMM with the reduce-scatter fused into its epilogue
-               (lb_gemm_bf16_scatter, fp32 red.global.add to the owner) vs GEMM + NCCL reduce_scatter
+               (lb_gemm_bf16_scatter16: packed bf16x2 red.global.add to the owner; fp32 accumulators
+               with LSET_B200_TP_RS_FP32=1) vs GEMM + NCCL reduce_scatter
   zero_step    sharded-optimizer step on a 256 Mi-parameter group: gradient reduce-scatter + average
                + ‖g‖² (lb_reduce_shard_f32) and AdamW + bf16 push all-gather (lb_adamw_push) vs NCCL
                reduce_scatter_tensor + the single-GPU AdamW kernel + all_gather_into_tensor
@@ -112,8 +113,9 @@ def main():
 
         ms_f, ms_n = timed(fused, args.iters, flush), timed(nccl, args.iters, flush)
         flops = 2.0 * T * H * k_loc
-        link = 4.0 * (world - 1) * rows * H                       # outbound fp32 partial rows
-        hbm = 2.0 * (T * k_loc + H * k_loc) + 4.0 * rows * H * 2
+        acc_bytes = 2.0 if st.rs_bf16 else 4.0
+        link = acc_bytes * (world - 1) * rows * H                 # outbound partial rows
+        hbm = 2.0 * (T * k_loc + H * k_loc) + acc_bytes * rows * H * 2
         out.append(dict(path="gemm_rs", layer=name, T=T, K_local=k_loc, N=H, fused_ms=ms_f,
                         nccl_ms=ms_n, **roofline(ms_f, flops, hbm, link, peaks)))
     nv.check_status(dev)
