@@ -95,3 +95,21 @@ def test_task_joint_encode_equals_separate():
     assert torch.allclose(a["query_embeds"], b["query_embeds"], atol=1e-5)
     lm = BiEncoderTask()(m, q, d, labels=torch.eye(2))
     assert torch.allclose(lm["loss"], BiEncoderTask()(m, q, d)["loss"], atol=1e-5)
+
+
+def test_fused_dispatcher_follows_reference_thresholds_and_falls_back_on_cpu():
+    from lset_b200.losses import fused_contrastive_loss
+    from lset_b200.ops.loss import reference_switches_to_fused
+
+    # sizes from which the reference replaces the eager label loss by its fused kernel
+    assert not reference_switches_to_fused(1023, 10**6, "multi")
+    assert reference_switches_to_fused(1024, 4096, "multi") and not reference_switches_to_fused(1024, 4095, "multi")
+    assert reference_switches_to_fused(2048, 8, "multi")
+    assert reference_switches_to_fused(2048, 4096, "soft") and not reference_switches_to_fused(4096, 4095, "cross")
+    # on the CPU (no streaming kernels) the dispatcher is the label-matrix loss itself
+    q, d = _emb(3, 8, 20), _emb(5, 8, 21)
+    labels = torch.tensor([[1., 0, 0, -1, 0], [0, 1, 1, 0, 0], [0, 0, 0, 0, 1]])
+    qi, di = (labels > 0).nonzero(as_tuple=True)
+    a = fused_contrastive_loss(q, d, labels, 0.1, pos_qi=qi, pos_di=di, force_fused=True)
+    b = contrastive_loss(q, d, labels, 0.1)
+    assert torch.allclose(a, b)
