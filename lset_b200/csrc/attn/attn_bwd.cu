@@ -218,23 +218,6 @@ __global__ void __launch_bounds__(kBwdThreads)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int half = warp >> 2;  // which 32 of the 64 KV columns this thread handles
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_dq, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-
   auto load_kv = [&](int j) {
     mbar_expect_tx(bar_kv, 2 * C::KV_BYTES);
 #pragma unroll
@@ -245,7 +228,13 @@ __global__ void __launch_bounds__(kBwdThreads)
                   seq0 + j * kAttnKvBlock);
     }
   };
+  // first loads before the TMEM allocation and the CTA barrier: their latency runs under the set-up
   if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_dq, 1);
+    mbar_fence_init();
     mbar_expect_tx(bar_q, 2 * C::Q_BYTES);
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -257,6 +246,15 @@ __global__ void __launch_bounds__(kBwdThreads)
       }
     load_kv(0);
   }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
 
   const int r = tid & 127;
   const int g = r / QT;
@@ -421,23 +419,6 @@ __global__ void __launch_bounds__(kBwdThreads)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int half = warp >> 2;
-  if (tid == 0) {
-    mbar_init(bar_kv, 1);
-    for (int i = 0; i < C::QBUFS; ++i) mbar_init(&bar_q[i], 1);
-    mbar_init(&bar_s[0], 1);
-    mbar_init(&bar_s[1], 1);
-    mbar_init(bar_acc, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
   constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
   constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
 
@@ -454,6 +435,34 @@ __global__ void __launch_bounds__(kBwdThreads)
                   seq0 + qb * 64);
     }
   };
+  // Barriers, then the K / V tile and the first two (Q, dO) blocks are requested before the TMEM
+  // allocation and the CTA barrier, so the load latency runs under that set-up.
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    for (int i = 0; i < C::QBUFS; ++i) mbar_init(&bar_q[i], 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(bar_acc, 1);
+    mbar_fence_init();
+    mbar_expect_tx(bar_kv, 2 * C::KV_BYTES);
+#pragma unroll
+    for (int p = 0; p < C::PANELS; ++p) {
+      tma_load_2d(sK + p * (128 * 128), &tmK, bar_kv, hk * HD + p * 64, seq0 + kv0);
+      tma_load_2d(sV + p * (128 * 128), &tmV, bar_kv, hk * HD + p * 64, seq0 + kv0);
+    }
+    if (n_inner > 0) load_q(0);
+    if (n_inner > 1) load_q(1);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+
   // Sᵀ = K·Qᵀ and dPᵀ = V·dOᵀ of inner step i into TMEM buffer i & 1 (issued by thread 0).
   auto issue_scores = [&](int i) -> bool {
     const int buf = i % C::QBUFS;
@@ -484,16 +493,6 @@ __global__ void __launch_bounds__(kBwdThreads)
     return true;
   };
 
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * C::KV_BYTES);
-#pragma unroll
-    for (int p = 0; p < C::PANELS; ++p) {
-      tma_load_2d(sK + p * (128 * 128), &tmK, bar_kv, hk * HD + p * 64, seq0 + kv0);
-      tma_load_2d(sV + p * (128 * 128), &tmV, bar_kv, hk * HD + p * 64, seq0 + kv0);
-    }
-    if (n_inner > 0) load_q(0);
-    if (n_inner > 1) load_q(1);
-  }
   const int r = tid & 127;
   const int kvpos = kv0 + r;
   const bool row_valid = kvpos < len;

@@ -80,24 +80,6 @@ __global__ void __launch_bounds__(128)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(&bar_kv[0], 1);
-    mbar_init(&bar_kv[1], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
-
   auto load_kv = [&](int j) {
     const int buf = j & 1;
     mbar_expect_tx(&bar_kv[buf], 2 * C::KV_BYTES);
@@ -110,7 +92,15 @@ __global__ void __launch_bounds__(128)
     }
   };
 
+  // The first loads are issued before the TMEM allocation and the CTA-wide barrier, so their
+  // latency runs under that set-up instead of after it.
   if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(&bar_kv[0], 1);
+    mbar_init(&bar_kv[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_fence_init();
     mbar_expect_tx(bar_q, C::Q_BYTES);
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -119,6 +109,15 @@ __global__ void __launch_bounds__(128)
                     seq0 + q0);
     load_kv(0);
   }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
 
   const int r = tid;
   const int g = r / QT;

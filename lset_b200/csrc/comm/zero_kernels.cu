@@ -199,3 +199,46 @@ extern "C" int lb_adamw_push(float* p, const float* g, float* m, float* v,
   adamw_push_kernel<<<comm_grid(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   return launch_rc();
 }
+
+// ------------------------------------------------------------------------------------------------
+// take_clear: out (bf16) = acc, acc = 0 in one pass. The reduce-scatter accumulators of the fused
+// tensor-parallel GEMMs are read once and must be zero again before their next use.
+namespace lb {
+namespace {
+
+template <bool ACC_FP32>
+__global__ void __launch_bounds__(256)
+    take_clear_kernel(void* __restrict__ acc, bf16* __restrict__ out, long long n8) {
+  for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += 1LL * gridDim.x * blockDim.x) {
+    if constexpr (ACC_FP32) {
+      float4* a = reinterpret_cast<float4*>(acc) + 2 * i;
+      const float4 x = a[0], y = a[1];
+      const float v[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
+      st16(out + 8 * i, pack8(v));
+      a[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      uint4* a = reinterpret_cast<uint4*>(acc) + i;
+      st16(out + 8 * i, *a);
+      *a = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace lb
+
+// acc: n elements (fp32 when acc_fp32, else bf16), out: n bf16; n a multiple of 8, both 16-byte
+// aligned.
+extern "C" int lb_take_clear(void* acc, void* out, long long n, int acc_fp32, void* stream) {
+  if (n <= 0) return 0;
+  if (n & 7) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = comm_grid(n / 8);
+  if (acc_fp32)
+    take_clear_kernel<true><<<grid, 256, 0, st>>>(acc, reinterpret_cast<bf16*>(out), n / 8);
+  else
+    take_clear_kernel<false><<<grid, 256, 0, st>>>(acc, reinterpret_cast<bf16*>(out), n / 8);
+  return launch_rc();
+}

@@ -69,10 +69,14 @@ class DeviceBarrier:
     matters for ops that need one ordering point each (fused tensor-parallel GEMMs, the cross-rank
     loss). ``LSET_B200_DEVICE_BARRIER=0`` falls back to the all-reduce."""
 
-    def __init__(self, device: torch.device, group=None, limit_s: float = 2.0):
+    def __init__(self, device: torch.device, group=None, limit_s: Optional[float] = None):
         self.group = group if group is not None else dist.group.WORLD
         self.device = torch.device(device)
-        self.limit_ns = int(limit_s * 1e9)
+        # Ranks reach a barrier at different times (host-side skew of the first steps, allocator
+        # stalls); the wait is bounded all the same: 5 s at most (the kernel accepts no more).
+        if limit_s is None:
+            limit_s = float(os.environ.get("LSET_B200_BARRIER_TIMEOUT_S", "5"))
+        self.limit_ns = int(min(max(limit_s, 0.001), 5.0) * 1e9)
         self.epoch = 0
         self.pad = None
         self._token = None

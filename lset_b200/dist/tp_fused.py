@@ -216,9 +216,19 @@ def _gemm_rs(st: SPState, a, w, b_mn: bool):
     nv.check_rc(rc, "lb_gemm_bf16_scatter")
     nv.count_launch(1)
     st.barrier()                                          # every contribution has landed
-    used = acc.local[:rows * N]
-    out = used.view(rows, N).to(torch.bfloat16, copy=True)
-    used.zero_()
+    # read the reduced rows and leave the accumulator zero for its next use, in one pass
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
+    n = rows * N
+    if n % 8 == 0:
+        rc = lib.lb_take_clear(nv.c_void_p(acc.local.data_ptr()), nv.c_void_p(out.data_ptr()),
+                               nv.c_ll(n), nv.c_int(int(buf.dtype == torch.float32)),
+                               nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_take_clear")
+        nv.count_launch(1)
+    else:
+        used = acc.local[:n]
+        out.copy_(used.view(rows, N))
+        used.zero_()
     return out
 
 
