@@ -1,6 +1,8 @@
 // Varlen (packed) flash attention forward on tcgen05: causal or bidirectional, grouped-query heads.
 //
-// One 128-thread CTA per (sequence, query tile, KV head); two CTAs share an SM. Per KV block of 64:
+// Persistent 128-thread CTAs (two per SM) walk over the (KV head, sequence, query tile) work items;
+// TMEM and the barriers are set up once per CTA and the next item's Q and first K/V block are
+// requested during the last block of the current one. Per KV block of 64:
 //   S = Q·Kᵀ          tcgen05.mma, A = Q tile (128 x hd), B = K block (64 x hd), S in TMEM
 //   online softmax     thread r owns row r: tcgen05.ld, mask, running max / sum in registers;
 //                      the O accumulator in TMEM is rescaled only when the max moved by > 2^8
@@ -46,23 +48,34 @@ struct FwdCfg {
   static constexpr int O_COL = 64;
 };
 
+// Work item w of the persistent grid: KV head w / tiles, query tile w % tiles of the plan.
+struct FwdTile {
+  int seq0, len, q0, nblk, hk;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(128)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, AttnFwdArgs a) {
   using C = FwdCfg<HD>;
   AttnPlanView plan{a.plan};
-  if (int(blockIdx.x) >= plan.count()) return;
-  const int b = plan.seq(blockIdx.x);
-  const int qt = plan.tile(blockIdx.x);
-  const int hk = blockIdx.y;
+  const int tiles = plan.count();
+  const int total = tiles * a.Hk;
+  if (int(blockIdx.x) >= total) return;
   const int G = a.Hq / a.Hk;
   const int QT = 128 / G;
-  const int seq0 = a.seq_start[b];
-  const int len = a.seq_end[b] - seq0;
-  const int q0 = qt * QT;
-  const int kv_end = a.causal ? min(len, q0 + QT) : len;
-  const int nblk = (kv_end + kAttnKvBlock - 1) / kAttnKvBlock;
+  auto decode = [&](int w) {
+    FwdTile t;
+    t.hk = w / tiles;
+    const int i = w - t.hk * tiles;
+    const int b = plan.seq(i);
+    t.seq0 = a.seq_start[b];
+    t.len = a.seq_end[b] - t.seq0;
+    t.q0 = plan.tile(i) * QT;
+    const int kv_end = a.causal ? min(t.len, t.q0 + QT) : t.len;
+    t.nblk = (kv_end + kAttnKvBlock - 1) / kAttnKvBlock;
+    return t;
+  };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -80,18 +93,30 @@ __global__ void __launch_bounds__(128)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  auto load_kv = [&](int j) {
-    const int buf = j & 1;
+
+  // KV block n of this CTA's whole run (all tiles) lives in slot n & 1; its barrier phase is
+  // (n >> 1) & 1. The score and P·V barriers complete once per block: phase n & 1.
+  auto load_kv = [&](const FwdTile& t, int j, int n) {
+    const int buf = n & 1;
     mbar_expect_tx(&bar_kv[buf], 2 * C::KV_BYTES);
 #pragma unroll
     for (int p = 0; p < C::PANELS; ++p) {
       tma_load_2d(sK + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmK, &bar_kv[buf],
-                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
+                  t.hk * HD + p * 64, t.seq0 + j * kAttnKvBlock);
       tma_load_2d(sV + buf * C::KV_BYTES + p * (kAttnKvBlock * 128), &tmV, &bar_kv[buf],
-                  hk * HD + p * 64, seq0 + j * kAttnKvBlock);
+                  t.hk * HD + p * 64, t.seq0 + j * kAttnKvBlock);
     }
   };
+  auto load_q = [&](const FwdTile& t) {
+    mbar_expect_tx(bar_q, C::Q_BYTES);
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int p = 0; p < C::PANELS; ++p)
+        tma_load_2d(sQ + p * (128 * 128) + g * QT * 128, &tmQ, bar_q,
+                    (t.hk * G + g) * HD + p * 64, t.seq0 + t.q0);
+  };
 
+  FwdTile cur = decode(blockIdx.x);
   // The first loads are issued before the TMEM allocation and the CTA-wide barrier, so their
   // latency runs under that set-up instead of after it.
   if (tid == 0) {
@@ -101,13 +126,8 @@ __global__ void __launch_bounds__(128)
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     mbar_fence_init();
-    mbar_expect_tx(bar_q, C::Q_BYTES);
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int p = 0; p < C::PANELS; ++p)
-        tma_load_2d(sQ + p * (128 * 128) + g * QT * 128, &tmQ, bar_q, (hk * G + g) * HD + p * 64,
-                    seq0 + q0);
-    load_kv(0);
+    load_q(cur);
+    load_kv(cur, 0, 0);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -118,159 +138,177 @@ __global__ void __launch_bounds__(128)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+  constexpr uint32_t idesc_s = umma_idesc_bf16(128, kAttnKvBlock, 0, 0);
+  constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
 
   const int r = tid;
   const int g = r / QT;
-  const int qpos = q0 + r % QT;
-  const bool row_valid = qpos < len;
-  float m_ref = -INFINITY;
-  float l_sum = 0.f;
-  constexpr uint32_t idesc_s = umma_idesc_bf16(128, kAttnKvBlock, 0, 0);
-  constexpr uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
   bool failed = false;
+  int n = 0;  // KV blocks processed so far by this CTA (over all its tiles)
 
-  {
-    const bool ok = mbar_wait(bar_q, 0);
-    if (__syncthreads_or(!ok)) {
-      report_status(a.status, kStatusTimeoutProducer);
-      failed = true;
-    }
-  }
+  // Persistent loop: TMEM and the barriers are set up once; the Q tile and the first K/V block of
+  // the next work item are requested while the current one is still in its last block.
+  for (int w = blockIdx.x, it = 0; w < total && !failed; w += gridDim.x, ++it) {
+    const bool has_next = w + int(gridDim.x) < total;
+    const FwdTile nxt = has_next ? decode(w + gridDim.x) : cur;
+    const int qpos = cur.q0 + r % QT;
+    const bool row_valid = qpos < cur.len;
+    const int len = cur.len;
+    const int nblk = cur.nblk;
+    float m_ref = -INFINITY;
+    float l_sum = 0.f;
 
-  for (int j = 0; j < nblk && !failed; ++j) {
-    const int buf = j & 1;
-    // 1. K/V block landed -> S = Q K^T
     {
-      const bool ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1);
+      const bool ok = mbar_wait(bar_q, it & 1);
       if (__syncthreads_or(!ok)) {
         report_status(a.status, kStatusTimeoutProducer);
         failed = true;
         break;
       }
     }
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t qa = smem_u32(sQ);
-      const uint32_t ka = smem_u32(sK + buf * C::KV_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint64_t ad = umma_smem_desc(qa + (ks / 4) * (128 * 128) + (ks % 4) * 32, 16, 1024);
-        const uint64_t bd =
-            umma_smem_desc(ka + (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32, 16, 1024);
-        umma_bf16(tmem_base, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_s);
-    }
-    // 2. softmax statistics of this block
-    {
-      const bool ok = mbar_wait(bar_s, j & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
-      }
-    }
-    tc_fence_after();
-    float s[kAttnKvBlock];
-    {
-      uint32_t t0[32], t1[32];
-      tmem_ld_32x32b_x32(tmem_row, t0);
-      tmem_ld_32x32b_x32(tmem_row + 32, t1);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        s[c] = __uint_as_float(t0[c]);
-        s[32 + c] = __uint_as_float(t1[c]);
-      }
-    }
-    float mx = -INFINITY;
-    const int kv0 = j * kAttnKvBlock;
-#pragma unroll
-    for (int c = 0; c < kAttnKvBlock; ++c) {
-      const int kvpos = kv0 + c;
-      const bool valid = row_valid && kvpos < len && (!a.causal || kvpos <= qpos);
-      s[c] = valid ? s[c] * a.scale_log2 : -INFINITY;
-      mx = fmaxf(mx, s[c]);
-    }
-    // 3. previous P·V finished: its K/V/P slots are free and O may be touched
-    if (j > 0) {
-      const bool ok = mbar_wait(bar_o, (j - 1) & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
-      }
-      tc_fence_after();
-    }
-    if (tid == 0 && j + 1 < nblk) load_kv(j + 1);
-    // 4. lazy rescale, P -> shared memory
-    const float m_new = fmaxf(m_ref, mx);
-    const bool need = m_new > m_ref + 8.f;
-    if (__any_sync(0xffffffffu, need)) {
-      const float alpha = (m_new == -INFINITY) ? 1.f
-                          : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new));
-      l_sum *= alpha;
-      m_ref = m_new;
-      if (j > 0) {
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
-        }
-        tmem_st_wait();
-      }
-    }
-    const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-    uint8_t* sP = C::P_IN_K ? (sK + buf * C::KV_BYTES) : sPx;
-#pragma unroll
-    for (int c8 = 0; c8 < kAttnKvBlock / 8; ++c8) {
-      float p[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        p[i] = exp2f(s[c8 * 8 + i] - m_use);
-        l_sum += p[i];
-      }
-      uint4 q;
-      q.x = pack_bf16x2(p[0], p[1]);
-      q.y = pack_bf16x2(p[2], p[3]);
-      q.z = pack_bf16x2(p[4], p[5]);
-      q.w = pack_bf16x2(p[6], p[7]);
-      *reinterpret_cast<uint4*>(sP + swz128_offset(r, c8)) = q;
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    // 5. O += P V
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t pa = smem_u32(sP);
-      const uint32_t va = smem_u32(sV + buf * C::KV_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < kAttnKvBlock / 16; ++ks) {
-        const uint64_t ad = umma_smem_desc(pa + ks * 32, 16, 1024);
-        const uint64_t bd = umma_smem_desc(va + ks * 2048, kAttnKvBlock * 128, 1024);
-        umma_bf16(tmem_base + C::O_COL, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-      }
-      umma_commit(bar_o);
-    }
-  }
 
-  if (!failed) {
-    const bool ok = mbar_wait(bar_o, (nblk - 1) & 1);
-    if (__syncthreads_or(!ok)) {
-      report_status(a.status, kStatusTimeoutMma);
-      failed = true;
+    for (int j = 0; j < nblk; ++j, ++n) {
+      const int buf = n & 1;
+      const bool last = j + 1 == nblk;
+      // 1. K/V block landed -> S = Q K^T
+      {
+        const bool ok = mbar_wait(&bar_kv[buf], (n >> 1) & 1);
+        if (__syncthreads_or(!ok)) {
+          report_status(a.status, kStatusTimeoutProducer);
+          failed = true;
+          break;
+        }
+      }
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ);
+        const uint32_t ka = smem_u32(sK + buf * C::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t ad = umma_smem_desc(qa + (ks / 4) * (128 * 128) + (ks % 4) * 32, 16, 1024);
+          const uint64_t bd =
+              umma_smem_desc(ka + (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32, 16, 1024);
+          umma_bf16(tmem_base, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s);
+      }
+      // 2. softmax statistics of this block
+      {
+        const bool ok = mbar_wait(bar_s, n & 1);
+        if (__syncthreads_or(!ok)) {
+          report_status(a.status, kStatusTimeoutMma);
+          failed = true;
+          break;
+        }
+      }
+      tc_fence_after();
+      // the last score product of this tile has read Q: the next tile's Q may land now
+      if (tid == 0 && last && has_next) load_q(nxt);
+      float s[kAttnKvBlock];
+      {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32b_x32(tmem_row, t0);
+        tmem_ld_32x32b_x32(tmem_row + 32, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          s[c] = __uint_as_float(t0[c]);
+          s[32 + c] = __uint_as_float(t1[c]);
+        }
+      }
+      float mx = -INFINITY;
+      const int kv0 = j * kAttnKvBlock;
+#pragma unroll
+      for (int c = 0; c < kAttnKvBlock; ++c) {
+        const int kvpos = kv0 + c;
+        const bool valid = row_valid && kvpos < len && (!a.causal || kvpos <= qpos);
+        s[c] = valid ? s[c] * a.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, s[c]);
+      }
+      // 3. previous P·V finished: its K/V/P slots are free and O may be touched (for the first
+      //    block of a tile the previous tile's epilogue has already waited for it)
+      if (j > 0) {
+        const bool ok = mbar_wait(bar_o, (n - 1) & 1);
+        if (__syncthreads_or(!ok)) {
+          report_status(a.status, kStatusTimeoutMma);
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+      }
+      if (tid == 0) {
+        if (!last) load_kv(cur, j + 1, n + 1);
+        else if (has_next) load_kv(nxt, 0, n + 1);  // first block of the next work item
+      }
+      // 4. lazy rescale, P -> shared memory
+      const float m_new = fmaxf(m_ref, mx);
+      const bool need = m_new > m_ref + 8.f;
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = (m_new == -INFINITY) ? 1.f
+                            : (m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new));
+        l_sum *= alpha;
+        m_ref = m_new;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_row + C::O_COL + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      uint8_t* sP = C::P_IN_K ? (sK + buf * C::KV_BYTES) : sPx;
+#pragma unroll
+      for (int c8 = 0; c8 < kAttnKvBlock / 8; ++c8) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          p[i] = exp2f(s[c8 * 8 + i] - m_use);
+          l_sum += p[i];
+        }
+        uint4 q;
+        q.x = pack_bf16x2(p[0], p[1]);
+        q.y = pack_bf16x2(p[2], p[3]);
+        q.z = pack_bf16x2(p[4], p[5]);
+        q.w = pack_bf16x2(p[6], p[7]);
+        *reinterpret_cast<uint4*>(sP + swz128_offset(r, c8)) = q;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      // 5. O += P V
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP);
+        const uint32_t va = smem_u32(sV + buf * C::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < kAttnKvBlock / 16; ++ks) {
+          const uint64_t ad = umma_smem_desc(pa + ks * 32, 16, 1024);
+          const uint64_t bd = umma_smem_desc(va + ks * 2048, kAttnKvBlock * 128, 1024);
+          umma_bf16(tmem_base + C::O_COL, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(bar_o);
+      }
     }
-  }
-  if (!failed) {
+    if (failed) break;
+
+    {
+      const bool ok = mbar_wait(bar_o, (n - 1) & 1);
+      if (__syncthreads_or(!ok)) {
+        report_status(a.status, kStatusTimeoutMma);
+        failed = true;
+        break;
+      }
+    }
     tc_fence_after();
     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-    const long long tok = 1LL * seq0 + qpos;
-    bf16* orow = a.O + tok * a.ldo + (hk * G + g) * HD;
+    const long long tok = 1LL * cur.seq0 + qpos;
+    bf16* orow = a.O + tok * a.ldo + (cur.hk * G + g) * HD;
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t o[32];
@@ -289,8 +327,12 @@ __global__ void __launch_bounds__(128)
       }
     }
     if (row_valid && a.lse != nullptr)
-      a.lse[1LL * (hk * G + g) * a.T + tok] =
+      a.lse[1LL * (cur.hk * G + g) * a.T + tok] =
           (l_sum > 0.f) ? (m_ref * kLn2F + logf(l_sum)) : -INFINITY;
+    // the accumulator reads above are ordered before the next tile's MMAs (issued by thread 0
+    // after the CTA barrier at the top of the next tile)
+    tc_fence_before();
+    cur = nxt;
   }
   tc_fence_before();
   __syncthreads();
@@ -344,7 +386,17 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
       return -10;
     configured = true;
   }
-  dim3 grid(max_tiles, a.Hk);
+  // persistent: as many CTAs as fit at once (shared memory allows two per SM at head_dim <= 128),
+  // never more than the upper bound of the work items; a CTA beyond the real count exits at once
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long upper = 1LL * max_tiles * a.Hk;
+  const long long resident = 1LL * sms * (C::SMEM_BYTES <= 113 * 1024 ? 2 : 1);
+  const int grid = static_cast<int>(upper < resident ? upper : resident);
   kern<<<grid, 128, C::SMEM_BYTES, st>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
