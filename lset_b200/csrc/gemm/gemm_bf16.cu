@@ -66,6 +66,13 @@ struct GemmArgs {
   //    sigmoid(s - lse) - 1, of a negative exp(s - lse) * row_scale (row_scale = sum over the
   //    row's positives of sigmoid(lse - s_p)).
   int loss_mode;
+  // EPI_GLU: B = fused [gate; up] weight [2 * glu_I, K]; N = glu_I features. A 128 x 256 tile holds
+  // gate and up of the same 128 features side by side; the epilogue stores both halves into
+  // C = gate_up [M, 2 * glu_I] (for the backward) and act(gate) * up into glu_h [M, glu_I].
+  int glu_I;
+  void* glu_h;
+  long long ld_h;
+  int glu_kind;  // 0 = SwiGLU, 1 = tanh-GeGLU
   // ---- peer gather (GATHER 1: rows of B, GATHER 2: rows of A): the rows live in `world` ranks'
   // buffers, n_local rows each; two extra warps pull them into b_local ([world * n_local, K], the
   // base of that operand's tensor map) and publish one flag per (rank, row tile); tiles are
@@ -84,7 +91,7 @@ struct GemmArgs {
   int* status;
 };
 
-enum { EPI_STORE = 0, EPI_LSE = 1, EPI_PGRAD = 2 };
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_PGRAD = 2, EPI_GLU = 3 };
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int BN>
@@ -177,7 +184,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   constexpr int kPullRows = 16;  // rows per pull item (one warp); divides BM and BN
   [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 0;
   const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
-  const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + BN - 1) / BN;
+  constexpr int kTileN = EPI == EPI_GLU ? 128 : BN;  // output features (columns) per tile
+  const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + kTileN - 1) / kTileN;
   const int kb_main = (g.K + BK - 1) / BK;
   const int kb_total = kb_main + g.kb_ext;
   const int total = tiles_m * tiles_n * g.splits;
@@ -197,7 +205,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       m0 = peer * g.n_local + (mi % tiles_per_peer) * BM;
     } else {
       m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * BM;
-      n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BN;
+      n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * kTileN;
       chunk = 0;
     }
   };
@@ -269,6 +277,10 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
               tma_load_2d(sb + c * (BK * 128), tb, &full[stage], n0 + 64 * c, kc);
+          } else if constexpr (EPI == EPI_GLU) {
+            // gate rows and up rows of the same 128 features, side by side in the B tile
+            tma_load_2d(sb, tb, &full[stage], kc, n0);
+            tma_load_2d(sb + 128 * 128, tb, &full[stage], kc, g.glu_I + n0);
           } else {
             tma_load_2d(sb, tb, &full[stage], kc, n0);
           }
@@ -404,6 +416,88 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         break;
       }
       tc_fence_after();
+      if constexpr (EPI == EPI_GLU) {
+        // gate chunk c and up chunk c of the tile -> gate_up (both halves) and h = act(gate) * up.
+        // Values are rounded to bf16 before the activation, as the stand-alone GLU kernel sees them.
+        uint8_t* sblk = reinterpret_cast<uint8_t*>(epi_stage + (warp - 2) * C::EPI_STAGE_WORDS);
+        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(g.C);
+        __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(g.glu_h);
+        const int I = g.glu_I;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, rg);
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + 128 + c * 32, ru);
+          tmem_ld_wait();
+          const int f = n0 + c * 32;
+          if (f >= I) continue;  // uniform over the warp
+          uint32_t pg[16], pu[16], ph[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            pg[j] = pack_bf16x2(__uint_as_float(rg[2 * j]), __uint_as_float(rg[2 * j + 1]));
+            pu[j] = pack_bf16x2(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1]));
+            const float2 gv = unpack_bf16x2(pg[j]), uv = unpack_bf16x2(pu[j]);
+            float a0, a1;
+            if (g.glu_kind == 0) {
+              a0 = gv.x * (1.f / (1.f + __expf(-gv.x)));
+              a1 = gv.y * (1.f / (1.f + __expf(-gv.y)));
+            } else {
+              const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+              a0 = 0.5f * gv.x * (1.f + tanhf(k0 * (gv.x + k1 * gv.x * gv.x * gv.x)));
+              a1 = 0.5f * gv.y * (1.f + tanhf(k0 * (gv.y + k1 * gv.y * gv.y * gv.y)));
+            }
+            ph[j] = pack_bf16x2(a0 * uv.x, a1 * uv.y);
+          }
+          uint8_t* srow = sblk + lane * 144;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            *reinterpret_cast<uint4*>(srow + 16 * j) =
+                make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
+            *reinterpret_cast<uint4*>(srow + 64 + 16 * j) =
+                make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
+          }
+          __syncwarp();
+          {
+            const int rr = lane >> 3, cc = lane & 7;
+            const int fcol = f + (cc & 3) * 8;
+            const long long col = (cc < 4 ? 0 : I) + fcol;
+            if (fcol < I) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int lr = i * 4 + rr;
+                const int grow = m0 + q * 32 + lr;
+                if (grow < g.M)
+                  *reinterpret_cast<uint4*>(gu + static_cast<long long>(grow) * g.ldc + col) =
+                      *reinterpret_cast<const uint4*>(sblk + lr * 144 + cc * 16);
+              }
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(srow + 16 * j) =
+                make_uint4(ph[4 * j], ph[4 * j + 1], ph[4 * j + 2], ph[4 * j + 3]);
+          __syncwarp();
+          {
+            const int rr = lane >> 2, cc = lane & 3;
+            const int fcol = f + cc * 8;
+            if (fcol < I) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int lr = i * 8 + rr;
+                const int grow = m0 + q * 32 + lr;
+                if (grow < g.M)
+                  *reinterpret_cast<uint4*>(hout + static_cast<long long>(grow) * g.ld_h + fcol) =
+                      *reinterpret_cast<const uint4*>(sblk + lr * 144 + cc * 16);
+              }
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty[acc]);
+        continue;
+      }
       const int row = m0 + q * 32 + lane;
       const bool add_bias = (g.bias != nullptr) && (split == 0);
       [[maybe_unused]] float m_run = -INFINITY, l_run = 0.f, pos_val = 0.f;
@@ -899,6 +993,43 @@ extern "C" int lb_gemm_bf16_scatter16(const void* A, const void* B, const void* 
   if (M != world * rows_per_peer) return -3;
   return gemm_bf16_impl(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, 1, bn,
                         status, stream_, c_peers, world, rows_per_peer);
+}
+
+// Gated-MLP input projection with the activation in the epilogue: gate_up [M, 2I] = A · Wᵀ for the
+// fused weight W = [gate; up] ([2I, K]) and h [M, I] = act(gate) * up, act = SiLU (kind 0) or
+// tanh-GELU (kind 1). gate_up is written too: the backward of the activation needs it.
+extern "C" int lb_gemm_glu(const void* A, const void* W, void* gate_up, void* h, int M, int I, int K,
+                           long long lda, long long ldw, long long ld_gu, long long ld_h, int kind,
+                           int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || I <= 0) return 0;
+  if (K <= 0) return -4;
+  if ((I & 7) || (lda & 7) || (ldw & 7) || (ld_gu & 7) || (ld_h & 7)) return -3;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, W, 2, (uint64_t)K, (uint64_t)2 * I, (uint64_t)ldw * 2, BK, 128, true);
+  if (rc) return rc;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (I + 127) / 128;
+  GemmArgs g{};
+  g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
+  g.M = M;
+  g.N = I;
+  g.K = K;
+  g.C = gate_up;
+  g.ldc = ld_gu;
+  g.splits = 1;
+  g.kb_per_split = (K + BK - 1) / BK;
+  g.glu_I = I;
+  g.glu_h = h;
+  g.ld_h = ld_h;
+  g.glu_kind = kind;
+  g.status = status;
+  const long long total = 1LL * tiles_m * tiles_n;
+  const int sms = num_sms();
+  const int grid = (int)(total < sms ? total : sms);
+  return launch<0, 0, 256, __nv_bfloat16, EPI_GLU>(tmA, tmB, g, grid, stream);
 }
 
 // C[M, N] (bf16) = A · op(B) + A2 · op(B2) (+ bias) in one pass over the accumulator: the k-blocks

@@ -23,6 +23,7 @@ from ..ops import embedding as emb_ops
 from ..ops import gemm as gemm_ops
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
+from ..ops.runtime_options import enabled
 
 
 class Linear(nn.Linear):
@@ -176,7 +177,14 @@ class GatedMLP(nn.Module):
 
     def forward(self, x):
         if self.fused_gate_up:
-            h = act_ops.glu(self.gate_up_proj(x), self.kind)
+            gu = self.gate_up_proj
+            # plain bf16 projection on the GPU: the activation rides in the GEMM epilogue; wrapped
+            # layers (tensor parallel, LoRA, quantised) go through their own forward
+            if (type(gu) is Linear and gu.bias is None and "forward" not in gu.__dict__
+                    and gemm_ops.linear_glu_supported(x, gu.weight) and enabled("fused_glu_gemm")):
+                h = gemm_ops.linear_glu(x, gu.weight, self.kind)
+                return self.down_proj(h)
+            h = act_ops.glu(gu(x), self.kind)
         elif self.kind == "swiglu":
             h = act_ops.swiglu(self.gate_proj(x), self.up_proj(x))
         else:

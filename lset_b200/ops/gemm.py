@@ -222,3 +222,67 @@ class _LoRALinear(torch.autograd.Function):
 
 def lora_linear(x, w, lora_a, lora_b, bias, scale: float):
     return _LoRALinear.apply(x, w, lora_a, lora_b, bias, float(scale))
+
+
+_GLU_KINDS = {"swiglu": 0, "geglu": 1}
+
+
+class _LinearGlu(torch.autograd.Function):
+    """``h = act(x·Wgᵀ) * (x·Wuᵀ)`` for the fused weight ``W = [Wg; Wu]``: the activation runs in
+    the GEMM epilogue (``lb_gemm_glu``), so the ``[T, 2I]`` projection output is written once (for
+    the backward) and never read back in the forward."""
+
+    @staticmethod
+    def forward(ctx, x, w, kind):
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        T, K = x2.shape
+        I = w.shape[0] // 2
+
+        def launch():
+            gu = torch.empty(T, 2 * I, dtype=torch.bfloat16, device=x.device)
+            h = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
+            rc = nv.load().lb_gemm_glu(
+                nv.c_void_p(x2.data_ptr()), nv.c_void_p(w.data_ptr()), nv.c_void_p(gu.data_ptr()),
+                nv.c_void_p(h.data_ptr()), nv.c_int(T), nv.c_int(I), nv.c_int(K), nv.c_ll(K),
+                nv.c_ll(w.stride(0)), nv.c_ll(2 * I), nv.c_ll(I), nv.c_int(kind),
+                nv.c_void_p(nv.status_word(x.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
+            if rc != 0:
+                nv.check_rc(rc, f"lb_gemm_glu(T={T},I={I},K={K})")
+            nv.count_launch()
+            return h, gu
+
+        h, gu = run_expensive(launch)
+        ctx.save_for_backward(x2, w, gu)
+        ctx.kind = kind
+        ctx.shape = x.shape
+        return h.view(*x.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, w, gu = ctx.saved_tensors
+        T, I2 = gu.shape
+        I = I2 // 2
+        dh2 = dh.reshape(T, I)
+        dh2 = dh2 if dh2.is_contiguous() else dh2.contiguous()
+        dgu = torch.empty_like(gu)
+        rc = nv.load().lb_glu_bwd(
+            nv.c_int(ctx.kind), nv.c_void_p(dh2.data_ptr()), nv.c_ll(I),
+            nv.c_void_p(gu.data_ptr()), nv.c_void_p(gu.data_ptr() + 2 * I), nv.c_ll(I2),
+            nv.c_void_p(dgu.data_ptr()), nv.c_void_p(dgu.data_ptr() + 2 * I), nv.c_ll(I2),
+            nv.c_ll(T), nv.c_int(I), nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_glu_bwd")
+        nv.count_launch()
+        dx = matmul_abt(dgu, w, b_mn=True).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        dw = _accumulate_wgrad(w, dgu, x2) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def linear_glu_supported(x, w) -> bool:
+    return (nv.use_native(x, w) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and w.shape[0] % 16 == 0 and x.shape[-1] % 8 == 0 and w.stride(1) == 1)
+
+
+def linear_glu(x, w, kind: str = "swiglu"):
+    """Gated-MLP input projection + activation; ``w`` is the fused ``[2I, K]`` gate/up weight."""
+    return _LinearGlu.apply(x, w, _GLU_KINDS[kind])

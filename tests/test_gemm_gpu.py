@@ -131,3 +131,35 @@ def test_lora_linear_matches_three_products():
         err = (a.float() - b).abs().max().item()
         assert err < 3e-2 * b.abs().max().item(), (name, err, b.abs().max().item())
     assert base.weight.grad is None
+
+
+@pytest.mark.parametrize("T,I,K", [(300, 512, 256), (1000, 3072, 1024), (77, 200, 128), (2048, 9728, 2560)])
+@pytest.mark.parametrize("kind", ["swiglu", "geglu"])
+def test_linear_glu_epilogue(T, I, K, kind):
+    """Gate/up projection with the activation in the GEMM epilogue against the two-kernel path
+    (same rounding points) and against fp32 PyTorch, values and gradients."""
+    from lset_b200.ops.activation import glu
+    from lset_b200.ops.gemm import linear_glu
+
+    torch.manual_seed(2)
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(2 * I, K, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    g = (torch.randn(T, I, device="cuda") * 0.5).to(torch.bfloat16)
+    h = linear_glu(x, w, kind)
+    h.backward(g)
+    nv.check_status()
+    got = (h.detach(), x.grad.clone(), w.grad.clone())
+    x.grad = w.grad = None
+    h2 = glu(linear(x, w), kind)
+    h2.backward(g)
+    two = (h2.detach(), x.grad, w.grad)
+    # same rounding points as the two-kernel path: equal up to a last-bit difference of the activation
+    assert (got[0].float() - two[0].float()).abs().max() <= 1e-2 * two[0].float().abs().max()
+    for a, b, name in zip(got[1:], two[1:], ("dx", "dw")):
+        assert (a.float() - b.float()).abs().max() <= 1e-2 * b.float().abs().max(), name
+    xr, wr = x.detach().float(), w.detach().float()
+    gu = xr @ wr.t()
+    act = torch.nn.functional.silu(gu[:, :I]) if kind == "swiglu" else \
+        torch.nn.functional.gelu(gu[:, :I], approximate="tanh")
+    ref = act * gu[:, I:]
+    assert (got[0].float() - ref).abs().max() < 3e-2 * ref.abs().max()
