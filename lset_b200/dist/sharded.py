@@ -30,6 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import _native as nv
+from ..ops._grads import register_main_grad
 from ..ops.norm import scratch
 
 _ALIGN = 8  # elements; keeps every parameter 16-byte aligned in the bf16 buffer
@@ -86,6 +87,7 @@ class FlatGroup:
         for p, o in zip(self.params, offs):
             p.data = self.flat_param[o:o + p.numel()].view(p.shape)
             p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
+            register_main_grad(p)   # found by storage address too (detached aliases under AC)
             p.grad = None
         self.reduce_event = None     # recorded after the gradient reduction of this group
         self.gather_event = None     # recorded after the parameter all-gather of this group

@@ -32,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _native as nv
+from ..ops._grads import main_grad_of
 from ..ops.gemm import matmul_abt, wgrad_splits
 from . import symm
 
@@ -241,7 +242,7 @@ def _weight_grad(ctx_needs, w, dy, x):
     """dW = dyᵀ · x, added into ``w.main_grad`` when the sharding runtime provides one."""
     if not ctx_needs:
         return None
-    main = getattr(w, "main_grad", None)
+    main = main_grad_of(w)
     if dy.is_cuda and dy.dtype == torch.bfloat16:
         splits = wgrad_splits(w.shape[0], w.shape[1], x.shape[0])
         if main is not None:

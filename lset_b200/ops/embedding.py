@@ -7,6 +7,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native as nv
+from ._grads import main_grad_of
 
 
 class _Embedding(torch.autograd.Function):
@@ -39,7 +40,7 @@ class _Embedding(torch.autograd.Function):
             if tab is None or not ctx.needs_input_grad[2 + 2 * k]:
                 grads.append(None)
                 continue
-            main = getattr(tab, "main_grad", None)
+            main = main_grad_of(tab)
             dst = main if main is not None else torch.zeros(tab.shape, dtype=torch.float32,
                                                             device=tab.device)
             rc = lib.lb_embedding_bwd(nv.c_void_p(ids[k].data_ptr()), nv.c_void_p(dy.data_ptr()),

@@ -14,6 +14,7 @@ import ctypes
 import torch
 
 from . import _native as nv
+from ._grads import main_grad_of
 from ._ac import run_expensive
 
 
@@ -121,7 +122,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = matmul_abt(dy2, w, b_mn=True).view_as(x)
         if ctx.needs_input_grad[1]:
-            main = getattr(w, "main_grad", None)
+            main = main_grad_of(w)
             if main is not None and dy2.is_cuda:
                 # fp32 gradient accumulator owned by the sharding runtime: add straight into it.
                 matmul_abt(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True,
@@ -176,7 +177,7 @@ def matmul_ext(a, b, a2, b2, *, b_mn=False, bias=None):
 def _accumulate_wgrad(w, dy2, x2):
     """``dW = dy2ᵀ · x2`` into ``w.main_grad`` (returns None) or as a tensor of ``w``'s dtype."""
     splits = wgrad_splits(w.shape[0], w.shape[1], x2.shape[0]) if dy2.is_cuda else 1
-    main = getattr(w, "main_grad", None)
+    main = main_grad_of(w)
     if main is not None and dy2.is_cuda:
         matmul_abt(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True, splits=splits)
         return None

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from . import _native as nv
+from ._grads import main_grad_of
 from .runtime_options import enabled
 
 
@@ -70,7 +71,7 @@ def deliver_wgrad(w, n_values: int, device, kernel_call):
     """Run ``kernel_call(out_ptr, out_is_fp32, accumulate)`` so that the weight gradient lands either
     in ``w.main_grad`` (fp32 accumulator owned by the sharding runtime; returns None) or in a fresh
     tensor of ``w``'s dtype (returned)."""
-    main = getattr(w, "main_grad", None)
+    main = main_grad_of(w)
     if main is not None:
         kernel_call(main.data_ptr(), 1, 1)
         return None
@@ -272,13 +273,13 @@ class _LayerNorm(torch.autograd.Function):
         nv.count_launch(2)
         dw = db = None
         b = ctx.b_ref
-        mg = getattr(w, "main_grad", None)
+        mg = main_grad_of(w)
         if mg is not None:
             mg.add_(dwb[:H])
         else:
             dw = dwb[:H].to(w.dtype)
         if ctx.has_bias:
-            mgb = getattr(b, "main_grad", None)
+            mgb = main_grad_of(b)
             if mgb is not None:
                 mgb.add_(dwb[H:])
             else:

@@ -11,6 +11,7 @@ import math
 import torch
 
 from . import _native as nv
+from ._grads import main_grad_of
 from .norm import scratch
 from .runtime_options import enabled
 
@@ -121,7 +122,7 @@ def deliver_norm_wgrads(qw, kw, dwb, hd):
     if dwb is None:
         return dqw, dkw
     for w, sl, is_q in ((qw, dwb[:hd], True), (kw, dwb[hd:], False)):
-        mg = getattr(w, "main_grad", None)
+        mg = main_grad_of(w)
         if mg is not None:
             mg.add_(sl)
         elif is_q:

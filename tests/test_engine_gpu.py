@@ -63,6 +63,25 @@ def test_grad_cache_and_activation_checkpointing_on_gpu():
         assert cos > 0.995, (kw, cos)
 
 
+def test_weight_gradients_reach_main_grad_under_checkpointing(monkeypatch):
+    """Checkpointing hands the backward detached aliases of the parameters; the weight gradients
+    must still be accumulated straight into the fp32 buffers (nothing arrives as ``param.grad``)."""
+    from lset_b200.dist.sharded import FlatGroup
+
+    folded = []
+    orig = FlatGroup.collect_autograd_grads
+
+    def spy(self):
+        folded.extend(p for p in self.params if p.grad is not None)
+        return orig(self)
+
+    monkeypatch.setattr(FlatGroup, "collect_autograd_grads", spy)
+    eng = _engine(activation_checkpoint=True, ac_mode="selective")
+    eng.forward_backward(_batch(0, 8), True)
+    nv.check_status()
+    assert not folded, f"{len(folded)} weight gradients took the autograd route"
+
+
 def test_lora_on_gpu():
     eng = _engine(lora=True, lora_r=16, lora_alpha=32.0, fused_projections=False, lr=2e-3)
     base = eng.model.layers[0].mlp.down_proj.base_linear.weight.clone()
