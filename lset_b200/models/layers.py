@@ -144,14 +144,16 @@ class Attention(nn.Module):
             per = self.num_heads // self.num_kv_heads
             Hk = qkv.shape[-1] // ((per + 2) * hd)
             Hq = Hk * per
-            o = attn_ops.qkv_attention(qkv[:T].view(T, Hq + 2 * Hk, hd), qw, kw, cos, sin, ctx.pos,
+            if Tp != T:   # padded token shards (sequence parallelism); a full-range slice would
+                qkv = qkv[:T]  # still cost a zero-fill and a copy in the backward
+            o = attn_ops.qkv_attention(qkv.view(T, Hq + 2 * Hk, hd), qw, kw, cos, sin, ctx.pos,
                                        ctx.plan, Hq, Hk, self.causal, self.softmax_scale, eps, w_off)
         else:
-            q = self.q_proj(x)
+            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
             Tp = q.shape[0]
-            q = q[:T].view(T, -1, hd)
-            k = self.k_proj(x)[:T].view(T, -1, hd)
-            v = self.v_proj(x)[:T].view(T, -1, hd)
+            if Tp != T:
+                q, k, v = q[:T], k[:T], v[:T]
+            q, k, v = q.view(T, -1, hd), k.view(T, -1, hd), v.view(T, -1, hd)
             Hq = q.shape[1]
             q, k = rope_ops.qk_norm_rope(q, k, qw, kw, cos, sin, ctx.pos, eps, w_off)
             o = attn_ops.varlen_attention(q, k, v, ctx.plan, self.causal, self.softmax_scale)
