@@ -136,7 +136,7 @@ class AttentionSection:
 class DistributedSection:
     dp_size: int = 1
     tp_size: int = 1
-    async_tp: bool = False
+    async_tp: bool = False  # sequence-parallel TP with collectives fused into the GEMMs (no torch.compile needed)
     max_restarts: int = 0  # extension: passed to the launcher; resume from the newest checkpoint
     step_timeout_s: float = 0.0  # extension: watchdog limit for one step (0 = off)
 
