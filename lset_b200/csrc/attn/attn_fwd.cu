@@ -26,6 +26,7 @@ struct AttnFwdArgs {
   const int* seq_start;  // first token of each sequence
   const int* seq_end;    // one past its last token
   const int* plan;
+  unsigned* work_counter;  // zeroed by the launcher: hands out work items past the first wave
   bf16* O;
   long long ldo;   // elements between consecutive tokens of O
   float* lse;      // [Hq, T]
@@ -93,6 +94,7 @@ __global__ void __launch_bounds__(128)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  __shared__ int s_next[2];  // next work item of this CTA, published by thread 0 one tile ahead
 
   // KV block n of this CTA's whole run (all tiles) lives in slot n & 1; its barrier phase is
   // (n >> 1) & 1. The score and P·V barriers complete once per block: phase n & 1.
@@ -148,9 +150,15 @@ __global__ void __launch_bounds__(128)
 
   // Persistent loop: TMEM and the barriers are set up once; the Q tile and the first K/V block of
   // the next work item are requested while the current one is still in its last block.
-  for (int w = blockIdx.x, it = 0; w < total && !failed; w += gridDim.x, ++it) {
-    const bool has_next = w + int(gridDim.x) < total;
-    const FwdTile nxt = has_next ? decode(w + gridDim.x) : cur;
+  // Work items past the first wave are handed out by an atomic counter (tiles differ in length:
+  // causal tiles late in a sequence see more KV blocks), fetched one tile ahead so that the next
+  // item's loads can be requested early.
+  for (int w = blockIdx.x, it = 0; w < total && !failed; ++it) {
+    if (tid == 0) s_next[it & 1] = int(atomicAdd(a.work_counter, 1u)) + int(gridDim.x);
+    __syncthreads();
+    const int w_next = s_next[it & 1];
+    const bool has_next = w_next < total;
+    const FwdTile nxt = has_next ? decode(w_next) : cur;
     const int qpos = cur.q0 + r % QT;
     const bool row_valid = qpos < cur.len;
     const int len = cur.len;
@@ -333,6 +341,7 @@ __global__ void __launch_bounds__(128)
     // after the CTA barrier at the top of the next tile)
     tc_fence_before();
     cur = nxt;
+    w = w_next;
   }
   tc_fence_before();
   __syncthreads();
@@ -406,7 +415,8 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
 
 using namespace lb;
 
-// plan: int32 [1 + 2 * capacity]; capacity >= ceil(T / tile_tokens) + B always suffices.
+// plan: int32 [1 + 2 * capacity + 1] (the last word is scratch for the attention kernels);
+// capacity >= ceil(T / tile_tokens) + B always suffices.
 extern "C" int lb_attn_plan(const int* seq_start, const int* seq_end, int B, int tile_tokens,
                             int* plan, int capacity, void* stream) {
   if (B <= 0) return -3;
@@ -439,9 +449,12 @@ extern "C" int lb_attn_fwd(const void* q, long long ldq, const void* k, long lon
   rc = make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * hd, (uint64_t)T, (uint64_t)ldv * 2, 64, kAttnKvBlock,
                     true);
   if (rc) return rc;
-  AttnFwdArgs a{seq_start, seq_end, plan, (bf16*)o, ldo, lse, T, Hq, Hk, softmax_scale * kLog2eF, causal,
-                status};
+  // the plan buffer carries one spare word behind its 1 + 2 * max_tiles entries
+  unsigned* counter = reinterpret_cast<unsigned*>(const_cast<int*>(plan)) + 1 + 2 * max_tiles;
+  AttnFwdArgs a{seq_start, seq_end, plan, counter, (bf16*)o, ldo, lse, T, Hq, Hk,
+                softmax_scale * kLog2eF, causal, status};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), st) != cudaSuccess) return -12;
   if (hd == 128) return launch_fwd<128>(tmQ, tmK, tmV, a, max_tiles, st);
   if (hd == 64) return launch_fwd<64>(tmQ, tmK, tmV, a, max_tiles, st);
   if (hd == 256) return launch_fwd<256>(tmQ, tmK, tmV, a, max_tiles, st);

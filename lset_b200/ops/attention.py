@@ -55,7 +55,8 @@ class AttnPlan:
         if hit is not None:
             return hit
         cap = (self.T + tile_tokens - 1) // tile_tokens + self.B
-        plan = torch.empty(1 + 2 * cap, dtype=torch.int32, device=self.seq_start.device)
+        # one spare word behind the entries: the work counter of the persistent forward kernel
+        plan = torch.empty(1 + 2 * cap + 1, dtype=torch.int32, device=self.seq_start.device)
         rc = nv.load().lb_attn_plan(nv.c_void_p(self.seq_start.data_ptr()),
                                     nv.c_void_p(self.seq_end.data_ptr()), nv.c_int(self.B),
                                     nv.c_int(tile_tokens), nv.c_void_p(plan.data_ptr()),
