@@ -242,6 +242,15 @@ def varlen_attention(q, k, v, plan: AttnPlan, causal: bool, scale: float | None 
     # training at that width runs the eager path (inference still uses the native forward).
     if native_supported(q, k) and not (needs_grad and q.shape[-1] > 128):
         return _VarlenAttn.apply(q, k, v, plan, bool(causal), float(scale))
+    if plan.cu_seqlens is None and not q.is_cuda and plan.B > 0 and plan.T % plan.B == 0:
+        # CPU, padded [B, S] batch: one batched masked attention instead of a Python loop over the
+        # sequences (rows of padding tokens are zeroed like in the per-sequence form)
+        B, S = plan.B, plan.T // plan.B
+        pos = torch.arange(S, device=q.device)[None, :] + torch.arange(B, device=q.device)[:, None] * S
+        mask = (pos >= plan.seq_start[:, None]) & (pos < plan.seq_end[:, None])
+        out = padded_attention_ref(q.view(B, S, *q.shape[1:]), k.view(B, S, *k.shape[1:]),
+                                   v.view(B, S, *v.shape[1:]), mask, causal, scale)
+        return (out * mask[:, :, None, None].to(out.dtype)).reshape(plan.T, *q.shape[1:])
     return attention_ref(q, k, v, plan.seq_start, causal, scale, seq_end=plan.seq_end)
 
 
