@@ -44,14 +44,14 @@ def _worker(rank, world, port, out_dir):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    eng = _engine(world)
+    eng = _engine(world, output_dir=os.path.join(out_dir, "ckpt"))
     loss = eng.forward_backward(_batch(rank * 4, rank * 4 + 4), True)
     total = loss.clone()
     dist.all_reduce(total)
     grads = [eng.store._gather_fp32(g, g.grad_shard) for g in eng.store.groups]
     eng.optimizer_step()
     params = {n: p.detach().clone() for n, p in eng.model.named_parameters()}
-    ck = eng.save(1) if True else None
+    eng.save(1)   # the distributed checkpoint path (sharded optimizer state) must not raise
     if rank == 0:
         torch.save({"loss": total, "grads": grads, "params": params}, os.path.join(out_dir, "dp.pt"))
     dist.barrier()
