@@ -113,6 +113,33 @@ def check_status(device=None) -> None:
         raise NativeError(f"native kernel reported status {code}: {STATUS_NAMES.get(code, '?')}")
 
 
+_polls = {}
+
+
+def poll_status(device=None) -> None:
+    """Non-blocking variant of ``check_status`` for the training loop: starts an asynchronous copy
+    of the status word into pinned host memory and looks at the copy started by the *previous*
+    call (waiting for that old copy costs nothing in steady state). A bounded-wait failure
+    therefore raises one or two steps after it happened instead of going unnoticed."""
+    word = status_word(device)
+    key = (word.device.type, word.device.index)
+    prev = _polls.get(key)
+    if prev is not None:
+        host, event = prev
+        event.synchronize()
+        code = int(host[0])
+        if code != 0:
+            word.zero_()
+            _polls.pop(key, None)
+            raise NativeError(f"native kernel reported status {code}: {STATUS_NAMES.get(code, '?')}")
+    else:
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host.copy_(word, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record()
+    _polls[key] = (host, event)
+
+
 def count_launch(n: int = 1) -> None:
     global _launches
     _launches += n

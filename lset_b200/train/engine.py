@@ -325,6 +325,10 @@ class TrainingEngine:
         self.scheduler.step()
         self.optimizer.zero_grad()
         self._limit_run_ahead()
+        if self.device.type == "cuda":
+            from ..ops import _native as nv
+
+            nv.poll_status(self.device)  # a kernel that gave up a bounded wait fails the run loudly
 
     def _limit_run_ahead(self) -> None:
         """Keep the host at most ``max_inflight_steps`` optimizer steps ahead of the GPU. A host

@@ -232,3 +232,20 @@ def test_device_barrier_single_gpu_forms():
     torch.cuda.synchronize()
     assert status.item() == 0
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_poll_status_raises_one_call_late_without_blocking():
+    """The training loop's non-blocking status check: the value seen is the one copied by the
+    previous call; a non-zero status raises and clears the word."""
+    word = nv.status_word(torch.device("cuda", torch.cuda.current_device()))
+    word.zero_()
+    nv.poll_status()
+    nv.poll_status()                       # still clean
+    word.fill_(4)                          # what a kernel that gave up waiting for a peer writes
+    nv.poll_status()                       # copies the 4 ...
+    with pytest.raises(nv.NativeError):
+        nv.poll_status()                   # ... and the next call sees it
+    torch.cuda.synchronize()
+    assert word.item() == 0
+    nv.poll_status()
+    nv.poll_status()
