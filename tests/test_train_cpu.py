@@ -281,3 +281,22 @@ def test_chunked_encoder_weighted_merge():
     assert out.shape == (2, 16) and abs(float((out[0] ** 2).sum()) - 1.0) < 1e-5
     with pytest.raises(ValueError):
         encode_chunked(m, tok, None, ["abcdefghij"], device="cpu", pooling="cls", chunk_len=4)
+
+
+def test_main_grad_is_found_through_detached_aliases():
+    """Checkpointed blocks hand the backward detached aliases of the parameters: the fp32
+    accumulator is still found (by storage address), and an entry dies with its parameter."""
+    import gc
+
+    from lset_b200.ops._grads import main_grad_of, register_main_grad
+
+    p = torch.nn.Parameter(torch.zeros(4, 4))
+    p.main_grad = torch.ones(4, 4)
+    register_main_grad(p)
+    alias = p.detach()
+    assert main_grad_of(p) is p.main_grad and main_grad_of(alias) is p.main_grad
+    assert main_grad_of(p.detach()[:2]) is None          # a different shape is not the parameter
+    del p, alias
+    gc.collect()
+    fresh = [torch.zeros(4, 4) for _ in range(8)]        # may reuse the freed address
+    assert all(main_grad_of(t) is None for t in fresh)
