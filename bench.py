@@ -269,6 +269,7 @@ def run_ours(args):
         fused_projections=preset["lora_r"] == 0, collator=BenchCollator(), async_tp=tp > 1,
         lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0,
         init_on_device=args.config != "qwen3-0.6b",
+        fp8=args.fp8 is not None, fp8_recipe=args.fp8 or "rowwise",
         # the 8B model keeps ~3 GB of activations per layer at this batch: recompute the cheap ops
         activation_checkpoint=bool(preset.get("ac", False)))
     device = engine.device
@@ -328,11 +329,15 @@ def run_ours(args):
            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "last_loss": last,
            "api": "lset_b200.train.engine.TrainingEngine.train_step(pinned host batch) + loss.item()"}
     if rank == 0:
-        print(json.dumps(result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e,
-                                     launches,
-                                     {"host_enqueue_ms_per_step": round(host_ms, 2),
-                                      "fused_projections": preset["lora_r"] == 0,
-                                      "native_library": str(nv.lib_path().name)}, preset)))
+        line = result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e, launches,
+                           {"host_enqueue_ms_per_step": round(host_ms, 2),
+                            "fused_projections": preset["lora_r"] == 0,
+                            "native_library": str(nv.lib_path().name)}, preset)
+        if args.fp8 is not None:
+            # a side measurement, not the headline: linear layers on the 8-bit tensor-core GEMM
+            line["dtype"] = f"fp8 ({args.fp8}: e4m3 operands, e5m2 gradients) in linear layers, bf16 elsewhere"
+            line["vs_baseline"] = None
+        print(json.dumps(line))
     import torch.distributed as dist
 
     if dist.is_initialized():
@@ -491,6 +496,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--config", choices=sorted(PRESETS), default="qwen3-0.6b")
+    ap.add_argument("--fp8", choices=["tensorwise", "rowwise", "rowwise_with_gw_hp"], default=None,
+                    help="side measurement: FP8 linear layers (the headline number is bf16)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -224,6 +224,31 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
+// Instruction descriptor of kind::f8f6f4 with 8-bit float operands (both K-major), fp32
+// accumulation. Operand format codes: 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t umma_idesc_f8(int M, int N, int a_e5m2, int b_e5m2) {
+  return (1u << 4)                       // D format: f32
+         | (uint32_t(a_e5m2) << 7)       // A format
+         | (uint32_t(b_e5m2) << 10)      // B format
+         | (uint32_t(N >> 3) << 17)      // N / 8
+         | (uint32_t(M >> 4) << 24);     // M / 16
+}
+
+// D[tmem] (+)= A[smem] * B[smem] with 8-bit float operands: one instruction contracts 32 elements
+// (32 bytes of a K-major row, the same byte extent as 16 bf16 elements).
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]; A is read from tensor memory (bf16 packed two per column).
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
                                              uint32_t idesc, uint32_t accumulate) {

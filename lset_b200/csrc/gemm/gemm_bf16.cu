@@ -88,6 +88,13 @@ struct GemmArgs {
   // is reduced into that rank's buffer with red.global.add over NVLink.
   void* c_peers[8];
   int c_rows_per_peer;        // 0 = C is a single local matrix
+  // ---- 8-bit float operands (F8 kernels): the accumulator of element (r, c) is multiplied by
+  // f8_sa[r * f8_sa_stride] * f8_sb[c * f8_sb_stride] (the operands' dequantisation factors; a
+  // stride of 0 is one factor for the whole tensor). Operand formats: 0 = e4m3, 1 = e5m2.
+  const float* f8_sa;
+  const float* f8_sb;
+  int f8_sa_stride, f8_sb_stride;
+  int f8_a_e5m2, f8_b_e5m2;
   int* status;
 };
 
@@ -106,8 +113,10 @@ struct Cfg {
   // both strides are conflict-free for the lane-per-row writes and the 8-lanes-per-row reads
   static constexpr int EPI_STAGE_WORDS = 32 * 36;
   static constexpr int EPI_STAGE_BYTES = 4 * EPI_STAGE_WORDS * 4;
-  static constexpr int SMEM_BYTES =
-      STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
+  // per epilogue warp: the BN per-column dequantisation factors of the current tile (8-bit GEMM)
+  static constexpr int EPI_SCALE_BYTES = 4 * 256 * 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
+                                    EPI_STAGE_BYTES + EPI_SCALE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -133,12 +142,16 @@ __device__ __forceinline__ void red_add8_bf16(void* dst, const uint4& v) {
                : "memory");
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT, int EPI, int GATHER = 0>
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI, int GATHER = 0, int F8 = 0>
 __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB2, GemmArgs g) {
   using C = Cfg<BN>;
+  // 8-bit operands: K-major only; a k-block is still 128 bytes of every row, i.e. 128 elements,
+  // and the shared-memory tiles, swizzle and descriptors are byte-for-byte those of the bf16 form.
+  static_assert(!F8 || (!A_MN && !B_MN && GATHER == 0 && EPI == EPI_STORE), "fp8: plain TN GEMM");
+  constexpr int BKE = F8 ? 2 * BK : BK;  // elements per k-block
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -186,7 +199,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
   constexpr int kTileN = EPI == EPI_GLU ? 128 : BN;  // output features (columns) per tile
   const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + kTileN - 1) / kTileN;
-  const int kb_main = (g.K + BK - 1) / BK;
+  const int kb_main = (g.K + BKE - 1) / BKE;
   const int kb_total = kb_main + g.kb_ext;
   const int total = tiles_m * tiles_n * g.splits;
   // (m0, n0, flag index) of the `mn`-th output tile
@@ -265,7 +278,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
           const bool ext = kb >= kb_main;
           const CUtensorMap* ta = ext ? &tmA2 : &tmA;
           const CUtensorMap* tb = ext ? &tmB2 : &tmB;
-          const int kc = (ext ? kb - kb_main : kb) * BK;
+          const int kc = (ext ? kb - kb_main : kb) * BKE;
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -299,7 +312,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = F8 ? umma_idesc_f8(BM, BN, g.f8_a_e5m2, g.f8_b_e5m2)
+                                : umma_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -331,7 +345,10 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
                                         : umma_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc(sb + k * 2048, BK * 128, 1024)
                                         : umma_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if constexpr (F8)
+              umma_f8(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else
+              umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == C::STAGES) {
@@ -507,6 +524,23 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       [[maybe_unused]] float lse2 = 0.f, cf = 0.f;
       [[maybe_unused]] const bool lbl = g.labels != nullptr;
       [[maybe_unused]] float rscale = 0.f;
+      [[maybe_unused]] float f8_row = 1.f;
+      [[maybe_unused]] float* f8_cols = reinterpret_cast<float*>(
+          smem + C::STAGES * C::STAGE_BYTES + 256 + C::EPI_STAGE_BYTES) + (warp - 2) * 256;
+      if constexpr (F8) {
+        f8_row = (row < m_limit) ? g.f8_sa[(long long)row * g.f8_sa_stride] : 0.f;
+        if (g.f8_sb_stride == 0) {
+          f8_row *= g.f8_sb[0];  // one factor for all of B: folded into the row factor
+        } else {
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < BN / 32; ++i) {
+            const int cj = n0 + i * 32 + lane;
+            f8_cols[i * 32 + lane] = cj < g.N ? g.f8_sb[cj] : 0.f;
+          }
+          __syncwarp();
+        }
+      }
       if constexpr (EPI == EPI_PGRAD) {
         lse2 = (row < m_limit) ? g.lse[row] * kLog2e : 0.f;
         cf = g.coef != nullptr ? g.coef[0] : 1.f;
@@ -521,6 +555,22 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
+        if constexpr (F8) {
+          // dequantise in place: row factor of A times column factor of B
+          if (g.f8_sb_stride == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f8_row);
+          } else {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 sb = *reinterpret_cast<const float4*>(f8_cols + c * 32 + 4 * j4);
+              r[4 * j4] = __float_as_uint(__uint_as_float(r[4 * j4]) * f8_row * sb.x);
+              r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) * f8_row * sb.y);
+              r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) * f8_row * sb.z);
+              r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) * f8_row * sb.w);
+            }
+          }
+        }
         if (row < m_limit && col0 < g.N) {
           float v[32];
 #pragma unroll
@@ -742,12 +792,13 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE, int GATHER = 0>
+template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE, int GATHER = 0,
+          int F8 = 0>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
            cudaStream_t stream, const CUtensorMap* tmA2 = nullptr,
            const CUtensorMap* tmB2 = nullptr) {
   using C = Cfg<BN>;
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI, GATHER>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI, GATHER, F8>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
@@ -861,6 +912,77 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                             int* status, void* stream_) {
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bias,
                         splits, bn, status, stream_, nullptr, 0, 0);
+}
+
+// C = (A · B^T) ∘ (sa ⊗ sb) with 8-bit float operands (tcgen05 kind::f8f6f4, fp32 accumulation).
+//   A: [M, K] row-major bytes, row stride lda; B: [N, K] row-major bytes, row stride ldb (both
+//   K-major; lda, ldb multiples of 16). a_e5m2 / b_e5m2: 0 = e4m3, 1 = e5m2.
+//   sa / sb: dequantisation factors (device fp32), one per row of A / row of B when the stride is 1,
+//   one for the whole tensor when it is 0.
+//   out_fp32, accumulate, splits, bias, bn: as in lb_gemm_bf16.
+extern "C" int lb_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K,
+                           long long lda, long long ldb, long long ldc, int a_e5m2, int b_e5m2,
+                           const float* sa, int sa_stride, const float* sb, int sb_stride,
+                           int out_fp32, int accumulate, const void* bias, int splits, int bn,
+                           int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -4;
+  if ((N & 7) || (lda & 15) || (ldb & 15) || (ldc & 3)) return -3;
+  if (!out_fp32 && (ldc & 7)) return -3;
+  if (sa == nullptr || sb == nullptr) return -3;
+  if (!out_fp32 && (accumulate || splits > 1)) return -5;
+  constexpr int BKE = 2 * BK;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int sms = num_sms();
+  if (bn != 128 && bn != 256) {
+    auto eff = [&](int b) {
+      const long long t = 1LL * tiles_m * ((N + b - 1) / b);
+      const long long waves = (t + sms - 1) / sms;
+      return double(t) * b / double(waves * sms);
+    };
+    bn = (N > 128 && eff(256) >= eff(128)) ? 256 : 128;
+  }
+  const int tiles_n = (N + bn - 1) / bn;
+  const int kb_total = (K + BKE - 1) / BKE;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per - 1) / kb_per;
+  if (splits > 1) accumulate = 1;
+
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, 1, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BKE, BM, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, 1, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BKE, bn, true);
+  if (rc) return rc;
+
+  GemmArgs g{};
+  g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.C = C;
+  g.ldc = ldc;
+  g.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  g.accumulate = accumulate;
+  g.splits = splits;
+  g.kb_per_split = kb_per;
+  g.status = status;
+  g.f8_sa = sa;
+  g.f8_sb = sb;
+  g.f8_sa_stride = sa_stride ? 1 : 0;
+  g.f8_sb_stride = sb_stride ? 1 : 0;
+  g.f8_a_e5m2 = a_e5m2 ? 1 : 0;
+  g.f8_b_e5m2 = b_e5m2 ? 1 : 0;
+  const long long total = 1LL * tiles_m * tiles_n * splits;
+  const int grid = (int)(total < sms ? total : sms);
+  if (bn == 256)
+    return out_fp32 ? launch<0, 0, 256, float, EPI_STORE, 0, 1>(tmA, tmB, g, grid, stream)
+                    : launch<0, 0, 256, __nv_bfloat16, EPI_STORE, 0, 1>(tmA, tmB, g, grid, stream);
+  return out_fp32 ? launch<0, 0, 128, float, EPI_STORE, 0, 1>(tmA, tmB, g, grid, stream)
+                  : launch<0, 0, 128, __nv_bfloat16, EPI_STORE, 0, 1>(tmA, tmB, g, grid, stream);
 }
 
 // GEMM fused with a reduce-scatter: C has M = world * rows_per_peer rows; row r is added (fp32

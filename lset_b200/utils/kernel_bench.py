@@ -2,6 +2,7 @@
 captures under ``profiles/`` are taken from).
 
     python -m lset_b200.utils.kernel_bench gemm  --m 23040 --n 4096 --k 1024 [--form fprop|dgrad|wgrad]
+    python -m lset_b200.utils.kernel_bench fp8   --m 23040 --n 4096 --k 1024 [--what gemm|cast|linear]
     python -m lset_b200.utils.kernel_bench attn  --seqs 64 --len 320 --hq 16 --hk 8 --hd 128 [--bwd]
     python -m lset_b200.utils.kernel_bench norm  --rows 23040 --h 1024 [--bwd]
     python -m lset_b200.utils.kernel_bench rope  --rows 23040 --hq 16 --hk 8 --hd 128 [--bwd]
@@ -67,6 +68,35 @@ def bench_gemm(a):
     flops = 2.0 * M * N * K
     byt = 2.0 * (M * K + N * K + M * N)
     return dict(kernel=f"gemm_{a.form}", M=M, N=N, K=K, ms=ms, **roofline(ms, flops, byt))
+
+
+def bench_fp8(a):
+    """8-bit GEMM alone (operands quantised beforehand), the cast of its activation operand, or
+    quantise + GEMM as the fp8 linear layer runs them; the bf16 GEMM of the same shape alongside."""
+    from ..ops import fp8 as f8
+    from ..ops.gemm import matmul_abt
+
+    M, N, K = a.m, a.n, a.k
+    x, w = _r(M, K), _r(N, K)
+    mode = f8.PER_ROW if a.rowwise else f8.PER_TENSOR
+    xq, _ = f8.quantize_fp8(x, mode)
+    wq, _ = f8.quantize_fp8(w, mode)
+    flops = 2.0 * M * N * K
+    if a.what == "gemm":
+        fn = lambda: f8.matmul_fp8(xq, wq)  # noqa: E731
+        byt = 1.0 * (M * K + N * K) + 2.0 * M * N
+    elif a.what == "cast":
+        fn = lambda: f8.quantize_fp8(x, mode, want_t=not a.rowwise)  # noqa: E731
+        flops, byt = 0.0, (2.0 * 2 + (1.0 if a.rowwise else 2.0)) * M * K   # two reads of x
+    else:
+        def fn():
+            q, _ = f8.quantize_fp8(x, mode)
+            f8.matmul_fp8(q, wq)
+        byt = (2.0 * 2 + 1.0 + 1.0) * M * K + 1.0 * N * K + 2.0 * M * N
+    ms = _time(fn, a.iters)
+    ms_bf16 = _time(lambda: matmul_abt(x, w), a.iters)
+    return dict(kernel=f"fp8_{a.what}", rowwise=bool(a.rowwise), M=M, N=N, K=K, ms=ms,
+                bf16_gemm_ms=ms_bf16, **roofline(ms, flops, byt))
 
 
 def bench_attn(a):
@@ -233,6 +263,10 @@ def main(argv=None):
     g.add_argument("--m", type=int, default=23040); g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=1024); g.add_argument("--form", default="fprop")
     g.add_argument("--bn", type=int, default=0); g.add_argument("--splits", type=int, default=2)
+    f = sub.add_parser("fp8")
+    f.add_argument("--m", type=int, default=23040); f.add_argument("--n", type=int, default=4096)
+    f.add_argument("--k", type=int, default=1024); f.add_argument("--what", default="gemm")
+    f.add_argument("--rowwise", action="store_true")
     t = sub.add_parser("attn")
     t.add_argument("--seqs", type=int, default=64); t.add_argument("--len", type=int, default=320)
     t.add_argument("--hq", type=int, default=16); t.add_argument("--hk", type=int, default=8)
@@ -259,12 +293,12 @@ def main(argv=None):
     em.add_argument("--bwd", action="store_true")
     ad = sub.add_parser("adamw")
     ad.add_argument("--n", type=int, default=268435456)
-    for p in (g, t, n, r, u, l, po, em, ad):
+    for p in (g, f, t, n, r, u, l, po, em, ad):
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     from ..ops import _native as nv
 
-    out = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "rope": bench_rope,
+    out = {"gemm": bench_gemm, "fp8": bench_fp8, "attn": bench_attn, "norm": bench_norm, "rope": bench_rope,
            "glu": bench_glu, "loss": bench_loss, "pool": bench_pool, "embed": bench_embed,
            "adamw": bench_adamw}[a.which](a)
     nv.check_status()
