@@ -53,6 +53,10 @@ PRESETS = {
         model=MODEL_4B, pairs=32, tp=2, negs=0, lora_r=0,
         metric="pairs/sec & tokens/sec, Qwen3-4B embed TP2 x sharded DP bf16, max over ranks",
         label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
+    "qwen3-4b": dict(
+        model=MODEL_4B, pairs=32, tp=1, negs=0, lora_r=0,
+        metric="pairs/sec & tokens/sec, Qwen3-4B embed sharded DP bf16, max over ranks",
+        label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
     "qwen3-8b-lora": dict(
         model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16, ac=True,
         metric="pairs/sec & tokens/sec, Qwen3-8B embed + LoRA r16, sharded DP bf16, 3 hard negatives, "
