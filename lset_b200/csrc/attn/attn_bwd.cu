@@ -74,30 +74,6 @@ struct AttnBwdArgs {
   int* status;
 };
 
-__device__ __forceinline__ void ld_row64(uint32_t taddr, float (&s)[64]) {
-  uint32_t t0[32], t1[32];
-  tmem_ld_32x32b_x32(taddr, t0);
-  tmem_ld_32x32b_x32(taddr + 32, t1);
-  tmem_ld_wait();
-#pragma unroll
-  for (int c = 0; c < 32; ++c) {
-    s[c] = __uint_as_float(t0[c]);
-    s[32 + c] = __uint_as_float(t1[c]);
-  }
-}
-
-__device__ __forceinline__ void st_row_bf16_swz(uint8_t* tile, int row, const float (&v)[64]) {
-#pragma unroll
-  for (int c8 = 0; c8 < 8; ++c8) {
-    uint4 q;
-    q.x = pack_bf16x2(v[c8 * 8 + 0], v[c8 * 8 + 1]);
-    q.y = pack_bf16x2(v[c8 * 8 + 2], v[c8 * 8 + 3]);
-    q.z = pack_bf16x2(v[c8 * 8 + 4], v[c8 * 8 + 5]);
-    q.w = pack_bf16x2(v[c8 * 8 + 6], v[c8 * 8 + 7]);
-    *reinterpret_cast<uint4*>(tile + swz128_offset(row, c8)) = q;
-  }
-}
-
 __device__ __forceinline__ void ld_row32(uint32_t taddr, float (&s)[32]) {
   uint32_t t0[32];
   tmem_ld_32x32b_x32(taddr, t0);

@@ -120,15 +120,6 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
-__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) {
-  uint4 q;
-  q.x = pack_bf16x2(v[0], v[1]);
-  q.y = pack_bf16x2(v[2], v[3]);
-  q.z = pack_bf16x2(v[4], v[5]);
-  q.w = pack_bf16x2(v[6], v[7]);
-  *reinterpret_cast<uint4*>(dst) = q;
-}
-
 __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
                "f"(d)
@@ -195,7 +186,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
   // GATHER 1: rows of B come from the peers; GATHER 2: rows of A do. n_local = rows per rank.
   constexpr int kGatherRows = GATHER == 2 ? BM : BN;
   constexpr int kPullRows = 16;  // rows per pull item (one warp); divides BM and BN
-  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 0;
+  // (1 without a gather, so that the index arithmetic below stays defined)
+  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + kGatherRows - 1) / kGatherRows : 1;
   const int tiles_m = GATHER == 2 ? g.world * tiles_per_peer : (g.M + BM - 1) / BM;
   constexpr int kTileN = EPI == EPI_GLU ? 128 : BN;  // output features (columns) per tile
   const int tiles_n = GATHER == 1 ? g.world * tiles_per_peer : (g.N + kTileN - 1) / kTileN;

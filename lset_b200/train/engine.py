@@ -186,7 +186,8 @@ class TrainingEngine:
             # async_tp: token-sharded residual stream with the all-gather / reduce-scatter fused
             # into the projection GEMMs over peer memory (decoder families, no LoRA adapters);
             # otherwise the Megatron all-reduce scheme.
-            sp = bool(async_tp) and not self.use_lora and hasattr(model, "_sp")
+            # FP8 linear layers keep their own forward, so they run under the all-reduce scheme.
+            sp = bool(async_tp) and not self.use_lora and not fp8 and hasattr(model, "_sp")
             apply_tp(model, self.tp_group, spec.tp_plan_fn(
                 model_config, use_sequence_parallel=sp, use_lora=self.use_lora,
                 fused_projections=fused_projections), sequence_parallel=sp)
