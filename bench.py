@@ -353,9 +353,11 @@ def run_ours(args):
 # reference arm: the unmodified reference package from baseline/_ref, through its own engine
 # ----------------------------------------------------------------------------------------------
 def run_reference(args):
-    if args.config != "qwen3-0.6b":
+    preset = PRESETS[args.config]
+    if preset["lora_r"] or preset["negs"]:
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference arm is wired for the headline config (qwen3-0.6b) only"}))
+                          "the reference arm is wired for the dense configs without hard negatives "
+                          "(qwen3-0.6b, qwen3-4b, qwen3-4b-tp2)"}))
         return
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "lset")):
@@ -382,11 +384,12 @@ def run_reference(args):
 
     # The reference engine loads a checkpoint directory: write config.json and random N(0, 0.02)
     # weights once (rank 0) and let the other ranks wait for the marker file.
-    model_dir = os.path.join(tempfile.gettempdir(), f"lset_ref_qwen3_06b_{os.environ.get('MASTER_PORT', '0')}")
+    model_dir = os.path.join(tempfile.gettempdir(),
+                             f"lset_ref_{args.config}_{os.environ.get('MASTER_PORT', '0')}")
     marker = os.path.join(model_dir, "READY")
     if rank == 0 and not os.path.exists(marker):
         os.makedirs(model_dir, exist_ok=True)
-        cfg = dict(MODEL, model_type="qwen3", architectures=["Qwen3ForCausalLM"])
+        cfg = dict(preset["model"], model_type="qwen3", architectures=["Qwen3ForCausalLM"])
         with open(os.path.join(model_dir, "config.json"), "w") as fh:
             json.dump(cfg, fh)
         from lset.models import get_model_spec
@@ -412,8 +415,11 @@ def run_reference(args):
             return
 
     n_batches = W + K + 1
-    # with dp > 1 the reference's DistributedSampler gives each rank 1/world of its dataset
-    samples = make_samples(n_batches * world, rank)
+    tp, P = preset["tp"], preset["pairs"]
+    dp = max(1, world // tp)
+    # with dp > 1 the reference's DistributedSampler gives each rank 1/dp of its dataset; the ranks
+    # of one tensor-parallel group must see the same samples
+    samples = make_samples(n_batches * dp, rank // tp if tp > 1 else rank, pairs=P)
     tokens = []
     state = {"i": 0, "e0": None, "e1": None}
     inner = RefPacked()
@@ -450,8 +456,8 @@ def run_reference(args):
 
     try:
         engine = RefEngine(
-            model_name="qwen3", model_path=model_dir, dataset=SeqDataset(samples), dp_size=world,
-            tp_size=1, batch_size=PAIRS_PER_GPU, lr=LR, max_steps=n_batches, grad_clip=1.0,
+            model_name="qwen3", model_path=model_dir, dataset=SeqDataset(samples), dp_size=dp,
+            tp_size=tp, batch_size=P, lr=LR, max_steps=n_batches, grad_clip=1.0,
             temperature=TEMPERATURE, log_interval=10**9, packed=True, scheduler_type="constant",
             collator=timing_collator)
         # keep the batches in order (the stock DataLoader shuffles; order does not change the work)
@@ -466,14 +472,17 @@ def run_reference(args):
         tok_all = _file_allreduce(float(sum(tokens)) / K, rank, world, "tok", sum)
     else:
         ms_all, tok_all = ms, float(sum(tokens)) / K
-    pairs = PAIRS_PER_GPU * world
+    pairs = P * dp
+    if tp > 1:
+        tok_all /= tp   # every rank of a tensor-parallel group counted the same tokens
     e2e = {"value": pairs / (ms_all / 1e3), "unit": "pairs/s", "ms_per_step": ms_all,
            "h2d_bytes_per_step": int(state.get("h2d", 0) / K), "d2h_bytes_per_step": 4,
            "api": "lset.train.engine.TrainingEngine.train() (stock loop: .to(device) + loss.item() per step)"}
     if rank == 0:
         line = result_line("reference", world, K, W, ms_all, pairs, tok_all, state.get("clocks"), e2e,
                            None, {"note": "timed region = steps W..W+K-1 of the reference's own "
-                                          "train() loop, marked from its DataLoader collate calls"})
+                                          "train() loop, marked from its DataLoader collate calls"},
+                           preset)
         line.pop("gpu_launches")
         print(json.dumps(line))
 
