@@ -348,6 +348,9 @@ class ParamStore:
             g.flat_param.copy_(full.to(self.compute_dtype))
 
 
+_HAS_FUSED_CPU_ADAMW = hasattr(torch, "_fused_adamw_")
+
+
 class ShardedAdamW:
     """AdamW over a ``ParamStore`` (torch.optim.AdamW semantics, decoupled weight decay) with
     global-norm clipping folded in. ``state_dict`` follows torch's AdamW schema so checkpoints are
@@ -402,7 +405,8 @@ class ShardedAdamW:
                     nv.check_rc(rc, "lb_sumsq_f32")
                     nv.count_launch(2)
                 else:
-                    parts[slot] += g.grad_shard.float().pow(2).sum()
+                    gs = g.grad_shard.reshape(-1).float()
+                    parts[slot] += torch.dot(gs, gs)       # one pass, no temporary
         if st.tp_group is not None and dist.get_world_size(st.tp_group) > 1:
             dist.all_reduce(parts[1:2], op=dist.ReduceOp.SUM, group=st.tp_group)
         torch.sum(parts, dim=0, keepdim=True, out=self._sumsq)
@@ -455,6 +459,16 @@ class ShardedAdamW:
                 nv.count_launch()
                 if g.compute_dtype != torch.bfloat16:
                     pshard.copy_(g.master)
+            elif _HAS_FUSED_CPU_ADAMW and g.master.dtype == torch.float32:
+                # torch's single-pass CPU kernel (same update rule); the gradient shard is consumed
+                # by this step, so the clip coefficient is applied to it in place
+                if self.grad_clip > 0:
+                    g.grad_shard.mul_(self._coef[0])
+                torch._fused_adamw_([g.master], [g.grad_shard], [g.exp_avg], [g.exp_avg_sq], [],
+                                    [torch.tensor(float(self.step_count))], lr=float(lr), beta1=b1,
+                                    beta2=b2, weight_decay=wd, eps=eps, amsgrad=False,
+                                    maximize=False)
+                pshard.copy_(g.master)
             else:
                 grad = g.grad_shard * self._coef[0]
                 g.master.mul_(1.0 - lr * wd)

@@ -52,11 +52,51 @@ class _Embedding(torch.autograd.Function):
         return None, None, grads[0], None, grads[1], None, grads[2]
 
 
+class _EmbeddingEager(torch.autograd.Function):
+    """CPU lookup whose backward adds the rows straight into the tables' fp32 accumulators
+    (``index_add_``) when they have one, instead of materialising a dense zero-filled
+    ``[vocab, H]`` gradient per call as aten's embedding backward does."""
+
+    @staticmethod
+    def forward(ctx, scale, n_tabs, *args):
+        ids, tabs = args[:n_tabs], args[n_tabs:]
+        out = tabs[0][ids[0]]
+        for i, t in zip(ids[1:], tabs[1:]):
+            out = out + t[i]
+        ctx.save_for_backward(*ids)
+        ctx.tabs, ctx.scale, ctx.n = tabs, scale, n_tabs
+        return out * scale if scale != 1.0 else out
+
+    @staticmethod
+    def backward(ctx, dy):
+        ids = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if ctx.scale != 1.0:
+            dy2 = dy2 * ctx.scale
+        grads = []
+        for k, tab in enumerate(ctx.tabs):
+            if not ctx.needs_input_grad[2 + ctx.n + k]:
+                grads.append(None)
+                continue
+            main = main_grad_of(tab)
+            dst = main if main is not None else torch.zeros_like(tab, dtype=torch.float32)
+            dst.index_add_(0, ids[k].reshape(-1), dy2.to(dst.dtype))
+            grads.append(None if main is not None else dst.to(tab.dtype))
+        return (None, None) + (None,) * ctx.n + tuple(grads)
+
+
 def embedding(ids, table, scale: float = 1.0, extra=()):
     """``scale * (table[ids] + sum(t[i] for i, t in extra))`` with the result shaped ``ids.shape + [H]``.
 
     ``extra`` holds up to two ``(ids, table)`` pairs (BERT position and token-type tables)."""
     native = nv.use_native(table) and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0
+    if not native and not table.is_cuda and torch.is_grad_enabled() and any(
+            t.requires_grad for t in (table, *[t for _, t in extra])):
+        all_ids = [ids] + [i.expand_as(ids) for i, _ in extra]
+        out = _EmbeddingEager.apply(float(scale), len(all_ids),
+                                    *[i.to(torch.int64) for i in all_ids], table,
+                                    *[t for _, t in extra])
+        return out
     if not native or len(extra) > 2:
         out = F.embedding(ids, table)
         for i, t in extra:

@@ -300,3 +300,34 @@ def test_main_grad_is_found_through_detached_aliases():
     gc.collect()
     fresh = [torch.zeros(4, 4) for _ in range(8)]        # may reuse the freed address
     assert all(main_grad_of(t) is None for t in fresh)
+
+
+def test_cpu_embedding_scatters_into_accumulators():
+    """The CPU lookup matches aten's embedding (values and gradients); with an fp32 accumulator
+    registered the rows are added into it and no dense gradient is returned."""
+    import torch.nn.functional as F
+
+    from lset_b200.ops import _grads
+    from lset_b200.ops.embedding import embedding
+
+    torch.manual_seed(0)
+    tab = torch.randn(50, 16, requires_grad=True)
+    pos = torch.randn(12, 16, requires_grad=True)
+    ids = torch.randint(0, 50, (3, 7))
+    pid = torch.arange(7)[None, :]
+    out = embedding(ids, tab, 2.0, extra=[(pid, pos)])
+    ref = (F.embedding(ids, tab) + F.embedding(pid.expand_as(ids), pos)) * 2.0
+    assert torch.allclose(out, ref)
+    g = torch.randn_like(out)
+    gt, gp = torch.autograd.grad(out, [tab, pos], g)
+    rt, rp = torch.autograd.grad(ref, [tab, pos], g)
+    assert torch.allclose(gt, rt, atol=1e-6) and torch.allclose(gp, rp, atol=1e-6)
+
+    tab2 = tab.detach().clone().requires_grad_()
+    tab2.main_grad = torch.ones(50, 16)
+    _grads.register_main_grad(tab2)
+    out2 = embedding(ids, tab2, 2.0)
+    out2.backward(g)
+    assert tab2.grad is None
+    r2, = torch.autograd.grad(F.embedding(ids, tab) * 2.0, [tab], g)
+    assert torch.allclose(tab2.main_grad, r2 + 1.0, atol=1e-6)
