@@ -90,6 +90,46 @@ def test_tp_matches_unsharded(fused, sp):
     assert torch.allclose(ref.embed_tokens.weight.grad, got["ge"], atol=1e-4)
 
 
+def _fp8_worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lset_b200.dist.tp import apply_tp
+    from lset_b200.train.quantization.fp8 import Float8Linear, apply_fp8_training
+
+    torch.manual_seed(0)
+    m = Qwen3Decoder(_cfg(), fused_projections=False)
+    init_normal_(m, 0.05)
+    full = {k: v.clone() for k, v in m.state_dict().items()}
+    apply_fp8_training(m, "tensorwise")      # the engine's order: fp8 first, then the TP plan
+    apply_tp(m, dist.group.WORLD, decoder_tp_plan(_cfg()))
+    n_fp8 = sum(isinstance(x, Float8Linear) for x in m.modules())
+    out = m(_ids(False))["hidden_states"]
+    out.pow(2).sum().backward()
+    g = m.layers[0].mlp.down_proj.weight.grad.clone()
+    if rank == 0:
+        torch.save({"out": out.detach(), "grad": g, "full": full, "n_fp8": n_fp8},
+                   os.path.join(out_dir, "tp_fp8.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_with_fp8_linears():
+    """FP8 linear layers keep working under the all-reduce tensor-parallel scheme: shards are
+    quantised per rank, so the result is fp8-close (not equal) to the unsharded full-precision model."""
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_fp8_worker, args=(2, _port(), out_dir), nprocs=2, join=True)
+    got = torch.load(os.path.join(out_dir, "tp_fp8.pt"), weights_only=False)
+    assert got["n_fp8"] >= 12
+    ref = Qwen3Decoder(_cfg(), fused_projections=False)
+    ref.load_state_dict(got["full"])
+    out = ref(_ids(False))["hidden_states"]
+    out.pow(2).sum().backward()
+    rel = lambda a, b: float((a - b).abs().max() / b.abs().max())  # noqa: E731
+    assert rel(got["out"], out.detach()) < 0.15
+    assert rel(got["grad"], ref.layers[0].mlp.down_proj.weight.grad[:, :32]) < 0.3
+
+
 def test_plans():
     p = decoder_tp_plan(None)
     assert p["layers.*.self_attn.q_proj"] == "colwise" and p["layers.*.mlp.down_proj"] == "rowwise"
