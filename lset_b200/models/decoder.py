@@ -149,6 +149,26 @@ class DecoderModel(nn.Module):
         return hidden
 
 
+    def run_stage(self, flat_ids, stream, ctx: StreamCtx, lo: int, hi: int):
+        """One pipeline stage: layers ``lo..hi-1``. The first stage (``lo == 0``) starts from the
+        embeddings of ``flat_ids``; later stages take ``stream = (branch, residual)`` from the
+        stage before. The last stage (``hi == len(layers)``) returns the final hidden states, the
+        others the open residual stream ``(branch, residual)`` for the next stage."""
+        if self.traits.sandwich_norms:
+            raise NotImplementedError("pipeline stages are not available for sandwich-norm blocks")
+        if lo == 0:
+            branch, residual = self._embed(flat_ids), None
+        else:
+            branch, residual = stream
+        for layer in list(self.layers)[lo:hi]:
+            branch, residual = layer(branch, residual, ctx, None)
+        if hi < len(self.layers):
+            return branch, residual
+        n = self.norm
+        hidden, _ = norm_ops.residual_rms_norm(residual, branch, n.weight, n.eps, n.w_off)
+        return hidden
+
+
 class Qwen3Decoder(DecoderModel):
     """Qwen3 embedder: causal attention, per-head QK RMSNorm, SwiGLU."""
 

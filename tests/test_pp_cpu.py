@@ -1,0 +1,116 @@
+"""Pipeline-parallel runner on CPU (gloo, 2 and 3 stages): embeddings, loss and every parameter
+gradient equal the unsplit model's; split helpers agree with the runner's layer ranges."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from lset_b200.dist.pp import get_pp_split_points, get_stage_module_names, stage_layer_range
+from lset_b200.models import Qwen3Config, Qwen3Decoder
+from lset_b200.models.layers import init_normal_
+
+
+def _cfg():
+    return Qwen3Config(vocab_size=200, hidden_size=32, intermediate_size=64, num_hidden_layers=5,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+
+
+def _port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _microbatches():
+    """Two packed micro-batches (queries, documents) and one padded one."""
+    def packed(lens, off):
+        ids = (torch.arange(sum(lens)) * 7 + off) % 200
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        pos = torch.cat([torch.arange(n) for n in lens])
+        return {"input_ids": ids, "cu_seqlens": cu, "position_ids": pos, "max_seqlen": max(lens)}
+
+    return [packed([5, 3, 6], 1), packed([9, 4, 7], 11),
+            {"input_ids": (torch.arange(12).reshape(3, 4) * 3) % 200}]
+
+
+def _loss(hiddens, mbs):
+    """InfoNCE between the last-token embeddings of micro-batch 0 and 1, plus a term on the
+    padded micro-batch, so that every micro-batch's gradient depends on the others."""
+    last = lambda h, mb: h[mb["cu_seqlens"][1:].long() - 1]  # noqa: E731
+    q = torch.nn.functional.normalize(last(hiddens[0], mbs[0]), dim=-1)
+    d = torch.nn.functional.normalize(last(hiddens[1], mbs[1]), dim=-1)
+    ce = torch.nn.functional.cross_entropy(q @ d.t() / 0.05, torch.arange(q.shape[0]))
+    return ce + hiddens[2].pow(2).mean()
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lset_b200.dist.pp import PipelineRunner
+
+    torch.manual_seed(0)
+    m = Qwen3Decoder(_cfg())
+    init_normal_(m, 0.05)
+    full = {k: v.clone() for k, v in m.state_dict().items()}
+    runner = PipelineRunner(m, dist.group.WORLD)
+    mbs = _microbatches()
+    hiddens = runner.encode(mbs)
+    loss = None
+    if runner.last:
+        leaves = [h.detach().requires_grad_() for h in hiddens]
+        loss = _loss(leaves, mbs)
+        loss.backward()
+        runner.backward([t.grad for t in leaves])
+    else:
+        assert hiddens == []
+        runner.backward()
+    grads = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+    torch.save({"grads": grads, "full": full, "loss": None if loss is None else loss.detach(),
+                "range": (runner.lo, runner.hi)}, os.path.join(out_dir, f"pp{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_matches_unsplit_model(stages):
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_worker, args=(stages, _port(), out_dir), nprocs=stages, join=True)
+    got = [torch.load(os.path.join(out_dir, f"pp{r}.pt"), weights_only=False) for r in range(stages)]
+    ref = Qwen3Decoder(_cfg())
+    ref.load_state_dict(got[0]["full"])
+    mbs = _microbatches()
+    hiddens = [ref(**mb)["hidden_states"] for mb in mbs]
+    loss = _loss(hiddens, mbs)
+    loss.backward()
+    assert torch.allclose(got[-1]["loss"], loss.detach(), atol=1e-5)
+    ref_grads = {n: p.grad for n, p in ref.named_parameters()}
+    seen = set()
+    for r, g in enumerate(got):
+        lo, hi = g["range"]
+        assert (lo, hi) == stage_layer_range(5, stages, r)
+        for name, grad in g["grads"].items():
+            assert torch.allclose(grad, ref_grads[name], atol=1e-5), name
+            seen.add(name)
+        owned = {n for n in g["grads"] if n.startswith("layers.")}
+        assert {int(n.split(".")[1]) for n in owned} == set(range(lo, hi))
+    assert seen == set(ref_grads)          # every parameter lives on exactly one stage
+
+
+def test_split_helpers_agree_with_ranges():
+    for n, pp in [(5, 2), (5, 3), (28, 4), (36, 8)]:
+        names = get_stage_module_names(n, pp)
+        points = get_pp_split_points(n, pp)
+        for s in range(pp):
+            lo, hi = stage_layer_range(n, pp, s)
+            layers = [x for x in names[s] if x.startswith("layers.")]
+            assert layers == [f"layers.{i}" for i in range(lo, hi)]
+            if s > 0:
+                assert points[f"layers.{lo}"] == "BEGINNING"
+        assert len(points) == pp - 1
