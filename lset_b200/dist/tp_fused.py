@@ -26,7 +26,6 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
 
 import torch
 import torch.distributed as dist

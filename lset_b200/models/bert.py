@@ -8,7 +8,6 @@ State-dict keys follow the reference (lset/models/encoder/bert/model.py:14-142):
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn as nn

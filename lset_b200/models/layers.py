@@ -10,7 +10,6 @@ lset/models/decoder/qwen3/attention.py:66-78, lset/models/decoder/qwen3/mlp.py:1
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Optional
 

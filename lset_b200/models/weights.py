@@ -8,7 +8,7 @@ lset/models/decoder/gemma/weights.py:1-36).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from pathlib import Path
 from typing import Dict, Sequence, Tuple
 

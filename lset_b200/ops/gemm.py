@@ -9,7 +9,6 @@ Replaces the cuBLAS calls behind ``nn.Linear`` in the reference
 """
 from __future__ import annotations
 
-import ctypes
 
 import torch
 

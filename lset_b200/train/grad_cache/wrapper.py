@@ -9,7 +9,7 @@ parallelism pass 2 contains the cross-rank gather and its reduce-scatter backwar
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import torch
 
