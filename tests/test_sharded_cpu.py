@@ -50,9 +50,22 @@ def _worker(rank, world, port, out_dir):
     grads = [eng.store._gather_fp32(g, g.grad_shard) for g in eng.store.groups]
     eng.optimizer_step()
     params = {n: p.detach().clone() for n, p in eng.model.named_parameters()}
-    eng.save(1)   # the distributed checkpoint path (sharded optimizer state) must not raise
+    eng.save(1)   # the distributed checkpoint path (sharded optimizer state)
+    # round trip under sharding: train on, load the checkpoint back, state equals the saved state
+    from lset_b200.train.checkpoint import latest_checkpoint, load_checkpoint
+
+    m_saved = [g.exp_avg.clone() for g in eng.store.groups]
+    eng.train_step(_batch(8 + rank * 4, 12 + rank * 4))
+    moved = max(float((p.detach() - params[n]).abs().max()) for n, p in eng.model.named_parameters())
+    ckpt = latest_checkpoint(os.path.join(out_dir, "ckpt"))
+    step = load_checkpoint(eng.model, eng.optimizer, ckpt, store=eng.store)
+    back = max(float((p.detach() - params[n]).abs().max()) for n, p in eng.model.named_parameters())
+    m_back = max(float((g.exp_avg - m).abs().max()) for g, m in zip(eng.store.groups, m_saved))
+    roundtrip = {"step": step, "moved": moved, "back": back, "m_back": m_back,
+                 "steps_seen": eng.optimizer.step_count}
     if rank == 0:
-        torch.save({"loss": total, "grads": grads, "params": params}, os.path.join(out_dir, "dp.pt"))
+        torch.save({"loss": total, "grads": grads, "params": params, "roundtrip": roundtrip},
+                   os.path.join(out_dir, "dp.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -73,3 +86,6 @@ def test_two_ranks_match_single_process():
     for g, ref in zip(eng.store.groups, got["grads"]):
         # data-parallel mean of per-rank gradients = union-batch gradient / world
         assert torch.allclose(g.flat_grad / 2, ref, atol=2e-5), (g.flat_grad / 2 - ref).abs().max()
+    rt = got["roundtrip"]
+    assert rt["step"] == 1 and rt["moved"] > 1e-4 and rt["back"] < 1e-6 and rt["m_back"] < 1e-7, rt
+    assert rt["steps_seen"] == 1        # the optimizer's step counter came back with the state
