@@ -186,3 +186,65 @@ def test_gather_single_process_is_identity_with_gradient():
         assert torch.equal(y, x)
         g, = torch.autograd.grad(y.pow(2).sum(), x)
         assert torch.allclose(g, 2 * x)
+
+
+# ---------------------------------------------------------------------------------- chunked encoder
+def test_chunked_encoder_planning_cache_retry_and_memmap(tmp_path, monkeypatch):
+    import lset_b200.eval.chunked_encoder as ce
+
+    # chunks overlap by `overlap` tokens and cover the whole document
+    chunks = ce.chunk_ids(list(range(10)), chunk_len=4, overlap=1)
+    assert chunks == [[0, 1, 2, 3], [3, 4, 5, 6], [6, 7, 8, 9]]
+    assert ce.chunk_ids([1, 2], 4, 1) == [[1, 2]]
+    # streams: longest first, never above the budget unless a single chunk is
+    lens = [5, 9, 2, 7, 3]
+    streams = ce.plan_streams(lens, budget=10)
+    assert sorted(i for s in streams for i in s) == list(range(5))
+    assert all(sum(lens[i] for i in s) <= 10 for s in streams) and streams[0][0] == 1
+    assert ce.plan_streams([50], budget=10) == [[0]]
+    # tokenisation cache: the second call does not tokenise
+    calls = []
+
+    def tok(texts):
+        calls.append(len(texts))
+        return [[ord(c) % 50 + 1 for c in t] for t in texts]
+
+    a = ce.cached_tokenize(tok, ["abc", "de"], tmp_path / "cache")
+    b = ce.cached_tokenize(tok, ["abc", "de"], tmp_path / "cache")
+    assert a == b and calls == [2]
+    assert ce.cached_tokenize(tok, ["abc", "xy"], tmp_path / "cache") != a and calls == [2, 2]
+
+    cfg = Qwen3Config(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=1, head_dim=16)
+    torch.manual_seed(0)
+    model = Qwen3Decoder(cfg).eval()
+    init_normal_(model, 0.1)
+    texts = ["abcdefghij", "xyz", "", "mnopqrstuvwxyzabcd"]
+    ref = ce.encode_chunked(model, tok, None, texts, device="cpu", chunk_len=6, overlap=2,
+                            token_budget=64)
+    assert ref.shape == (4, 32) and np.allclose(np.linalg.norm(ref, axis=1), 1.0, atol=1e-5)
+    # a tiny budget (one chunk per stream) gives the same embeddings
+    small = ce.encode_chunked(model, tok, None, texts, device="cpu", chunk_len=6, overlap=2,
+                              token_budget=1)
+    assert np.allclose(ref, small, atol=1e-5)
+    # an out-of-memory error on a multi-chunk stream is retried in halves
+    real, state = model.forward, {"raised": 0}
+
+    def flaky(ids, **kw):
+        if kw["cu_seqlens"].numel() > 2 and state["raised"] < 2:
+            state["raised"] += 1
+            raise torch.cuda.OutOfMemoryError("simulated")
+        return real(ids, **kw)
+
+    monkeypatch.setattr(model, "forward", flaky)
+    again = ce.encode_chunked(model, tok, None, texts, device="cpu", chunk_len=6, overlap=2,
+                              token_budget=64)
+    assert state["raised"] == 2 and np.allclose(ref, again, atol=1e-5)
+    monkeypatch.setattr(model, "forward", real)
+    with pytest.raises(ValueError):
+        ce.encode_chunked(model, tok, None, texts, device="cpu", pooling="last_token", chunk_len=6)
+    # large result sets stream into a memmap on disk
+    monkeypatch.setattr(ce, "CPU_STREAM_THRESHOLD", 2)
+    mm = ce.encode_chunked(model, tok, None, texts, device="cpu", chunk_len=6, overlap=2,
+                           out_path=str(tmp_path / "emb.npy"))
+    assert isinstance(mm, np.memmap) and np.allclose(np.load(tmp_path / "emb.npy"), ref, atol=1e-5)
