@@ -225,10 +225,11 @@ class LSETConfig:
             for key, raw in body.items():
                 if key in hints:
                     ann = hints[key]
-                    # YAML already typed most scalars; only numeric strings ("2e-5") need help.
+                    # YAML already typed most scalars; numeric strings ("2e-5") and comma-separated
+                    # lists written as one string ("64,128") need help.
                     if isinstance(raw, str):
                         base = [a for a in typing.get_args(ann) if a is not type(None)] or [ann]
-                        if base[0] in (int, float):
+                        if base[0] in (int, float) or typing.get_origin(base[0]) in (list, List):
                             raw = convert(raw, ann)
                     setattr(section, key, raw)
         return cfg

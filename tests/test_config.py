@@ -54,3 +54,14 @@ def test_validate_rejects(setup):
     setup(c)
     with pytest.raises(ValueError):
         c.validate()
+
+
+def test_yaml_list_fields_accept_lists_and_comma_strings(tmp_path):
+    from lset_b200.config import LSETConfig
+
+    f = tmp_path / "c.yaml"
+    f.write_text("training:\n  matryoshka_dims: [64, 128]\neval:\n  tasks: STSBenchmark,SICK-R\n")
+    c = LSETConfig.from_yaml(f)
+    assert c.training.matryoshka_dims == [64, 128] and c.eval.tasks == ["STSBenchmark", "SICK-R"]
+    f.write_text("training:\n  matryoshka_dims: 64,128\n")
+    assert LSETConfig.from_yaml(f).training.matryoshka_dims == [64, 128]

@@ -120,3 +120,59 @@ logging:
     w = LSETMTEBModel.from_pretrained(str(model), device="cpu")
     emb = w.encode([["what is alpha 1", "beta gamma delta"]])
     assert emb.shape == (2, 32)
+
+
+def _bert_dir(path):
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+
+    vocab = {"[PAD]": 0, "[UNK]": 1, **{w: i + 2 for i, w in enumerate(WORDS)},
+             **{str(i): len(WORDS) + 2 + i for i in range(64)}}
+    tok = Tokenizer(WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = Whitespace()
+    cfg = T.BertConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=4, max_position_embeddings=128)
+    torch.manual_seed(0)
+    T.BertModel(cfg).save_pretrained(str(path))
+    tok.save(str(path / "tokenizer.json"))
+    return path
+
+
+@pytest.mark.parametrize("variant", ["bert_padded_scored_gradcache", "qwen3_lora_ac_matryoshka"])
+def test_cli_train_variants(tmp_path, variant):
+    """Other corners of the YAML surface through the real CLI: an encoder with padded batches,
+    the scored (soft-label) and multi-positive dataset formats, GradCache; LoRA with activation
+    checkpointing and matryoshka dims on the decoder."""
+    data = tmp_path / "train.jsonl"
+    bert = variant.startswith("bert")
+    model = _bert_dir(tmp_path / "model") if bert else _model_dir(tmp_path / "model")
+    with open(data, "w") as fh:
+        for i in range(24):
+            q = f"what is {WORDS[i % 16]} {i}"
+            docs = [" ".join(WORDS[(i + k * j) % 16] for j in range(6 + k)) for k in range(1, 4)]
+            if bert:
+                row = {"query": q, "documents": [{"text": d, "score": float(3 - k)}
+                                                 for k, d in enumerate(docs)]}
+            else:
+                row = {"query": q, "positives": docs[:2], "negatives": docs[2:]}
+            fh.write(json.dumps(row) + "\n")
+    out = tmp_path / "run"
+    extra = ("packing:\n  enabled: false\ngrad_cache:\n  enabled: true\n  chunk_size: 2\n" if bert else
+             "packing:\n  enabled: true\nlora:\n  enabled: true\n  r: 4\n  alpha: 8\n"
+             "activation_checkpoint:\n  enabled: true\n  mode: selective\n")
+    cfg = tmp_path / "cfg.yaml"
+    cfg.write_text(f"model:\n  path: {model}\ndata:\n  train_path: {data}\n  max_seq_length: 32\n"
+                   f"  num_hard_negatives: 1\ntraining:\n  batch_size: 4\n  lr: 1.0e-3\n  max_steps: 3\n"
+                   f"  scheduler: cosine\n  warmup_steps: 1\n  temperature: 0.05\n"
+                   + ("" if bert else "  matryoshka_dims: 16,32\n") + extra +
+                   f"checkpoint:\n  save_steps: 3\n  output_dir: {out}\nlogging:\n  log_interval: 1\n")
+    r = _run(["-m", "lset_b200.cli", "train", "--config", str(cfg)])
+    assert r.returncode == 0, (r.stdout[-1000:], r.stderr[-2000:])
+    losses = [float(tok.split("=")[1]) for line in r.stdout.splitlines() if line.startswith("step=")
+              for tok in line.split() if tok.startswith("loss=")]
+    assert len(losses) == 3 and all(v == v and abs(v) < 1e4 for v in losses), losses
+    assert os.path.exists(out / "step_3" / "meta.pt")
+    if not bert:
+        blob = torch.load(out / "step_3" / "checkpoint.pt", weights_only=False)
+        assert any("lora_A" in k for k in blob["model"])
