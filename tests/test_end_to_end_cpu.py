@@ -176,3 +176,40 @@ def test_cli_train_variants(tmp_path, variant):
     if not bert:
         blob = torch.load(out / "step_3" / "checkpoint.pt", weights_only=False)
         assert any("lora_A" in k for k in blob["model"])
+
+
+def test_cli_multiprocess_dp_and_tp(tmp_path):
+    """``cli train`` with a world size above one re-executes itself under torchrun (gloo on a
+    machine without GPUs): sharded data parallelism, tensor parallelism, and both with the
+    sequence-parallel scheme. The same global batches give the same losses with and without
+    tensor parallelism, and the checkpoint is the sharded (DCP) layout with one file per rank."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(48):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positive": " ".join(WORDS[(i + j) % 16] for j in range(12)),
+                                 "negatives": [" ".join(WORDS[(i + 3 * j) % 16] for j in range(9))]}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+    losses = {}
+    for tag, extra in (("dp2", ["--distributed.dp_size", "2"]),
+                       ("tp2", ["--distributed.tp_size", "2"]),
+                       ("dp2tp2", ["--distributed.dp_size", "2", "--distributed.tp_size", "2",
+                                   "--distributed.async_tp", "true"])):
+        out = tmp_path / tag
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--training.batch_size", "4",
+                  "--training.max_steps", "3", "--training.lr", "1e-3", "--packing.enabled", "true",
+                  "--checkpoint.save_steps", "3", "--checkpoint.output_dir", str(out),
+                  "--logging.log_interval", "1", *extra])
+        assert r.returncode == 0, (tag, r.stderr[-2000:])
+        losses[tag] = [float(tok.split("=")[1]) for line in r.stdout.splitlines()
+                       if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
+        assert len(losses[tag]) == 3, (tag, r.stdout[-500:])
+        files = os.listdir(out / "step_3")
+        world = 4 if tag == "dp2tp2" else 2
+        assert "meta.pt" in files and ".metadata" in files
+        assert sum(f.endswith(".distcp") for f in files) == world
+    for a, b in zip(losses["dp2"], losses["dp2tp2"]):
+        assert abs(a - b) < 1e-3 * max(1.0, abs(a)), (losses["dp2"], losses["dp2tp2"])
