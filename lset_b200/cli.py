@@ -50,11 +50,25 @@ def _load(args, usage: str):
     return cfg, path, overrides
 
 
+def _rendezvous_port() -> int:
+    """``MASTER_PORT`` when the caller set one, else a port that is free right now (two jobs on
+    one machine must not meet on the launcher's default port)."""
+    import os
+    import socket
+
+    if os.environ.get("MASTER_PORT", "").isdigit():
+        return int(os.environ["MASTER_PORT"])
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def launcher_command(config, config_path: str, overrides) -> list:
     """The torchrun command line that ``train`` re-executes for a multi-GPU job."""
     world = config.distributed.dp_size * config.distributed.tp_size
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
-           f"--nproc_per_node={world}", "--master-addr", "127.0.0.1"]
+           f"--nproc_per_node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_rendezvous_port())]
     if config.distributed.max_restarts > 0:
         cmd.append(f"--max-restarts={config.distributed.max_restarts}")
     cmd += ["-m", "lset_b200.train.main", "--config", config_path]
