@@ -32,6 +32,7 @@ from ..tasks.bi_encoder import BiEncoderTask, global_loss_value
 from .checkpoint import latest_checkpoint, load_checkpoint, load_extra, save_checkpoint
 from .logging import TrainLogger
 from .scheduler import build_scheduler
+from .watchdog import maybe_fail
 from ..utils.tracing import PhaseTimer
 
 
@@ -70,6 +71,22 @@ def batch_bytes(obj) -> int:
     if isinstance(obj, dict):
         return sum(batch_bytes(v) for v in obj.values())
     return 0
+
+
+def _init_process_group(backend: str, rank: int, world: int) -> None:
+    """``init_process_group`` from the launcher's environment. A worker group restarted by the
+    launcher (``--max-restarts``) meets on the same store as the attempt before it; its rendezvous
+    keys are put under a prefix of their own so that addresses left by dead workers are not read."""
+    restart = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0"))
+    if restart == 0 or "MASTER_ADDR" not in os.environ or "MASTER_PORT" not in os.environ:
+        dist.init_process_group(backend)
+        return
+    from datetime import timedelta
+
+    store = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), world,
+                          is_master=False, timeout=timedelta(seconds=300))
+    dist.init_process_group(backend, store=dist.PrefixStore(f"attempt{restart}", store), rank=rank,
+                            world_size=world)
 
 
 class TrainingEngine:
@@ -124,7 +141,7 @@ class TrainingEngine:
         self.local_rank = int(os.environ.get("LOCAL_RANK", 0))
         use_cuda = torch.cuda.is_available() and device != "cpu"
         if world > 1 and not dist.is_initialized():
-            dist.init_process_group("nccl" if use_cuda else "gloo")
+            _init_process_group("nccl" if use_cuda else "gloo", self.rank, world)
             self.needs_dist_cleanup = True
         if use_cuda:
             torch.cuda.set_device(self.local_rank)
@@ -395,6 +412,7 @@ class TrainingEngine:
                     made_progress = True
                     n_pairs = self._batch_pairs(batch)
                     n_tok = batch_tokens(batch)
+                    maybe_fail(step, self.rank)      # host-side fault injection (off unless asked for)
                     loss = self.train_step(batch)
                     tp = self.logger.update_throughput(n_pairs * self.dp_size, n_tok * self.dp_size)
                     if self.log_interval and step % self.log_interval == 0:

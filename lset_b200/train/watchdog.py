@@ -62,3 +62,37 @@ class StepWatchdog:
                 if self.exit_process:
                     os._exit(EXIT_CODE)
                 return
+
+
+class InjectedFailure(RuntimeError):
+    """Raised by ``maybe_fail`` (host-side fault injection)."""
+
+
+def maybe_fail(step: int, rank: int) -> None:
+    """Host-side fault injection for recovery tests and drills.
+
+    ``LSET_B200_FAIL_AT_STEP="<step>[,<rank>[,<mode>]]"`` makes rank ``<rank>`` (default 0) fail
+    right before optimizer step ``<step>`` on the first attempt of a job (a group restarted by the
+    launcher runs through): ``mode`` ``raise`` (default) raises ``InjectedFailure``, ``exit`` ends
+    the process with the watchdog's exit code. The failure happens between steps on the host; on a
+    GPU the device is synchronised first, so no kernel or collective of this rank is in flight.
+    Nothing on the device is made to fault.
+    """
+    spec = os.environ.get("LSET_B200_FAIL_AT_STEP")
+    if not spec or int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")) > 0:
+        return
+    parts = spec.split(",")
+    if step != int(parts[0]) or rank != (int(parts[1]) if len(parts) > 1 and parts[1] else 0):
+        return
+    try:
+        import torch
+
+        if torch.cuda.is_available() and torch.cuda.is_initialized():
+            torch.cuda.synchronize()
+    except Exception:  # pragma: no cover - best effort before leaving
+        pass
+    mode = parts[2] if len(parts) > 2 else "raise"
+    print(f"[fault injection] rank {rank} fails before step {step} ({mode})", file=sys.stderr, flush=True)
+    if mode == "exit":
+        os._exit(EXIT_CODE)
+    raise InjectedFailure(f"injected failure on rank {rank} before step {step}")
