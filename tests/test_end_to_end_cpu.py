@@ -249,3 +249,35 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path):
     # first attempt: steps 0..2, checkpoint after step index 1; second attempt resumes at 2
     assert steps == [0, 1, 2, 2, 3, 4], steps
     assert os.path.exists(out / "step_4" / "meta.pt")
+
+
+def test_checkpoints_move_between_world_sizes(tmp_path):
+    """A sharded (two-rank) checkpoint resumes in a single process and a single-process checkpoint
+    resumes on two ranks (``checkpoint.resume_from: auto`` picks the newest complete one)."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positive": " ".join(WORDS[(i + j) % 16] for j in range(12))}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+
+    def run(out, steps, *extra):
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--training.batch_size", "4",
+                  "--training.max_steps", str(steps), "--training.lr", "1e-3",
+                  "--packing.enabled", "true", "--checkpoint.save_steps", "2",
+                  "--checkpoint.output_dir", str(out), "--logging.log_interval", "1", *extra])
+        assert r.returncode == 0, r.stderr[-2000:]
+        return [int(line.split()[0].split("=")[1]) for line in r.stdout.splitlines()
+                if line.startswith("step=")]
+
+    two = ("--distributed.dp_size", "2")
+    assert run(tmp_path / "a", 2, *two) == [0, 1]
+    assert os.path.exists(tmp_path / "a" / "step_2" / ".metadata")
+    assert run(tmp_path / "a", 4, "--checkpoint.resume_from", "auto") == [2, 3]
+    assert os.path.exists(tmp_path / "a" / "step_4" / "checkpoint.pt")
+    assert run(tmp_path / "b", 2) == [0, 1]
+    assert run(tmp_path / "b", 4, *two, "--checkpoint.resume_from", "auto") == [2, 3]
+    assert os.path.exists(tmp_path / "b" / "step_4" / ".metadata")
