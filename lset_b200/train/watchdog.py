@@ -74,7 +74,8 @@ def maybe_fail(step: int, rank: int) -> None:
     ``LSET_B200_FAIL_AT_STEP="<step>[,<rank>[,<mode>]]"`` makes rank ``<rank>`` (default 0) fail
     right before optimizer step ``<step>`` on the first attempt of a job (a group restarted by the
     launcher runs through): ``mode`` ``raise`` (default) raises ``InjectedFailure``, ``exit`` ends
-    the process with the watchdog's exit code. The failure happens between steps on the host; on a
+    the process with the watchdog's exit code, ``hang`` sleeps on the host (what a stuck data
+    loader looks like; the step watchdog is what ends it). The failure happens between steps on the host; on a
     GPU the device is synchronised first, so no kernel or collective of this rank is in flight.
     Nothing on the device is made to fault.
     """
@@ -95,4 +96,7 @@ def maybe_fail(step: int, rank: int) -> None:
     print(f"[fault injection] rank {rank} fails before step {step} ({mode})", file=sys.stderr, flush=True)
     if mode == "exit":
         os._exit(EXIT_CODE)
+    if mode == "hang":
+        while True:
+            time.sleep(3600.0)
     raise InjectedFailure(f"injected failure on rank {rank} before step {step}")

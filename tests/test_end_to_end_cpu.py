@@ -215,10 +215,12 @@ def test_cli_multiprocess_dp_and_tp(tmp_path):
         assert abs(a - b) < 1e-3 * max(1.0, abs(a)), (losses["dp2"], losses["dp2tp2"])
 
 
-def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path):
-    """A rank that fails on the host between steps (injected: an exception before step 3 on rank 1,
-    first attempt only) takes the worker group down; the launcher restarts it
-    (``distributed.max_restarts``) and the job continues from the newest complete checkpoint."""
+@pytest.mark.parametrize("mode", ["raise", "hang"])
+def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path, mode):
+    """A rank that fails on the host between steps (injected before step 3 on rank 1, first attempt
+    only: an exception, or a host-side hang that the step watchdog ends) takes the worker group
+    down; the launcher restarts it (``distributed.max_restarts``) and the job continues from the
+    newest complete checkpoint."""
     model = _model_dir(tmp_path / "model")
     data = tmp_path / "train.jsonl"
     with open(data, "w") as fh:
@@ -228,7 +230,7 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path):
     (tmp_path / "empty.yaml").write_text("{}\n")
     out = tmp_path / "run"
     env_backup = os.environ.get("LSET_B200_FAIL_AT_STEP")
-    os.environ["LSET_B200_FAIL_AT_STEP"] = "3,1,raise"
+    os.environ["LSET_B200_FAIL_AT_STEP"] = f"3,1,{mode}"
     try:
         r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
                   "--model.path", str(model), "--data.train_path", str(data),
@@ -236,7 +238,7 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path):
                   "--training.max_steps", "5", "--training.lr", "1e-3", "--packing.enabled", "true",
                   "--checkpoint.save_steps", "2", "--checkpoint.output_dir", str(out),
                   "--logging.log_interval", "1", "--distributed.dp_size", "2",
-                  "--distributed.max_restarts", "1"])
+                  "--distributed.max_restarts", "1", "--distributed.step_timeout_s", "8"])
     finally:
         if env_backup is None:
             os.environ.pop("LSET_B200_FAIL_AT_STEP", None)
@@ -244,6 +246,8 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path):
             os.environ["LSET_B200_FAIL_AT_STEP"] = env_backup
     assert r.returncode == 0, r.stderr[-3000:]
     assert "[fault injection] rank 1 fails before step 3" in r.stderr
+    if mode == "hang":
+        assert "[watchdog] rank 1: no training step finished" in r.stderr
     steps = [int(line.split()[0].split("=")[1]) for line in r.stdout.splitlines()
              if line.startswith("step=")]
     # first attempt: steps 0..2, checkpoint after step index 1; second attempt resumes at 2
