@@ -285,3 +285,38 @@ def test_checkpoints_move_between_world_sizes(tmp_path):
     assert run(tmp_path / "b", 2) == [0, 1]
     assert run(tmp_path / "b", 4, *two, "--checkpoint.resume_from", "auto") == [2, 3]
     assert os.path.exists(tmp_path / "b" / "step_4" / ".metadata")
+
+
+@pytest.mark.parametrize("tag,options", [
+    ("gradcache_dp2", ["--distributed.dp_size", "2", "--grad_cache.enabled", "true",
+                       "--grad_cache.token_budget", "150"]),
+    ("lora_tp2", ["--distributed.tp_size", "2", "--lora.enabled", "true", "--lora.r", "4"]),
+    ("fp8_tp2", ["--distributed.tp_size", "2", "--fp8.enabled", "true", "--fp8.recipe", "rowwise"]),
+    ("padded_sp_dp2_tp2_ac", ["--packing.enabled", "false", "--distributed.dp_size", "2",
+                              "--distributed.tp_size", "2", "--distributed.async_tp", "true",
+                              "--activation_checkpoint.enabled", "true"]),
+])
+def test_cli_multiprocess_feature_combinations(tmp_path, tag, options):
+    """Feature combinations that involve collectives of their own, through the launcher on CPU:
+    GradCache with rank-aligned minibatch plans, LoRA and FP8 layers under tensor parallelism,
+    sequence parallelism on padded batches with data parallelism and activation checkpointing."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positives": [" ".join(WORDS[(i + j) % 16] for j in range(12)),
+                                               " ".join(WORDS[(i + 2 * j) % 16] for j in range(7))],
+                                 "negatives": [" ".join(WORDS[(i + 3 * j) % 16] for j in range(9))]}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+    r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+              "--model.path", str(model), "--data.train_path", str(data),
+              "--data.max_seq_length", "48", "--data.num_hard_negatives", "1",
+              "--training.batch_size", "4", "--training.max_steps", "2", "--training.lr", "1e-3",
+              "--packing.enabled", "true", "--checkpoint.save_steps", "0",
+              "--checkpoint.output_dir", str(tmp_path / "out"), "--logging.log_interval", "1",
+              *options])
+    assert r.returncode == 0, r.stderr[-2000:]
+    losses = [float(tok.split("=")[1]) for line in r.stdout.splitlines() if line.startswith("step=")
+              for tok in line.split() if tok.startswith("loss=")]
+    assert len(losses) == 2 and all(v == v and abs(v) < 1e4 for v in losses), losses
