@@ -248,3 +248,53 @@ def test_chunked_encoder_planning_cache_retry_and_memmap(tmp_path, monkeypatch):
     mm = ce.encode_chunked(model, tok, None, texts, device="cpu", chunk_len=6, overlap=2,
                            out_path=str(tmp_path / "emb.npy"))
     assert isinstance(mm, np.memmap) and np.allclose(np.load(tmp_path / "emb.npy"), ref, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------- tracing / options
+def test_roofline_arithmetic_and_peak_loading(tmp_path):
+    from lset_b200.utils.tracing import FALLBACK_PEAKS, PhaseTimer, load_peaks, nvtx_range, roofline
+
+    missing = load_peaks(str(tmp_path / "nope.json"))
+    assert missing["source"] == "fallback" and missing["hbm_gbs"] == FALLBACK_PEAKS["hbm_gbs"]
+    f = tmp_path / "peaks.json"
+    f.write_text('{"hbm_gbs": 6000.0, "bf16_tflops": 1500.0, "clocks": {"sm": 1900}}')
+    peaks = load_peaks(str(f))
+    assert peaks["source"] == "measured" and peaks["hbm_gbs"] == 6000.0
+    assert peaks["bf16_tflops_sustained"] == FALLBACK_PEAKS["bf16_tflops_sustained"]   # absent key
+    # 1 ms for 1.5 PFLOP-ms of math at a 1500 TFLOP/s peak = exactly at the compute roof
+    r = roofline(1.0, flops=1.5e12, hbm_bytes=1e9, peaks=peaks)
+    assert r["bound"] == "compute" and r["fraction_of_roof"] == pytest.approx(1.0)
+    assert r["tflops"] == pytest.approx(1500.0) and r["hbm_gbs"] == pytest.approx(1000.0)
+    # a copy of 12 GB in 4 ms at 6000 GB/s: memory-bound, half of the roof
+    r = roofline(4.0, hbm_bytes=12e9, peaks=peaks)
+    assert r["bound"] == "hbm" and r["fraction_of_roof"] == pytest.approx(0.5)
+    # bytes that must cross NVLink bind a fused collective
+    r = roofline(1.0, flops=1e9, nvlink_bytes=0.385e9, peaks=peaks)
+    assert r["bound"] == "nvlink" and r["fraction_of_roof"] == pytest.approx(0.5)
+    assert roofline(1.0, flops=1.4e12, peaks=dict(peaks), sustained=True)["fraction_of_roof"] == \
+        pytest.approx(1.0)
+    # without a GPU the timer and the NVTX range are inert
+    t = PhaseTimer()
+    with t.phase("x"), nvtx_range("y"):
+        pass
+    assert t.report() == {}
+
+
+def test_runtime_options_and_reference_env_switches(monkeypatch):
+    from lset_b200.ops import runtime_options as ro
+
+    saved = dict(vars(ro.options))
+    try:
+        assert ro.enabled("fused_rmsnorm") and not ro.enabled("fused_glu_gemm")
+        monkeypatch.setenv("LSET_DISABLE_FUSED_RMSNORM", "1")      # the reference's switch
+        assert not ro.enabled("fused_rmsnorm") and ro.enabled("fused_layernorm")
+        monkeypatch.delenv("LSET_DISABLE_FUSED_RMSNORM")
+        ro.configure(fused_layernorm=False, attention_backend="flash_attn")
+        assert not ro.enabled("fused_layernorm") and ro.options.attention_backend == "native"
+        ro.configure(fused=False)
+        assert not ro.enabled("fused_rmsnorm")
+        with pytest.raises(ValueError):
+            ro.configure(no_such_switch=True)
+    finally:
+        for k, v in saved.items():
+            setattr(ro.options, k, v)
