@@ -4,6 +4,10 @@
 * multi-positive: ``mean_q( -mean_{p in pos(q)} sim[q,p] + logsumexp_{valid} sim[q,:] )``
 * soft labels (``scores`` given): targets are the teacher scores over the non-ignored columns,
   normalised to sum to one; loss is ``logsumexp_{valid} sim[q,:] - sum_k target[q,k] sim[q,k]``.
+  Non-finite scores mean "no teacher score": target 0. (The reference leaves the collator's -inf
+  fill for other samples' documents in the targets, lset/train/data/collator.py:190-199 with
+  lset/losses/contrastive.py:26-38, which makes every row's target sum -inf and the loss of a
+  scored dataset identically zero.)
 Queries without a positive (resp. with a zero score sum) or without a valid column are skipped;
 with none left the result is a zero that still carries gradient. bf16 CUDA inputs with a Python
 float temperature run on the streaming tensor-core kernels (``ops.loss.fused_label_loss``), which
@@ -29,7 +33,10 @@ def contrastive_loss(query_embeds, doc_embeds, labels, temperature=0.02, scores=
     valid = labels >= 0
     masked = sim.masked_fill(~valid, float("-inf"))
     if scores is not None:
-        target = scores.to(sim.device).float().masked_fill(~valid, 0.0)
+        # "no teacher score" entries (the collator fills documents of other samples with -inf)
+        # are in-batch negatives with target 0
+        target = torch.nan_to_num(scores.to(sim.device).float(), nan=0.0, posinf=0.0, neginf=0.0)
+        target = target.masked_fill(~valid, 0.0)
         tsum = target.sum(dim=1)
         keep = (tsum > 0) & valid.any(dim=1)
         if not keep.any():

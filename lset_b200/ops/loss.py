@@ -206,6 +206,7 @@ def fused_label_loss(q, k, labels, temperature: float, scores=None):
     if scores is not None:
         tw = torch.zeros(Q, Kp, dtype=torch.float32, device=dev)
         tw[:, :K] = scores.to(dev, torch.float32)
+        torch.nan_to_num_(tw, nan=0.0, posinf=0.0, neginf=0.0)   # "no teacher score": target 0
         tw[:, :K].masked_fill_(labels < 0, 0.0)
         tsum = tw.sum(dim=1)
         keep = (tsum > 0) & any_valid

@@ -113,3 +113,28 @@ def test_fused_dispatcher_follows_reference_thresholds_and_falls_back_on_cpu():
     a = fused_contrastive_loss(q, d, labels, 0.1, pos_qi=qi, pos_di=di, force_fused=True)
     b = contrastive_loss(q, d, labels, 0.1)
     assert torch.allclose(a, b)
+
+
+def test_scored_batches_train_documents_of_other_samples_are_negatives():
+    """The collator fills the score matrix with -inf for documents of other samples; those are
+    in-batch negatives with target 0, and the loss of a scored batch is the soft-label
+    cross-entropy over all documents (not identically zero)."""
+    from lset_b200.losses.contrastive import contrastive_loss
+
+    torch.manual_seed(0)
+    q = torch.nn.functional.normalize(torch.randn(3, 16), dim=-1).requires_grad_()
+    d = torch.nn.functional.normalize(torch.randn(6, 16), dim=-1).requires_grad_()
+    labels = torch.zeros(3, 6)
+    scores = torch.full((3, 6), float("-inf"))
+    for i in range(3):
+        labels[i, 2 * i] = 1.0
+        scores[i, 2 * i], scores[i, 2 * i + 1] = 3.0, 1.0
+    loss = contrastive_loss(q, d, labels, 0.05, scores=scores)
+    sim = (q @ d.t()) / 0.05
+    target = torch.zeros(3, 6)
+    for i in range(3):
+        target[i, 2 * i], target[i, 2 * i + 1] = 0.75, 0.25
+    want = (torch.logsumexp(sim, dim=1) - (target * sim).sum(1)).mean()
+    assert float(loss) > 0 and torch.allclose(loss, want, atol=1e-5)
+    loss.backward()
+    assert torch.isfinite(q.grad).all() and torch.isfinite(d.grad).all() and float(d.grad.abs().sum()) > 0
