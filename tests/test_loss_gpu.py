@@ -167,3 +167,32 @@ def test_fused_dense_loss_types(loss_type, Q, K, D, give_idx):
         err = (a.float() - b).abs().max().item()
         assert err < 3e-2 * (b.abs().max().item() + 1e-6), (name, err, b.abs().max().item())
     assert q.grad[4].abs().max().item() == 0.0
+
+
+def test_fused_label_loss_reads_missing_teacher_scores_as_zero_targets():
+    """Score matrices from the collator hold -inf for documents of other samples: the streaming
+    kernels must treat them as targets of zero (in-batch negatives), with finite loss and
+    gradients equal to the eager soft-label cross-entropy on the zero-filled scores."""
+    from lset_b200.ops.loss import fused_label_loss
+
+    Q, per, D = 96, 4, 512
+    K = Q * per
+    q, k = _emb(Q, D, 16).requires_grad_(), _emb(K, D, 17).requires_grad_()
+    labels = torch.zeros(Q, K, device="cuda")
+    scores = torch.full((Q, K), float("-inf"), device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    vals = torch.rand(Q, per, device="cuda", generator=g) * 3 + 0.1
+    for j in range(per):
+        cols = torch.arange(Q, device="cuda") * per + j
+        scores[torch.arange(Q, device="cuda"), cols] = vals[:, j]
+    labels[torch.arange(Q, device="cuda"), torch.arange(Q, device="cuda") * per] = 1.0
+    loss = fused_label_loss(q, k, labels, 0.05, scores)
+    loss.backward()
+    nv.check_status()
+    assert torch.isfinite(loss) and torch.isfinite(q.grad).all() and torch.isfinite(k.grad).all()
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    ref = _eager_label_loss(qr, kr, labels, 0.05, torch.nan_to_num(scores, neginf=0.0))
+    ref.backward()
+    assert ref.item() > 0 and abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item()))
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad)):
+        assert (a.float() - b).abs().max().item() < 3e-2 * (b.abs().max().item() + 1e-6)
