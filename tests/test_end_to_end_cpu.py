@@ -320,3 +320,15 @@ def test_cli_multiprocess_feature_combinations(tmp_path, tag, options):
     losses = [float(tok.split("=")[1]) for line in r.stdout.splitlines() if line.startswith("step=")
               for tok in line.split() if tok.startswith("loss=")]
     assert len(losses) == 2 and all(v == v and abs(v) < 1e4 for v in losses), losses
+
+
+def test_cli_eval_without_mteb_says_what_is_missing(tmp_path):
+    try:
+        import mteb  # noqa: F401
+        pytest.skip("mteb is installed")
+    except ImportError:
+        pass
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text(f"model:\n  path: {tmp_path}\neval:\n  tasks: [STSBenchmark]\n")
+    r = _run(["-m", "lset_b200.cli", "eval", "--config", str(cfg)])
+    assert r.returncode != 0 and "mteb" in (r.stderr + r.stdout)
