@@ -332,3 +332,40 @@ def test_cli_eval_without_mteb_says_what_is_missing(tmp_path):
     cfg.write_text(f"model:\n  path: {tmp_path}\neval:\n  tasks: [STSBenchmark]\n")
     r = _run(["-m", "lset_b200.cli", "eval", "--config", str(cfg)])
     assert r.returncode != 0 and "mteb" in (r.stderr + r.stdout)
+
+
+def test_run_eval_with_a_stand_in_for_mteb(tmp_path, monkeypatch, capsys):
+    """``run_eval`` glue (cf. lset/eval/run.py:10-46) against a stand-in ``mteb`` module: the model
+    is loaded from the checkpoint directory, handed to ``mteb.evaluate`` with the configured tasks
+    and batch size, and the main score of every task is printed and returned."""
+    import types
+
+    model = _model_dir(tmp_path / "model")
+    seen = {}
+
+    class Result:
+        def __init__(self, name, score):
+            self.task_name, self._score = name, score
+
+        def get_score(self):
+            return self._score
+
+    def evaluate(wrapper, tasks, encode_kwargs=None):
+        seen["tasks"], seen["kwargs"] = list(tasks), encode_kwargs
+        emb = wrapper.encode([{"text": ["what is alpha 1", "beta gamma"]}])
+        sim = wrapper.similarity(emb, emb)
+        return types.SimpleNamespace(task_results=[Result(t, float(sim[0, 1])) for t in tasks])
+
+    fake = types.SimpleNamespace(get_tasks=lambda tasks: list(tasks), evaluate=evaluate)
+    monkeypatch.setitem(sys.modules, "mteb", fake)
+    from lset_b200.config import LSETConfig
+    from lset_b200.eval.run import run_eval
+
+    cfg = LSETConfig()
+    cfg.apply_overrides([("model.path", str(model)), ("eval.tasks", "STSBenchmark,SICK-R"),
+                         ("eval.batch_size", "16"), ("eval.max_length", "32")])
+    scores = run_eval(cfg)
+    assert seen["tasks"] == ["STSBenchmark", "SICK-R"] and seen["kwargs"] == {"batch_size": 16}
+    assert set(scores) == {"STSBenchmark", "SICK-R"} and all(-1.0 <= v <= 1.0 for v in scores.values())
+    out = capsys.readouterr().out
+    assert "STSBenchmark: main_score=" in out and "SICK-R: main_score=" in out
