@@ -114,3 +114,37 @@ def test_split_helpers_agree_with_ranges():
             if s > 0:
                 assert points[f"layers.{lo}"] == "BEGINNING"
         assert len(points) == pp - 1
+
+
+def _mesh_worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lset_b200.dist.mesh import build_mesh
+
+    m2 = build_mesh(dp_size=2, tp_size=2, device_type="cpu")
+    m3 = build_mesh(dp_size=1, tp_size=2, pp_size=2, device_type="cpu")
+    info = {"names2": m2.mesh_dim_names, "names3": m3.mesh_dim_names,
+            "tp2": dist.get_process_group_ranks(m2.get_group("tp")),
+            "dp2": dist.get_process_group_ranks(m2.get_group("dp")),
+            "pp3": dist.get_process_group_ranks(m3.get_group("pp")),
+            "tp3": dist.get_process_group_ranks(m3.get_group("tp"))}
+    # a collective over the tensor-parallel sub-group only sums its two members
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=m2.get_group("tp"))
+    info["tp_sum"] = float(t)
+    torch.save(info, os.path.join(out_dir, f"mesh{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_mesh_layout_tp_innermost_pp_outermost():
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_mesh_worker, args=(4, _port(), out_dir), nprocs=4, join=True)
+    got = [torch.load(os.path.join(out_dir, f"mesh{r}.pt"), weights_only=False) for r in range(4)]
+    assert got[0]["names2"] == ("dp", "tp") and got[0]["names3"] == ("pp", "dp", "tp")
+    assert [g["tp2"] for g in got] == [[0, 1], [0, 1], [2, 3], [2, 3]]     # neighbours share TP
+    assert [g["dp2"] for g in got] == [[0, 2], [1, 3], [0, 2], [1, 3]]
+    assert [g["pp3"] for g in got] == [[0, 2], [1, 3], [0, 2], [1, 3]]
+    assert [g["tp3"] for g in got] == [[0, 1], [0, 1], [2, 3], [2, 3]]
+    assert [g["tp_sum"] for g in got] == [1.0, 1.0, 5.0, 5.0]
