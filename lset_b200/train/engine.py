@@ -255,6 +255,7 @@ class TrainingEngine:
 
         # ---------------------------------------------------------------- data
         self.dataset = dataset
+        self._data_gen, self._data_seed, self._batch_in_epoch = None, seed, 0
         self.collator = collator if collator is not None else self._pick_collator(
             dataset, tokenizer, max_seq_length, length_sorted)
         self.sampler = None
@@ -264,6 +265,7 @@ class TrainingEngine:
                 self.sampler = DistributedSampler(dataset, num_replicas=dp_size, rank=self.dp_rank,
                                                   shuffle=True, seed=seed)
             gen = torch.Generator().manual_seed(seed)
+            self._data_gen, self._data_seed = gen, seed
             self.dataloader = DataLoader(
                 dataset, batch_size=batch_size, sampler=self.sampler,
                 shuffle=self.sampler is None, collate_fn=self.collator, drop_last=True,
@@ -382,7 +384,7 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------ loop
     def train(self):
-        start = 0
+        start, skip = 0, 0
         resume = self.resume_from
         if resume == "auto":
             resume = latest_checkpoint(self.output_dir)
@@ -394,6 +396,7 @@ class TrainingEngine:
                 self.epoch = int(extra.get("epoch", 0))
                 if "rng" in extra:
                     torch.set_rng_state(extra["rng"])
+                skip = int(extra.get("batch_in_epoch", 0))
             self.micro_step = start
         step = start
         last_loss = None
@@ -405,11 +408,21 @@ class TrainingEngine:
             while step < self.max_steps:
                 if self.sampler is not None:
                     self.sampler.set_epoch(self.epoch)
-                made_progress = False
-                for batch in self.dataloader:
+                if self._data_gen is not None:
+                    # the order of an epoch depends on (seed, epoch) only, so that a resumed run
+                    # can continue in the middle of one
+                    self._data_gen.manual_seed(self._data_seed + self.epoch)
+                batches = iter(self.dataloader)
+                made_progress = skip > 0
+                for _ in range(skip):          # resume: batches this epoch had already consumed
+                    if next(batches, None) is None:
+                        break
+                self._batch_in_epoch, skip = skip, 0
+                for batch in batches:
                     if step >= self.max_steps:
                         break
                     made_progress = True
+                    self._batch_in_epoch += 1
                     n_pairs = self._batch_pairs(batch)
                     n_tok = batch_tokens(batch)
                     maybe_fail(step, self.rank)      # host-side fault injection (off unless asked for)
@@ -428,7 +441,9 @@ class TrainingEngine:
                     if self.save_steps and (step + 1) % self.save_steps == 0:
                         self.save(step + 1)
                     step += 1
-                self.epoch += 1
+                if step < self.max_steps:
+                    self.epoch += 1
+                    self._batch_in_epoch = 0
                 if not made_progress:
                     break
         finally:
@@ -443,7 +458,8 @@ class TrainingEngine:
 
     def save(self, step: int) -> str:
         extra = {"scheduler": self.scheduler.state_dict(), "epoch": self.epoch,
-                 "rng": torch.get_rng_state(), "micro_step": self.micro_step}
+                 "rng": torch.get_rng_state(), "micro_step": self.micro_step,
+                 "batch_in_epoch": self._batch_in_epoch}
         return save_checkpoint(self.model, self.optimizer, step, self.output_dir, store=self.store,
                                extra=extra)
 

@@ -111,3 +111,38 @@ def test_train_runs(workspace, capsys, family, fmt, options):
     losses = [float(tok.split("=")[1]) for line in out.splitlines() if line.startswith("step=")
               for tok in line.split() if tok.startswith("loss=")]
     assert len(losses) >= 2 and all(math.isfinite(v) for v in losses), (losses, out[-500:])
+
+
+@pytest.mark.parametrize("packed", ["true", "false"])
+def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, packed):
+    """An interrupted run that resumes from its checkpoint sees the batches the uninterrupted run
+    would have seen (the order of an epoch depends on seed and epoch only; the checkpoint records
+    how far into the epoch it was) and therefore logs the same losses, also across an epoch end."""
+    root, dirs, files = workspace
+
+    def run(out, max_steps, resume=None):
+        cfg = LSETConfig()
+        over = {"model.path": str(dirs["qwen3"]), "data.train_path": str(files["triplet"]),
+                "data.max_seq_length": "32", "data.num_hard_negatives": "1",
+                "training.batch_size": "4", "training.lr": "1e-3", "training.scheduler": "constant",
+                "training.max_steps": str(max_steps), "training.temperature": "0.05",
+                "packing.enabled": packed, "checkpoint.output_dir": str(out),
+                "checkpoint.save_steps": "4", "logging.log_interval": "1"}
+        if resume:
+            over["checkpoint.resume_from"] = resume
+        cfg.apply_overrides(list(over.items()))
+        train(cfg)
+        text = capsys.readouterr().out
+        return {int(line.split()[0].split("=")[1]): float(line.split()[1].split("=")[1])
+                for line in text.splitlines() if line.startswith("step=")}
+
+    # 24 samples / batch 4 = 6 batches per epoch: steps 4..9 cross the epoch boundary
+    whole = run(root / f"whole_{packed}", 10)
+    assert sorted(whole) == list(range(10))
+    first = run(root / f"split_{packed}", 4)
+    rest = run(root / f"split_{packed}", 10, resume="auto")
+    assert sorted(rest) == list(range(4, 10))
+    for step in range(4):
+        assert first[step] == pytest.approx(whole[step], abs=1e-5)
+    for step in range(4, 10):
+        assert rest[step] == pytest.approx(whole[step], abs=1e-4), (step, rest, whole)
