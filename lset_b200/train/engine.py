@@ -397,6 +397,10 @@ class TrainingEngine:
                 if "rng" in extra:
                     torch.set_rng_state(extra["rng"])
                 skip = int(extra.get("batch_in_epoch", 0))
+                if self.task_store is not None and "task" in extra:
+                    self.task.load_state_dict(extra["task"])
+                    self.task_store.load_master(extra["task"])
+                    self.task_optimizer.load_state_dict(extra["task_optimizer"])
             self.micro_step = start
         step = start
         last_loss = None
@@ -460,6 +464,9 @@ class TrainingEngine:
         extra = {"scheduler": self.scheduler.state_dict(), "epoch": self.epoch,
                  "rng": torch.get_rng_state(), "micro_step": self.micro_step,
                  "batch_in_epoch": self._batch_in_epoch}
+        if self.task_store is not None:    # the learnable temperature lives outside the model
+            extra["task"] = {k: v.detach().cpu() for k, v in self.task.state_dict().items()}
+            extra["task_optimizer"] = self.task_optimizer.state_dict()
         return save_checkpoint(self.model, self.optimizer, step, self.output_dir, store=self.store,
                                extra=extra)
 

@@ -113,11 +113,12 @@ def test_train_runs(workspace, capsys, family, fmt, options):
     assert len(losses) >= 2 and all(math.isfinite(v) for v in losses), (losses, out[-500:])
 
 
-@pytest.mark.parametrize("packed", ["true", "false"])
-def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, packed):
+@pytest.mark.parametrize("packed,learnable", [("true", "false"), ("false", "false"), ("true", "true")])
+def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, packed, learnable):
     """An interrupted run that resumes from its checkpoint sees the batches the uninterrupted run
     would have seen (the order of an epoch depends on seed and epoch only; the checkpoint records
-    how far into the epoch it was) and therefore logs the same losses, also across an epoch end."""
+    how far into the epoch it was) and therefore logs the same losses, also across an epoch end.
+    With a learnable temperature its value and optimizer moments come back too."""
     root, dirs, files = workspace
 
     def run(out, max_steps, resume=None):
@@ -126,7 +127,8 @@ def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, pac
                 "data.max_seq_length": "32", "data.num_hard_negatives": "1",
                 "training.batch_size": "4", "training.lr": "1e-3", "training.scheduler": "constant",
                 "training.max_steps": str(max_steps), "training.temperature": "0.05",
-                "packing.enabled": packed, "checkpoint.output_dir": str(out),
+                "packing.enabled": packed, "training.learnable_temperature": learnable,
+                "checkpoint.output_dir": str(out),
                 "checkpoint.save_steps": "4", "logging.log_interval": "1"}
         if resume:
             over["checkpoint.resume_from"] = resume
@@ -137,10 +139,10 @@ def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, pac
                 for line in text.splitlines() if line.startswith("step=")}
 
     # 24 samples / batch 4 = 6 batches per epoch: steps 4..9 cross the epoch boundary
-    whole = run(root / f"whole_{packed}", 10)
+    whole = run(root / f"whole_{packed}_{learnable}", 10)
     assert sorted(whole) == list(range(10))
-    first = run(root / f"split_{packed}", 4)
-    rest = run(root / f"split_{packed}", 10, resume="auto")
+    first = run(root / f"split_{packed}_{learnable}", 4)
+    rest = run(root / f"split_{packed}_{learnable}", 10, resume="auto")
     assert sorted(rest) == list(range(4, 10))
     for step in range(4):
         assert first[step] == pytest.approx(whole[step], abs=1e-5)
