@@ -396,6 +396,8 @@ class TrainingEngine:
                 self.epoch = int(extra.get("epoch", 0))
                 if "rng" in extra:
                     torch.set_rng_state(extra["rng"])
+                if "cuda_rng" in extra and self.device.type == "cuda":
+                    torch.cuda.set_rng_state(extra["cuda_rng"].cpu(), self.device)
                 skip = int(extra.get("batch_in_epoch", 0))
                 if self.task_store is not None and "task" in extra:
                     self.task.load_state_dict(extra["task"])
@@ -464,6 +466,8 @@ class TrainingEngine:
         extra = {"scheduler": self.scheduler.state_dict(), "epoch": self.epoch,
                  "rng": torch.get_rng_state(), "micro_step": self.micro_step,
                  "batch_in_epoch": self._batch_in_epoch}
+        if self.device.type == "cuda":     # dropout masks on the GPU come from its own generator
+            extra["cuda_rng"] = torch.cuda.get_rng_state(self.device)
         if self.task_store is not None:    # the learnable temperature lives outside the model
             extra["task"] = {k: v.detach().cpu() for k, v in self.task.state_dict().items()}
             extra["task_optimizer"] = self.task_optimizer.state_dict()
