@@ -238,7 +238,7 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path, mode):
                   "--training.max_steps", "5", "--training.lr", "1e-3", "--packing.enabled", "true",
                   "--checkpoint.save_steps", "2", "--checkpoint.output_dir", str(out),
                   "--logging.log_interval", "1", "--distributed.dp_size", "2",
-                  "--distributed.max_restarts", "1", "--distributed.step_timeout_s", "8"])
+                  "--distributed.max_restarts", "1", "--distributed.step_timeout_s", "15"])
     finally:
         if env_backup is None:
             os.environ.pop("LSET_B200_FAIL_AT_STEP", None)
