@@ -126,6 +126,12 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str],
     world, rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
     if world == 1:
         return model
+    cfg = getattr(model, "config", None)
+    for field in ("num_attention_heads", "num_key_value_heads"):
+        heads = getattr(cfg, field, None)
+        if isinstance(heads, int) and heads % world:
+            raise ValueError(f"{field}={heads} cannot be split over {world} tensor-parallel ranks "
+                             f"(whole attention heads stay on one rank)")
     if sequence_parallel is None:
         sequence_parallel = any(v == "sequence" for v in plan.values())
     sp_state = None
