@@ -451,6 +451,9 @@ class TrainingEngine:
                     self.epoch += 1
                     self._batch_in_epoch = 0
                 if not made_progress:
+                    if step == start and self.rank == 0:
+                        print(f"[lset_b200] no full batch of {self.batch_size} samples per rank in "
+                              f"the dataset ({len(self.dataset)} samples): nothing to train on")
                     break
         finally:
             if self.watchdog is not None:
