@@ -80,6 +80,10 @@ def launcher_command(config, config_path: str, overrides) -> list:
 def cmd_train(args):
     cfg, path, overrides = _load(args, "train")
     cfg.validate()
+    for field, value in (("model.path", cfg.model.path), ("data.train_path", cfg.data.train_path)):
+        if not value:
+            print(f"Error: {field} is required for train (set it in the YAML file or with --{field})")
+            sys.exit(1)
     if cfg.distributed.dp_size * cfg.distributed.tp_size > 1:
         sys.exit(subprocess.run(launcher_command(cfg, path, overrides)).returncode)
     from .train.main import train
