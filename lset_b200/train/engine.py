@@ -102,7 +102,8 @@ class TrainingEngine:
                  lora: bool = False, lora_r: int = 8, lora_alpha: float = 16.0,
                  lora_dropout: float = 0.0, lora_targets=None, qlora: bool = False,
                  qlora_block_size: int = 64, fp8: bool = False, fp8_recipe: str = "rowwise",
-                 attn_backend: str = "auto", cuda_graph: bool = False, top_k: Optional[int] = None,
+                 attn_backend: str = "auto", cuda_graph: bool = False,
+                 cuda_graph_token_budget: Optional[int] = None, top_k: Optional[int] = None,
                  cascade: bool = False, cascade_d_small: int = 64, cascade_K_prime: int = 256,
                  activation_checkpoint: bool = False, ac_mode: str = "selective",
                  ac_ratio: float = 1.0, async_tp: bool = False,
@@ -117,7 +118,8 @@ class TrainingEngine:
         if cuda_graph:
             from .cuda_graph import validate_cuda_graph_config
 
-            validate_cuda_graph_config(packed, use_grad_cache, compile_model=False)
+            validate_cuda_graph_config(packed, use_grad_cache, compile_model=False,
+                                       token_budget=cuda_graph_token_budget)
         if fp8 and (lora or qlora):
             raise ValueError("FP8 training + LoRA/QLoRA is not supported")
         if qlora and tp_size > 1:

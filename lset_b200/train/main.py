@@ -35,7 +35,8 @@ def engine_kwargs(config: LSETConfig, max_steps: int) -> dict:
         lora_targets=config.lora.targets, qlora=config.qlora.enabled,
         qlora_block_size=config.qlora.block_size, fp8=config.fp8.enabled,
         fp8_recipe=config.fp8.recipe, attn_backend=config.attention.backend,
-        cuda_graph=config.cuda_graph.enabled, top_k=t.top_k, cascade=t.cascade,
+        cuda_graph=config.cuda_graph.enabled,
+        cuda_graph_token_budget=config.cuda_graph.token_budget, top_k=t.top_k, cascade=t.cascade,
         cascade_d_small=t.cascade_d_small, cascade_K_prime=t.cascade_K_prime,
         activation_checkpoint=config.activation_checkpoint.enabled,
         ac_mode=config.activation_checkpoint.mode, ac_ratio=config.activation_checkpoint.ratio,

@@ -86,6 +86,9 @@ CASES = [
     ("bert", "pair", {"packing.enabled": "true", "model.fused_projections": "true",
                       "data.length_sorted": "true"}),
     ("qwen3", "pair", {"packing.enabled": "true", "training.top_k": "2"}),
+    ("qwen3", "pair", {"packing.enabled": "true", "cuda_graph.enabled": "true",
+                       "cuda_graph.token_budget": "256", "attention.backend": "sdpa",
+                       "training.scheduler": "wsd", "training.warmup_steps": "1"}),
     ("qwen3", "triplet", {"packing.enabled": "true", "activation_checkpoint.enabled": "true",
                           "activation_checkpoint.mode": "full", "activation_checkpoint.ratio": "0.5"}),
 ]
