@@ -84,6 +84,13 @@ def _wrap_targets(model: nn.Module, targets: Iterable[str], r, alpha, dropout) -
         parent = model.get_submodule(fqn.rsplit(".", 1)[0]) if "." in fqn else model
         setattr(parent, fqn.rsplit(".", 1)[-1], LoRALinear(mod, r=r, alpha=alpha, dropout=dropout))
         n += 1
+    leaves = {fqn.rsplit(".", 1)[-1] for fqn, _ in model.named_modules()}
+    missing = sorted(t for t in wanted if t not in leaves)
+    if missing:
+        fused = sorted(leaves & {"qkv_proj", "gate_up_proj"})
+        hint = (f"; this model has fused projections {fused}: name them as targets or load it with "
+                f"model.fused_projections: false") if fused else ""
+        print(f"[lset_b200] LoRA targets without a matching layer: {missing}{hint}")
     return n
 
 
