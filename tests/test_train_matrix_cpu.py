@@ -151,3 +151,21 @@ def test_resume_continues_mid_epoch_with_the_same_batches(workspace, capsys, pac
         assert first[step] == pytest.approx(whole[step], abs=1e-5)
     for step in range(4, 10):
         assert rest[step] == pytest.approx(whole[step], abs=1e-4), (step, rest, whole)
+
+
+@pytest.mark.parametrize("family,pooling", [("qwen3", "last_token"), ("llama", "mean"),
+                                            ("gemma", "mean"), ("bert", "cls"), ("xlmr", "cls")])
+def test_eval_wrapper_loads_every_family(workspace, family, pooling):
+    """``LSETMTEBModel.from_pretrained`` picks the family's default pooling, encodes through the
+    packed forward, and a text gets the same embedding alone as inside a batch."""
+    import numpy as np
+
+    from lset_b200.eval.mteb_evaluator import LSETMTEBModel
+
+    _, dirs, _ = workspace
+    w = LSETMTEBModel.from_pretrained(str(dirs[family]), device="cpu")
+    assert w.pooling == pooling
+    texts = ["what is alpha 1", "beta gamma delta kernel tensor memory gradient batch index", "vector"]
+    emb = w.encode([texts])
+    assert emb.shape == (3, 32) and np.allclose(np.linalg.norm(emb, axis=1), 1.0, atol=1e-4)
+    assert np.allclose(w.encode([[texts[1]]])[0], emb[1], atol=1e-5)
