@@ -253,6 +253,18 @@ def test_elastic_restart_resumes_from_newest_checkpoint(tmp_path, mode):
     # first attempt: steps 0..2, checkpoint after step index 1; second attempt resumes at 2
     assert steps == [0, 1, 2, 2, 3, 4], steps
     assert os.path.exists(out / "step_4" / "meta.pt")
+    if mode == "raise":
+        # the recovered job logs the losses of a job that never failed
+        losses = [float(line.split()[1].split("=")[1]) for line in r.stdout.splitlines()
+                  if line.startswith("step=")]
+        os.environ.pop("LSET_B200_FAIL_AT_STEP", None)
+        clean = _run([a if a != str(out) else str(tmp_path / "clean") for a in r.args[1:]])
+        assert clean.returncode == 0, clean.stderr[-2000:]
+        ref = [float(line.split()[1].split("=")[1]) for line in clean.stdout.splitlines()
+               if line.startswith("step=")]
+        assert len(ref) == 5
+        assert losses[:3] == pytest.approx(ref[:3], abs=1e-4)
+        assert losses[3:] == pytest.approx(ref[2:], abs=1e-4), (losses, ref)
 
 
 def test_checkpoints_move_between_world_sizes(tmp_path):
