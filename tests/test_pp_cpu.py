@@ -10,13 +10,21 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from lset_b200.dist.pp import get_pp_split_points, get_stage_module_names, stage_layer_range
-from lset_b200.models import Qwen3Config, Qwen3Decoder
+from lset_b200.models import LlamaBidirectionalModel, LlamaConfig, Qwen3Config, Qwen3Decoder
 from lset_b200.models.layers import init_normal_
 
 
 def _cfg():
     return Qwen3Config(vocab_size=200, hidden_size=32, intermediate_size=64, num_hidden_layers=5,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+
+
+def _build(family):
+    if family == "llama":      # bidirectional attention, no per-head norms
+        return LlamaBidirectionalModel(LlamaConfig(
+            vocab_size=200, hidden_size=32, intermediate_size=64, num_hidden_layers=5,
+            num_attention_heads=4, num_key_value_heads=2, head_dim=8))
+    return Qwen3Decoder(_cfg())
 
 
 def _port():
@@ -49,14 +57,14 @@ def _loss(hiddens, mbs):
     return ce + hiddens[2].pow(2).mean()
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, family="qwen3"):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from lset_b200.dist.pp import PipelineRunner
 
     torch.manual_seed(0)
-    m = Qwen3Decoder(_cfg())
+    m = _build(family)
     init_normal_(m, 0.05)
     full = {k: v.clone() for k, v in m.state_dict().items()}
     runner = PipelineRunner(m, dist.group.WORLD)
@@ -78,12 +86,12 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("stages", [2, 3])
-def test_pipeline_matches_unsplit_model(stages):
+@pytest.mark.parametrize("stages,family", [(2, "qwen3"), (3, "qwen3"), (2, "llama")])
+def test_pipeline_matches_unsplit_model(stages, family):
     out_dir = tempfile.mkdtemp()
-    mp.spawn(_worker, args=(stages, _port(), out_dir), nprocs=stages, join=True)
+    mp.spawn(_worker, args=(stages, _port(), out_dir, family), nprocs=stages, join=True)
     got = [torch.load(os.path.join(out_dir, f"pp{r}.pt"), weights_only=False) for r in range(stages)]
-    ref = Qwen3Decoder(_cfg())
+    ref = _build(family)
     ref.load_state_dict(got[0]["full"])
     mbs = _microbatches()
     hiddens = [ref(**mb)["hidden_states"] for mb in mbs]
