@@ -156,3 +156,65 @@ def test_mesh_layout_tp_innermost_pp_outermost():
     assert [g["pp3"] for g in got] == [[0, 2], [1, 3], [0, 2], [1, 3]]
     assert [g["tp3"] for g in got] == [[0, 1], [0, 1], [2, 3], [2, 3]]
     assert [g["tp_sum"] for g in got] == [1.0, 1.0, 5.0, 5.0]
+
+
+def _train_worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lset_b200.dist.pp import PipelineRunner
+    from lset_b200.dist.sharded import ParamStore, ShardedAdamW
+
+    torch.manual_seed(0)
+    m = _build("qwen3")
+    init_normal_(m, 0.05)
+    runner = PipelineRunner(m, dist.group.WORLD)
+    solo = dist.new_group([rank]) if world > 1 else None
+    for r in range(world):                     # new_group is collective: every rank makes every group
+        if r != rank and world > 1:
+            dist.new_group([r])
+    store = ParamStore(m, dp_group=solo, compute_dtype=torch.float32, device=torch.device("cpu"))
+    opt = ShardedAdamW(store, lr=1e-2, weight_decay=0.0)
+    mbs, losses = _microbatches(), []
+    for _ in range(3):
+        hiddens = runner.encode(mbs)
+        if runner.last:
+            leaves = [h.detach().requires_grad_() for h in hiddens]
+            loss = _loss(leaves, mbs)
+            loss.backward()
+            runner.backward([t.grad for t in leaves])
+            losses.append(float(loss.detach()))
+        else:
+            runner.backward()
+        store.finish_backward()
+        opt.step()
+        opt.zero_grad()
+    if runner.last:
+        torch.save(losses, os.path.join(out_dir, "pp_losses.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipeline_stages_train_like_the_unsplit_model():
+    """Each stage owns the optimizer state of its layers: three AdamW steps through the pipeline
+    give the loss trajectory of the same optimizer on the unsplit model."""
+    from lset_b200.dist.sharded import ParamStore, ShardedAdamW
+
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_train_worker, args=(2, _port(), out_dir), nprocs=2, join=True)
+    got = torch.load(os.path.join(out_dir, "pp_losses.pt"), weights_only=False)
+    torch.manual_seed(0)
+    ref = _build("qwen3")
+    init_normal_(ref, 0.05)
+    store = ParamStore(ref, dp_group=None, compute_dtype=torch.float32, device=torch.device("cpu"))
+    opt = ShardedAdamW(store, lr=1e-2, weight_decay=0.0)
+    mbs, want = _microbatches(), []
+    for _ in range(3):
+        loss = _loss([ref(**mb)["hidden_states"] for mb in mbs], mbs)
+        loss.backward()
+        want.append(float(loss.detach()))
+        store.finish_backward()
+        opt.step()
+        opt.zero_grad()
+    assert want[2] < want[0]
+    assert got == pytest.approx(want, abs=1e-4), (got, want)
