@@ -169,10 +169,8 @@ def _train_worker(rank, world, port, out_dir):
     m = _build("qwen3")
     init_normal_(m, 0.05)
     runner = PipelineRunner(m, dist.group.WORLD)
-    solo = dist.new_group([rank]) if world > 1 else None
-    for r in range(world):                     # new_group is collective: every rank makes every group
-        if r != rank and world > 1:
-            dist.new_group([r])
+    # new_group is collective: every rank creates every group, in the same order
+    solo = [dist.new_group([r]) for r in range(world)][rank]
     store = ParamStore(m, dp_group=solo, compute_dtype=torch.float32, device=torch.device("cpu"))
     opt = ShardedAdamW(store, lr=1e-2, weight_decay=0.0)
     mbs, losses = _microbatches(), []
