@@ -13,8 +13,10 @@ in-batch negatives, AdamW, gradient clipping at 1.0. Weak scaling: the global ba
 Two timed regions of K steps each, after W warm-up steps, both bracketed by a barrier and a
 device synchronisation and timed with CUDA events (max over ranks):
   * device: batches already resident on the GPU  -> "value" / "ms_per_step"
-  * e2e:    ``TrainingEngine.train_step`` on pinned host batches (H2D copy of the step's inputs) plus
-            a device->host read of the step's loss every step -> "e2e"
+  * e2e:    ``TrainingEngine.train()``, the loop a user runs: DataLoader + collator on the host,
+            pinned-memory H2D copy of the step's inputs, the step, and a device->host read of the
+            step's global loss for the log line, every step -> "e2e"
+Keys that describe the measurement rather than the workload are under "diagnostics".
 Every step touches several GB of weights, optimizer state and activations, far more than the
 126 MB L2, so no explicit L2 flush is needed between steps (stated in "config").
 Rank 0 prints ONE JSON line.
@@ -46,27 +48,25 @@ MODEL_8B = dict(MODEL, hidden_size=4096, intermediate_size=12288, num_hidden_lay
                 num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=False)
 PRESETS = {
     "qwen3-0.6b": dict(
-        model=MODEL, pairs=64, tp=1, negs=0, lora_r=0,
+        model=MODEL, pairs=64, tp=1, negs=0, lora_r=0, q_len=(16, 64), d_len=(128, 512),
         metric="pairs/sec & tokens/sec, Qwen3-0.6B embed FSDP2 bf16, 1/2/4/8 B200, max over ranks",
         label="Qwen3-0.6B (28L, H1024, 16q/8kv heads, hd128, FFN3072, vocab 151936), random init"),
     "qwen3-4b-tp2": dict(
-        model=MODEL_4B, pairs=32, tp=2, negs=0, lora_r=0,
+        model=MODEL_4B, pairs=32, tp=2, negs=0, lora_r=0, q_len=(16, 64), d_len=(256, 1024),
         metric="pairs/sec & tokens/sec, Qwen3-4B embed TP2 x sharded DP bf16, max over ranks",
         label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
     "qwen3-4b": dict(
-        model=MODEL_4B, pairs=32, tp=1, negs=0, lora_r=0,
+        model=MODEL_4B, pairs=32, tp=1, negs=0, lora_r=0, q_len=(16, 64), d_len=(256, 1024),
         metric="pairs/sec & tokens/sec, Qwen3-4B embed sharded DP bf16, max over ranks",
         label="Qwen3-4B (36L, H2560, 32q/8kv heads, hd128, FFN9728, vocab 151936), random init"),
     "qwen3-8b-lora": dict(
-        model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16, ac=True,
+        model=MODEL_8B, pairs=16, tp=1, negs=3, lora_r=16, ac=True, q_len=(32, 32), d_len=(512, 512),
         metric="pairs/sec & tokens/sec, Qwen3-8B embed + LoRA r16, sharded DP bf16, 3 hard negatives, "
                "max over ranks",
         label="Qwen3-8B (36L, H4096, 32q/8kv heads, hd128, FFN12288, vocab 151936), random init, "
-              "frozen base + LoRA r16 on q/k/v/o"),
+              "frozen base + LoRA r16 alpha 32 on q/k/v/o/gate/up/down"),
 }
 PAIRS_PER_GPU = 64
-QUERY_LEN = (16, 64)
-DOC_LEN = (128, 512)
 TOKEN_ID_MAX = 151642
 TEMPERATURE = 0.02
 LR = 2e-5
@@ -136,7 +136,7 @@ class ClockSampler:
 # data
 # ----------------------------------------------------------------------------------------------
 def make_samples(n_batches: int, rank: int, seed: int = 1234, pairs: int = PAIRS_PER_GPU,
-                 negs: int = 0):
+                 negs: int = 0, q_len=(16, 64), d_len=(128, 512)):
     """Pre-tokenised samples: ``n_batches * pairs`` (query, positive[, negatives]) dicts for one
     data-parallel rank."""
     import torch
@@ -150,9 +150,9 @@ def make_samples(n_batches: int, rank: int, seed: int = 1234, pairs: int = PAIRS
 
     out = []
     for _ in range(n_batches * pairs):
-        item = {"query": seq(*QUERY_LEN), "positive": seq(*DOC_LEN)}
+        item = {"query": seq(*q_len), "positive": seq(*d_len)}
         if negs:
-            item["negatives"] = [seq(*DOC_LEN) for _ in range(negs)]
+            item["negatives"] = [seq(*d_len) for _ in range(negs)]
         out.append(item)
     return out
 
@@ -204,7 +204,11 @@ def barrier_sync(device):
     torch.cuda.synchronize(device)
 
 
-def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, launches, extra_cfg,
+def _len_text(r):
+    return str(r[0]) if r[0] == r[1] else f"U[{r[0]},{r[1]}]"
+
+
+def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, launches, diagnostics,
                 preset=None):
     preset = preset or PRESETS["qwen3-0.6b"]
     pairs_s = pairs / (ms / 1e3)
@@ -217,18 +221,19 @@ def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, lau
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (pairs_s / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
         "dtype": "bf16", "data": "synthetic", "impl": impl,
-        "config": dict({
+        "config": {
             "model": preset["label"],
             "global_batch": pairs, "pairs_per_dp_rank": preset["pairs"],
             "hard_negatives_per_pair": preset["negs"],
-            "seq_len": "query U[16,64], passage U[128,512], packed varlen stream (cu_seqlens)",
+            "seq_len": f"query {_len_text(preset['q_len'])}, passage {_len_text(preset['d_len'])}, "
+                       "packed varlen stream (cu_seqlens)",
             "parallelism": par + (" (sharded optimizer/grad, ZeRO)" if n_gpus // tp > 1 else ""),
             "loss": "InfoNCE T=0.02, global in-batch negatives", "optimizer": "AdamW lr 2e-5, clip 1.0",
             "l2": "per-step working set (weights+optimizer+activations, several GB) exceeds the "
                   "126 MB L2; no explicit flush",
             "timing": "CUDA events on the launching stream, max over ranks, barrier+sync both sides",
-        }, **extra_cfg),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        },
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "diagnostics": diagnostics,
     }
     return line
 
@@ -236,7 +241,53 @@ def result_line(impl, n_gpus, steps, warmup, ms, pairs, tokens, clocks, e2e, lau
 # ----------------------------------------------------------------------------------------------
 # this framework
 # ----------------------------------------------------------------------------------------------
+class TimedCollator:
+    """Wraps a collator and marks the timed region of a ``train()`` loop from its collate calls (the
+    DataLoader collates batch i right before step i): events are recorded at the calls ``first``
+    and ``first + steps``, each with a barrier and a device synchronisation outside the region."""
+
+    def __init__(self, inner, device=None, local_rank=0):
+        self.inner, self.device, self.local_rank = inner, device, local_rank
+        self.first = self.steps = None
+        self.calls = 0
+        self.h2d = 0
+        self.tokens = []
+        self.e0 = self.e1 = self.sampler = self.clocks = None
+
+    def arm(self, first: int, steps: int, device, sample_clocks: bool = True):
+        self.first, self.steps, self.device, self.calls = first, steps, device, 0
+        self.sample_clocks = sample_clocks
+
+    def __call__(self, batch):
+        import torch
+
+        i = self.calls
+        self.calls += 1
+        if self.first is not None and i == self.first:
+            barrier_sync(self.device)
+            if self.sample_clocks:
+                self.sampler = ClockSampler(self.local_rank)
+                self.sampler.start()
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        if self.first is not None and i == self.first + self.steps:
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e1.record()
+            barrier_sync(self.device)
+            if self.sampler is not None:
+                self.clocks = self.sampler.stop()
+        out = self.inner(batch)
+        if self.first is not None and self.first <= i < self.first + self.steps:
+            parts = [out[k] for k in ("query", "doc", "neg") if k in out]
+            self.tokens.append(sum(int(p["input_ids"].numel()) for p in parts))
+            self.h2d += sum(v.numel() * v.element_size() for p in parts for v in p.values()
+                            if torch.is_tensor(v))
+        return out
+
+
 def run_ours(args):
+    import contextlib
+
     import torch
 
     rank, local_rank, world = dist_env()
@@ -245,7 +296,7 @@ def run_ours(args):
     from lset_b200.models import Qwen3Config
     from lset_b200.ops import _native as nv
     from lset_b200.train.data.collator import PackedCollator
-    from lset_b200.train.engine import TrainingEngine, batch_bytes, pin, to_device
+    from lset_b200.train.engine import TrainingEngine, pin, to_device
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
@@ -266,21 +317,28 @@ def run_ours(args):
                 out["neg"] = self._batch([n for s in batch for n in s["negatives"]])
             return out
 
+    lens = dict(q_len=preset["q_len"], d_len=preset["d_len"])
+    # the end-to-end region runs the engine's own loop over this dataset (DataLoader, sampler,
+    # collator, pinned-memory copies); every rank holds the same list, the sampler splits it
+    e2e_steps = K + 2
+    e2e_data = ListDataset(make_samples(e2e_steps * dp, 10_000, pairs=P, negs=preset["negs"], **lens))
+    timed = TimedCollator(BenchCollator(), local_rank=local_rank)
+    ac_mode = preset.get("ac_mode", "full")
     engine = TrainingEngine(
-        "qwen3", None, dataset=None, dp_size=dp, tp_size=tp, batch_size=P, lr=LR,
-        max_steps=10**9, grad_clip=1.0, temperature=TEMPERATURE, packed=True, log_interval=0,
+        "qwen3", None, dataset=e2e_data, dp_size=dp, tp_size=tp, batch_size=P, lr=LR,
+        max_steps=10**9, grad_clip=1.0, temperature=TEMPERATURE, packed=True, log_interval=1,
         scheduler_type="constant", model_config=Qwen3Config(**preset["model"]),
-        fused_projections=preset["lora_r"] == 0, collator=BenchCollator(), async_tp=tp > 1,
+        fused_projections=preset["lora_r"] == 0, collator=timed, async_tp=tp > 1,
         lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]), lora_alpha=32.0,
         init_on_device=args.config != "qwen3-0.6b",
         fp8=args.fp8 is not None, fp8_recipe=args.fp8 or "rowwise",
-        # the 8B model keeps ~3 GB of activations per layer at this batch: recompute the cheap ops
-        activation_checkpoint=bool(preset.get("ac", False)))
+        # the 8B model at this batch keeps several GB of activations per layer: recompute them
+        activation_checkpoint=bool(preset.get("ac", False)), ac_mode=ac_mode)
     device = engine.device
-    n_batches = W + 2 * K
+    n_batches = W + K
     # ranks of one tensor-parallel group see the same batch
     samples = make_samples(n_batches, engine.dp_rank if tp > 1 else rank, pairs=P,
-                           negs=preset["negs"])
+                           negs=preset["negs"], **lens)
     coll = BenchCollator()
     host = [pin(coll(samples[i * P:(i + 1) * P])) for i in range(n_batches)]
     tokens = [sum(int(b[k]["input_ids"].numel()) for k in ("query", "doc", "neg") if k in b)
@@ -302,40 +360,43 @@ def run_ours(args):
     nv.reset_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    t_host = time.perf_counter()
+    t_host, wait0 = time.perf_counter(), engine.host_wait_s
     for i in range(K):
         engine.forward_backward(staged[i], True)
         engine.optimizer_step()
         engine.micro_step += 1
-    host_ms = (time.perf_counter() - t_host) * 1e3 / K   # time the host needs to enqueue a step
+    # host time to enqueue a step, without the time it spent blocked on the run-ahead limit
+    # (waiting for the GPU to finish the step before the previous one)
+    wait_ms = (engine.host_wait_s - wait0) * 1e3 / K
+    host_ms = (time.perf_counter() - t_host) * 1e3 / K - wait_ms
     e1.record()
     barrier_sync(device)
+    clocks = sampler.stop()
     ms_dev = max_over_ranks(e0.elapsed_time(e1) / K, device)
     launches = nv.launches()
     tok_dev = sum_over_ranks(float(sum(tokens[W:W + K])) / K, device) / tp
     del staged
 
-    # ---- end-to-end region: pinned host batch -> H2D -> step -> loss read back, every step
-    barrier_sync(device)
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    last = 0.0
-    for i in range(K):
-        last = engine.train_step(host[W + K + i]).item()
-    e3.record()
-    barrier_sync(device)
-    clocks = sampler.stop()
-    ms_e2e = max_over_ranks(e2.elapsed_time(e3) / K, device)
+    # ---- end-to-end region: the engine's own train() loop. Every step: DataLoader + collate on
+    # the host, pinned batch -> H2D, forward/backward/optimizer, loss read back for the log line.
+    engine.max_steps = e2e_steps           # step 0 starts the loader; steps 1..K are timed
+    engine.needs_dist_cleanup = False      # the process group is still needed for the reductions
+    timed.arm(1, K, device, sample_clocks=False)
+    with contextlib.redirect_stdout(sys.stderr):   # the loop's own log lines
+        last = engine.train()
+    ms_e2e = max_over_ranks(timed.e0.elapsed_time(timed.e1) / K, device)
     nv.check_status(device)
-    h2d = sum(batch_bytes(b) for b in host[W + K:W + 2 * K]) / K
     pairs = P * dp
     e2e = {"value": pairs / (ms_e2e / 1e3), "unit": "pairs/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "last_loss": last,
-           "api": "lset_b200.train.engine.TrainingEngine.train_step(pinned host batch) + loss.item()"}
+           "h2d_bytes_per_step": int(timed.h2d / K), "d2h_bytes_per_step": 4, "last_loss": last,
+           "api": "lset_b200.train.engine.TrainingEngine.train() (DataLoader + collator + pinned "
+                  "H2D + step + global loss read back and logged every step)"}
     if rank == 0:
         line = result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e, launches,
                            {"host_enqueue_ms_per_step": round(host_ms, 2),
+                            "host_blocked_on_gpu_ms_per_step": round(wait_ms, 2),
                             "fused_projections": preset["lora_r"] == 0,
+                            "activation_checkpoint": ac_mode if preset.get("ac") else "off",
                             "native_library": str(nv.lib_path().name)}, preset)
         if args.fp8 is not None:
             # a side measurement, not the headline: linear layers on the 8-bit tensor-core GEMM
@@ -354,11 +415,6 @@ def run_ours(args):
 # ----------------------------------------------------------------------------------------------
 def run_reference(args):
     preset = PRESETS[args.config]
-    if preset["lora_r"] or preset["negs"]:
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference arm is wired for the dense configs without hard negatives "
-                          "(qwen3-0.6b, qwen3-4b, qwen3-4b-tp2)"}))
-        return
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "lset")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lset is not installed"}))
@@ -397,15 +453,19 @@ def run_reference(args):
 
         spec = get_model_spec("qwen3")
         torch.manual_seed(0)
-        m = spec.model_cls(spec.config_cls.from_hf_json(os.path.join(model_dir, "config.json")))
+        # built and filled on the GPU (host-side N(0, 0.02) of a multi-billion-parameter model takes
+        # minutes), then written as the bf16 checkpoint the reference engine loads
+        with torch.device(device):
+            m = spec.model_cls(spec.config_cls.from_hf_json(os.path.join(model_dir, "config.json")))
         sd = {}
         for k, v in m.state_dict().items():
-            t = v.detach().clone()
+            t = v.detach()
             if t.dim() >= 2:
                 t.normal_(0.0, 0.02)
-            sd["model." + k] = t.to(torch.bfloat16).contiguous()
+            sd["model." + k] = t.to(torch.bfloat16).cpu().contiguous()
         save_file(sd, os.path.join(model_dir, "model.safetensors"))
         del m, sd
+        torch.cuda.empty_cache()
         open(marker, "w").close()
     t_wait = time.time()
     while not os.path.exists(marker):
@@ -419,10 +479,21 @@ def run_reference(args):
     dp = max(1, world // tp)
     # with dp > 1 the reference's DistributedSampler gives each rank 1/dp of its dataset; the ranks
     # of one tensor-parallel group must see the same samples
-    samples = make_samples(n_batches * dp, rank // tp if tp > 1 else rank, pairs=P)
+    samples = make_samples(n_batches * dp, rank // tp if tp > 1 else rank, pairs=P,
+                           negs=preset["negs"], q_len=preset["q_len"], d_len=preset["d_len"])
     tokens = []
     state = {"i": 0, "e0": None, "e1": None}
-    inner = RefPacked()
+    if preset["negs"]:
+        # the reference's packed collator takes one "negative" per sample; several hard negatives
+        # per query are flattened into its "neg" batch with the reference's own packing routine
+        from lset.train.data.packing import pack_sequences as ref_pack
+
+        def inner(batch):
+            return {"query": ref_pack([s["query"]["input_ids"] for s in batch]),
+                    "doc": ref_pack([s["positive"]["input_ids"] for s in batch]),
+                    "neg": ref_pack([n["input_ids"] for s in batch for n in s["negatives"]])}
+    else:
+        inner = RefPacked()
 
     def timing_collator(batch):
         # called by the engine's DataLoader right before each step (num_workers = 0)
@@ -444,9 +515,10 @@ def run_reference(args):
             state["clocks"] = state["sampler"].stop()
         out = inner(batch)
         if W <= i < W + K:
-            tokens.append(int(out["query"]["input_ids"].numel() + out["doc"]["input_ids"].numel()))
+            parts = [out[k] for k in ("query", "doc", "neg") if k in out]
+            tokens.append(sum(int(p["input_ids"].numel()) for p in parts))
             state["h2d"] = state.get("h2d", 0) + sum(
-                v.numel() * v.element_size() for part in (out["query"], out["doc"])
+                v.numel() * v.element_size() for part in parts
                 for v in part.values() if torch.is_tensor(v))
         state["i"] = i + 1
         return out
@@ -459,7 +531,9 @@ def run_reference(args):
             model_name="qwen3", model_path=model_dir, dataset=SeqDataset(samples), dp_size=dp,
             tp_size=tp, batch_size=P, lr=LR, max_steps=n_batches, grad_clip=1.0,
             temperature=TEMPERATURE, log_interval=10**9, packed=True, scheduler_type="constant",
-            collator=timing_collator)
+            collator=timing_collator, lora=preset["lora_r"] > 0, lora_r=max(1, preset["lora_r"]),
+            lora_alpha=32.0, activation_checkpoint=bool(preset.get("ac", False)),
+            ac_mode=preset.get("ac_mode", "full"))
         # keep the batches in order (the stock DataLoader shuffles; order does not change the work)
         engine.train()
     except Exception as exc:  # pragma: no cover - depends on the box
@@ -481,7 +555,9 @@ def run_reference(args):
     if rank == 0:
         line = result_line("reference", world, K, W, ms_all, pairs, tok_all, state.get("clocks"), e2e,
                            None, {"note": "timed region = steps W..W+K-1 of the reference's own "
-                                          "train() loop, marked from its DataLoader collate calls"},
+                                          "train() loop, marked from its DataLoader collate calls",
+                                  "activation_checkpoint":
+                                      preset.get("ac_mode", "full") if preset.get("ac") else "off"},
                            preset)
         line.pop("gpu_launches")
         print(json.dumps(line))

@@ -20,6 +20,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
+from ..ops import block as block_ops
 from ..ops import gemm as gemm_ops
 from ..ops import norm as norm_ops
 from .configs import GemmaConfig, LlamaConfig, Qwen3Config
@@ -64,6 +65,8 @@ class DecoderBlock(nn.Module):
     def forward(self, branch, residual, ctx: StreamCtx, prev_post_norm: Optional[RMSNorm] = None):
         """``branch`` is the previous block's un-added output (or the embeddings for block 0).
         Returns ``(branch_out, residual)`` with the final add left to the next norm."""
+        if prev_post_norm is None and block_ops.usable(self, branch, ctx):
+            return block_ops.run(self, branch, residual, ctx)   # the whole block in one native call
         n_in, n_post = self.input_layernorm, self.post_attention_layernorm
         if residual is None:
             x, residual = n_in(branch), branch

@@ -21,6 +21,7 @@ class RuntimeOptions:
     fused_rmsnorm: bool = True
     fused_qk_norm_rope: bool = True
     fused_double_rmsnorm: bool = True
+    block_runner: bool = True       # whole decoder blocks issued by the native block runner
     fused_glu_gemm: bool = False    # gated-MLP activation in the epilogue of the gate/up GEMM (measured slower: off)
     attention_backend: str = "auto"  # auto | native | sdpa
 
@@ -33,6 +34,7 @@ _ENV = {
     "fused_qk_norm_rope": "LSET_DISABLE_FUSED_QK_NORM_ROPE",
     "fused_double_rmsnorm": "LSET_DISABLE_FUSED_DOUBLE_RMSNORM",
     "fused_glu_gemm": "LSET_DISABLE_FUSED_GLU_GEMM",
+    "block_runner": "LSET_DISABLE_BLOCK_RUNNER",
 }
 
 options = RuntimeOptions()

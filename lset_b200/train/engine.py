@@ -275,6 +275,7 @@ class TrainingEngine:
         self.micro_step = 0
         self.max_inflight_steps = max_inflight_steps
         self._inflight = []
+        self.host_wait_s = 0.0
         self.epoch = 0
         # per-phase device timing (h2d / forward_backward / optimizer); LSET_B200_PROFILE=1 enables it
         self.timer = PhaseTimer(enabled=os.environ.get("LSET_B200_PROFILE", "0") == "1")
@@ -363,8 +364,10 @@ class TrainingEngine:
         ev = torch.cuda.Event()
         ev.record()
         self._inflight.append(ev)
+        t0 = time.perf_counter()
         while len(self._inflight) > self.max_inflight_steps:
             self._inflight.pop(0).synchronize()
+        self.host_wait_s += time.perf_counter() - t0   # host time spent waiting for the GPU
 
     def train_step(self, batch: dict):
         """One micro-step from a host batch: H2D copy, forward/backward and, on the accumulation
