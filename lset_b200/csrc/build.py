@@ -8,6 +8,8 @@ Usage:  python -m lset_b200.csrc.build [--force] [--verbose]
 from __future__ import annotations
 
 import concurrent.futures as cf
+import contextlib
+import hashlib
 import os
 import shutil
 import subprocess
@@ -18,6 +20,8 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 OBJ_DIR = CSRC / "_build"
 LIB_PATH = PKG / "_C.so"
+MANIFEST_PATH = PKG / "_C.so.manifest"   # digest of the sources the library was built from
+LOCK_PATH = PKG / "_C.so.lock"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,6 +47,50 @@ def _headers_mtime() -> float:
     return max(hs) if hs else 0.0
 
 
+def source_digest() -> str:
+    """SHA-256 over every source and header (path and content) and the compiler flags: the
+    library is current iff the digest stored next to it equals this one. File times are not used,
+    they do not survive a copy of the tree to another machine."""
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    files = sorted(p for p in CSRC.rglob("*") if p.suffix in (".cu", ".cuh", ".h")
+                   and "_build" not in p.parts)
+    for f in files:
+        h.update(str(f.relative_to(CSRC)).encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    try:
+        return LIB_PATH.exists() and MANIFEST_PATH.read_text().strip() == source_digest()
+    except OSError:
+        return False
+
+
+@contextlib.contextmanager
+def build_lock():
+    """Exclusive lock for builders on one machine (the ranks of a job start together)."""
+    import fcntl
+
+    with open(LOCK_PATH, "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
+def ensure_built(verbose: bool = False) -> Path:
+    """Build the library unless the one in the tree was made from the present sources. Safe to
+    call from several processes at once: one builds, the others wait and find it current."""
+    if is_current():
+        return LIB_PATH
+    with build_lock():
+        if not is_current():
+            build(verbose=verbose)
+    return LIB_PATH
+
+
 def _compile_one(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, str]:
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if ptxas_v:
@@ -62,7 +110,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
         rel = src.relative_to(CSRC)
         obj = OBJ_DIR / ("_".join(rel.with_suffix("").parts) + ".o")
         objs.append(obj)
-        if force or ptxas_v or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m):
+        stale = not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
+        if force or ptxas_v or stale or not MANIFEST_PATH.exists():
             todo.append((src, obj))
     if todo:
         workers = max(1, min(len(todo), os.cpu_count() or 4))
@@ -73,12 +122,18 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
     need_link = bool(todo) or not LIB_PATH.exists() or any(
         o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs
     )
-    if need_link:
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
+    digest = source_digest()
+    if need_link or not MANIFEST_PATH.exists() or MANIFEST_PATH.read_text().strip() != digest:
+        # link under a temporary name and move it into place: a process that loads the library
+        # meanwhile sees either the old file or the complete new one
+        tmp = LIB_PATH.with_name(f"_C.so.tmp{os.getpid()}")
+        cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(tmp, LIB_PATH)
+        MANIFEST_PATH.write_text(digest + "\n")
     return LIB_PATH
 
 

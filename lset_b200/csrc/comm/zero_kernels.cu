@@ -11,9 +11,13 @@
 //                  stored into EVERY rank's parameter buffer = optimizer step fused with the
 //                  parameter all-gather (a push: each byte crosses NVLink once per peer).
 //
-// Neither kernel waits on another GPU: ordering between ranks (gradients complete before they are
-// read, pushes complete before the next forward) is established on the host side by stream-ordered
-// collectives, so there is no device-side spin here at all.
+// Neither kernel waits on another GPU itself. Ordering between ranks (gradients complete before
+// they are read, pushes complete before the next forward) comes from a launch placed in front of
+// them on the same stream: by default the device barrier of comm/probe.cu, a kernel that spins,
+// with an iteration limit, on flags in symmetric memory and reports a peer that never arrives
+// through the status word; with LSET_B200_DEVICE_BARRIER=0 a one-element NCCL all-reduce instead.
+// The AdamW kernel honours the skip flag that the clip-coefficient kernel derives from the status
+// words of all ranks, so a step whose barrier timed out changes no parameter.
 //
 // Replaces, for the sharded runtime, the NCCL reduce-scatter / all-gather that FSDP2 issues for the
 // reference (lset/distributed/parallel.py:129-160) plus clip_grad_norm_ and AdamW(fused=True)
@@ -91,6 +95,7 @@ struct AdamPushArgs {
 };
 
 __global__ void __launch_bounds__(256) adamw_push_kernel(AdamPushArgs a) {
+  if (a.coef != nullptr && a.coef[2] != 0.f) return;   // the step was marked faulted: apply nothing
   const float gs = a.coef != nullptr ? a.coef[0] : 1.f;
   const float step = a.lr / a.bc1;
   const float decay = 1.f - a.lr * a.wd;

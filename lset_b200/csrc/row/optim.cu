@@ -38,11 +38,16 @@ __global__ void __launch_bounds__(256)
 }
 
 // coef_out[0] = min(1, max_norm / (norm + 1e-6)); coef_out[1] = norm. max_norm <= 0 disables.
+// coef_out[2] = 1 when this step must not be applied: `fault` (nullable device float, e.g. the
+// status words of all ranks summed) is non-zero, i.e. some kernel of the step gave up a bounded
+// wait and the gradients cannot be trusted. The AdamW kernels return at once when they see it,
+// so a faulted step leaves parameters and moments untouched without the host having to look.
 __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm,
-                                 float* __restrict__ coef_out) {
+                                 float* __restrict__ coef_out, const float* __restrict__ fault) {
   const float norm = sqrtf(sumsq[0]);
   coef_out[1] = norm;
   coef_out[0] = (max_norm > 0.f) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  coef_out[2] = (fault != nullptr && fault[0] != 0.f) ? 1.f : 0.f;
 }
 
 struct AdamArgs {
@@ -53,11 +58,12 @@ struct AdamArgs {
   bf16* p_bf16;      // nullable: bf16 compute copy written after the update
   long long n;
   float lr, beta1, beta2, eps, wd, bc1, bc2_sqrt, grad_scale;
-  const float* coef;  // nullable device scalar multiplied into the gradient (clip)
+  const float* coef;  // nullable: [0] clip coefficient, [2] non-zero = skip this step
   int zero_grad;
 };
 
 __global__ void __launch_bounds__(256) adamw_kernel(AdamArgs a) {
+  if (a.coef != nullptr && a.coef[2] != 0.f) return;
   const float gs = a.grad_scale * (a.coef != nullptr ? a.coef[0] : 1.f);
   const float step = a.lr / a.bc1;
   const float decay = 1.f - a.lr * a.wd;
@@ -129,8 +135,11 @@ extern "C" int lb_sumsq_f32(const float* x, long long n, float* scratch, float* 
   return launch_rc();
 }
 
-extern "C" int lb_clip_coef(const float* sumsq, float max_norm, float* coef_out, void* stream) {
-  clip_coef_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, coef_out);
+// coef_out: 3 floats (see clip_coef_kernel); fault: nullable device float.
+extern "C" int lb_clip_coef(const float* sumsq, float max_norm, float* coef_out, const float* fault,
+                            void* stream) {
+  clip_coef_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, coef_out,
+                                                                        fault);
   return launch_rc();
 }
 

@@ -280,6 +280,7 @@ class ParamStore:
             # orders "all pushes done" before the next forward on every rank.
             self._barrier("gather").sync()
             return
+        hooked = {id(g) for _, gs in self._groups_of_layer for g in gs}
         for g in self.groups:
             if self.comm_stream is not None:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -291,6 +292,12 @@ class ParamStore:
             else:
                 dist.all_gather_into_tensor(g.flat_param, g.flat_param[g.lo:g.hi].clone(),
                                             group=self.dp_group)
+        # Groups that belong to a layer are waited for by that layer's forward hook. The others
+        # (embeddings, final norm, a task's own parameters) have no hook and are read first by the
+        # next forward: the compute stream waits for them here.
+        for g in self.groups:
+            if id(g) not in hooked:
+                self._wait_gather(g)
 
     def _wait_gather(self, g: FlatGroup) -> None:
         if g.gather_event is not None:
@@ -311,6 +318,20 @@ class ParamStore:
     def trainable_parameters(self):
         for g in self.groups:
             yield from g.params
+
+    def canonical_index(self) -> dict:
+        """``id(param) -> position`` among the module's trainable parameters in module order: the
+        numbering of ``torch.optim`` state dicts, independent of how this store grouped them."""
+        hit = self.__dict__.get("_canon")
+        if hit is None:
+            owned = {id(p) for p in self.trainable_parameters()}
+            hit, n = {}, 0
+            for p in self.module.parameters():
+                if id(p) in owned and id(p) not in hit:
+                    hit[id(p)] = n
+                    n += 1
+            self._canon = hit
+        return hit
 
     def named_master_tensors(self):
         """``(name, fp32 tensor)`` for every trainable parameter, gathered across ranks (a
@@ -365,9 +386,11 @@ class ShardedAdamW:
         self.grad_clip = grad_clip
         self.step_count = 0
         dev = store.device
-        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        # [squared global gradient norm, fault flag (sum of the ranks' status words)]
+        self._sumsq = torch.zeros(2, dtype=torch.float32, device=dev)
         self._parts = torch.zeros(2, dtype=torch.float32, device=dev)
-        self._coef = torch.ones(2, dtype=torch.float32, device=dev)  # [clip coefficient, norm]
+        # [clip coefficient, norm, skip flag]
+        self._coef = torch.tensor([1.0, 0.0, 0.0], dtype=torch.float32, device=dev)
         self.state = {}  # torch.optim.Optimizer API expected by LR schedulers
 
     # -- torch.optim-like surface ------------------------------------------------------------
@@ -407,9 +430,16 @@ class ShardedAdamW:
                 else:
                     gs = g.grad_shard.reshape(-1).float()
                     parts[slot] += torch.dot(gs, gs)       # one pass, no temporary
-        if st.tp_group is not None and dist.get_world_size(st.tp_group) > 1:
+        tp_on = st.tp_group is not None and dist.get_world_size(st.tp_group) > 1
+        if tp_on:
             dist.all_reduce(parts[1:2], op=dist.ReduceOp.SUM, group=st.tp_group)
-        torch.sum(parts, dim=0, keepdim=True, out=self._sumsq)
+        torch.sum(parts, dim=0, keepdim=True, out=self._sumsq[0:1])
+        if native:
+            # the status word of the bounded waits rides along: non-zero on any rank marks the
+            # step as faulted on every rank (same reduction as the norm, no extra collective)
+            self._sumsq[1:2].copy_(nv.status_word(st.device))
+            if tp_on:
+                dist.all_reduce(self._sumsq[1:2], op=dist.ReduceOp.SUM, group=st.tp_group)
         if st.world > 1:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=st.dp_group)
 
@@ -426,11 +456,13 @@ class ShardedAdamW:
         native = st.device.type == "cuda"
         if native:
             rc = nv.load().lb_clip_coef(nv.c_void_p(self._sumsq.data_ptr()), nv.c_float(self.grad_clip),
-                                        nv.c_void_p(self._coef.data_ptr()), nv.c_void_p(nv.stream_ptr()))
+                                        nv.c_void_p(self._coef.data_ptr()),
+                                        nv.c_void_p(self._sumsq.data_ptr() + 4),
+                                        nv.c_void_p(nv.stream_ptr()))
             nv.check_rc(rc, "lb_clip_coef")
             nv.count_launch()
         else:
-            norm = self._sumsq.sqrt()
+            norm = self._sumsq[0:1].sqrt()
             self._coef[1] = norm[0]
             self._coef[0] = torch.clamp(self.grad_clip / (norm[0] + 1e-6), max=1.0) \
                 if self.grad_clip > 0 else 1.0
@@ -484,34 +516,35 @@ class ShardedAdamW:
         """torch AdamW layout: per-parameter ``step / exp_avg / exp_avg_sq`` (full tensors; a
         collective when world > 1) plus ``param_groups`` with integer parameter ids."""
         st = self.store
-        state, idx = {}, 0
+        canon = st.canonical_index()
+        state = {}
         step_t = torch.tensor(float(self.step_count))
         for g in st.groups:
             m = st._gather_fp32(g, g.exp_avg)
             v = st._gather_fp32(g, g.exp_avg_sq)
             for p, o in zip(g.params, g.offsets):
-                state[idx] = {"step": step_t.clone(),
-                              "exp_avg": m[o:o + p.numel()].view(p.shape).clone(),
-                              "exp_avg_sq": v[o:o + p.numel()].view(p.shape).clone()}
-                idx += 1
+                state[canon[id(p)]] = {"step": step_t.clone(),
+                                       "exp_avg": m[o:o + p.numel()].view(p.shape).clone(),
+                                       "exp_avg_sq": v[o:o + p.numel()].view(p.shape).clone()}
+        state = dict(sorted(state.items()))
         pg = {k: v for k, v in self.param_groups[0].items() if k != "params"}
         pg.update(amsgrad=False, maximize=False, foreach=None, capturable=False,
-                  differentiable=False, fused=True, params=list(range(idx)))
+                  differentiable=False, fused=True, params=list(range(len(state))))
         return {"state": state, "param_groups": [pg]}
 
     def load_state_dict(self, sd: dict) -> None:
         st = self.store
-        idx = 0
+        canon = st.canonical_index()
         for g in st.groups:
             m = torch.zeros(g.numel, dtype=torch.float32, device=st.device)
             v = torch.zeros(g.numel, dtype=torch.float32, device=st.device)
             for p, o in zip(g.params, g.offsets):
+                idx = canon[id(p)]
                 ent = sd["state"].get(idx, sd["state"].get(str(idx)))
                 if ent is not None:
                     m[o:o + p.numel()] = ent["exp_avg"].reshape(-1).to(st.device, torch.float32)
                     v[o:o + p.numel()] = ent["exp_avg_sq"].reshape(-1).to(st.device, torch.float32)
                     self.step_count = int(float(ent["step"]))
-                idx += 1
             g.exp_avg.copy_(m[g.lo:g.hi])
             g.exp_avg_sq.copy_(v[g.lo:g.hi])
         if sd.get("param_groups"):

@@ -160,15 +160,18 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str],
             target_name = parent_name if leaf in ("base_linear", "lora_B") else name
             sections = _section_sizes(target_name, module, owner)
             module.weight.data = _shard_rows(w, sections, rank, world)
+            module.weight._tp_meta = ("rows", sections or [w.shape[0]])
             if module.bias is not None:
                 module.bias.data = _shard_rows(module.bias.data, sections, rank, world)
                 module.bias._tp_sharded = True
+                module.bias._tp_meta = ("rows", sections or [w.shape[0]])
             module.out_features = module.weight.shape[0]
         else:
             if w.shape[1] % world:
                 raise ValueError(f"{name}: {w.shape[1]} input features not divisible by tp={world}")
             per = w.shape[1] // world
             module.weight.data = w[:, rank * per:(rank + 1) * per].contiguous()
+            module.weight._tp_meta = ("cols", [w.shape[1]])
             module.in_features = per
         module.weight._tp_sharded = True
         # lora_A of a colwise target / lora_B of a rowwise target stay replicated and un-hooked;
@@ -194,6 +197,34 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str],
     model._sp = sp_state
     model._tp_group = tp_group
     return model
+
+
+def unshard(local: torch.Tensor, meta, group) -> torch.Tensor:
+    """Full tensor from this rank's shard (a collective over ``group``). ``meta`` is the
+    ``_tp_meta`` tag ``apply_tp`` leaves on a sharded parameter: ``("rows", sections)`` for
+    column-parallel layers (each section of output features was split separately, so that a fused
+    q/k/v or gate/up weight keeps whole heads per rank) or ``("cols", [in_features])``."""
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    kind, sections = meta
+    if kind == "cols":
+        return torch.cat(parts, dim=1)
+    out, start = [], 0
+    for n in sections:
+        per = n // world
+        out.extend(p[start:start + per] for p in parts)
+        start += per
+    return torch.cat(out, dim=0)
+
+
+def reshard(full: torch.Tensor, meta, rank: int, world: int) -> torch.Tensor:
+    """Inverse of ``unshard``: this rank's shard of a full tensor."""
+    kind, sections = meta
+    if kind == "cols":
+        per = full.shape[1] // world
+        return full[:, rank * per:(rank + 1) * per].contiguous()
+    return _shard_rows(full, sections, rank, world)
 
 
 def tp_sharded(p: nn.Parameter) -> bool:

@@ -81,7 +81,7 @@ def encode_chunked(model, tokenize_fn, pool_fn, texts: Sequence[str], *, device,
                    overlap: int = DEFAULT_OVERLAP, token_budget: int = DEFAULT_TOKEN_BUDGET,
                    max_pos: Optional[int] = None, out_path: Optional[str] = None,
                    dim: Optional[int] = None, tokenize_cache_dir: Optional[str] = None,
-                   oom_retry_halving: bool = True) -> np.ndarray:
+                   oom_retry_halving: bool = True, post_pooling=None) -> np.ndarray:
     if pooling not in ("mean", "last_token", "cls"):
         raise ValueError(f"unknown pooling {pooling!r}")
     encoded = cached_tokenize(tokenize_fn, texts, Path(tokenize_cache_dir) if tokenize_cache_dir else None)
@@ -133,6 +133,10 @@ def encode_chunked(model, tokenize_fn, pool_fn, texts: Sequence[str], *, device,
         acc.index_add_(0, owners_t[sel], emb * w[:, None])
         weight.index_add_(0, owners_t[sel], w)
     out = acc / weight.clamp(min=1.0)[:, None]
+    if post_pooling is not None:   # dense projection between pooling and normalisation
+        with torch.no_grad():
+            w_dtype = next(iter(post_pooling.buffers())).dtype
+            out = post_pooling(out.to(w_dtype)).float()
     if normalize:
         out = torch.nn.functional.normalize(out, dim=-1, eps=1e-12)
     result = out.cpu().numpy().astype(np.float32)

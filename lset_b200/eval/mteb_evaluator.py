@@ -27,7 +27,7 @@ class LSETMTEBModel:
                  device=None, query_prefix: str = "", document_prefix: str = "",
                  model_name: str = "lset-b200/model", revision: str = "local",
                  token_budget: int = DEFAULT_TOKEN_BUDGET, chunked: bool = True,
-                 chunk_len: int = DEFAULT_CHUNK_LEN):
+                 chunk_len: int = DEFAULT_CHUNK_LEN, post_pooling=None):
         self.model = model.eval()
         self.tokenizer = tokenizer
         self.pooling = pooling
@@ -36,6 +36,7 @@ class LSETMTEBModel:
         self.query_prefix, self.document_prefix = query_prefix, document_prefix
         self.model_name, self.revision = model_name, revision
         self.token_budget, self.chunked, self.chunk_len = token_budget, chunked, chunk_len
+        self.post_pooling = post_pooling
 
     @classmethod
     def from_pretrained(cls, model_path: str, pooling: str = "auto", max_length: int = 512,
@@ -51,8 +52,11 @@ class LSETMTEBModel:
         dtype = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         model = model.to(device=dev, dtype=dtype)
         pool = spec.default_pooling if pooling in (None, "auto") else pooling
+        proj = spec.post_pooling_fn(model_path) if spec.post_pooling_fn is not None else None
+        if proj is not None:
+            proj = proj.to(device=dev, dtype=dtype)
         return cls(model, load_tokenizer(model_path), pool, max_length, dev,
-                   model_name=f"lset-b200/{Path(model_path).name}", **kw)
+                   model_name=f"lset-b200/{Path(model_path).name}", post_pooling=proj, **kw)
 
     # ------------------------------------------------------------------ encoding
     def _tokenize_many(self, texts: List[str]) -> List[List[int]]:
@@ -68,7 +72,8 @@ class LSETMTEBModel:
         chunk_len = self.chunk_len if (self.chunked and self.pooling == "mean") else 10**9
         return encode_chunked(self.model, self._tokenize_many, None, texts, device=self.device,
                               pad_id=self._pad_id(), pooling=self.pooling, normalize=True,
-                              chunk_len=chunk_len, token_budget=self.token_budget)
+                              chunk_len=chunk_len, token_budget=self.token_budget,
+                              post_pooling=self.post_pooling)
 
     def encode(self, inputs: Iterable, *, task_metadata=None, hf_split=None, hf_subset=None,
                prompt_type=None, **kwargs) -> np.ndarray:

@@ -4,6 +4,7 @@ from .bert import BertEncoder
 from .configs import BertConfig, GemmaConfig, LlamaConfig, Qwen3Config
 from .decoder import EmbeddingGemmaModel, LlamaBidirectionalModel, Qwen3Decoder
 from .parallel_plan import bert_tp_plan, decoder_tp_plan
+from .projection import PostPoolingDense, gemma_post_pooling
 from .registry import (ModelSpec, detect_model_type, get_model_spec, list_models, register_alias,
                        register_model)
 
@@ -23,10 +24,11 @@ register_model("xlm-roberta", ModelSpec(BertConfig, BertEncoder, _w.load_xlm_rob
 register_alias("bge-m3", "xlm-roberta")
 register_model("embeddinggemma", ModelSpec(GemmaConfig, EmbeddingGemmaModel, _w.load_gemma_weights,
                                            decoder_tp_plan, default_pooling="mean",
-                                           default_padding_side="right"))
+                                           default_padding_side="right",
+                                           post_pooling_fn=gemma_post_pooling))
 
 __all__ = [
     "BertConfig", "BertEncoder", "EmbeddingGemmaModel", "GemmaConfig", "LlamaBidirectionalModel",
-    "LlamaConfig", "ModelSpec", "Qwen3Config", "Qwen3Decoder", "detect_model_type",
+    "LlamaConfig", "ModelSpec", "PostPoolingDense", "Qwen3Config", "Qwen3Decoder", "detect_model_type",
     "get_model_spec", "list_models", "register_alias", "register_model",
 ]

@@ -34,18 +34,22 @@ def lib_path() -> Path:
 
 
 def load():
-    """Return the ``ctypes.CDLL`` for the native library, building it in-tree when missing."""
+    """Return the ``ctypes.CDLL`` for the native library. The library in the tree is used when it
+    was built from the present sources (a digest stored next to it says so); otherwise it is
+    rebuilt first, under a file lock so that the ranks of one job do not build at the same time.
+    ``LSET_B200_NO_BUILD=1`` forbids building: a missing or outdated library is then an error."""
     global _lib
     if _lib is not None:
         return _lib
     with _lock:
         if _lib is None:
-            if not _LIB_PATH.exists():
-                if os.environ.get("LSET_B200_NO_BUILD"):
-                    raise NativeError(f"{_LIB_PATH} is missing and LSET_B200_NO_BUILD is set")
-                from lset_b200.csrc.build import build
+            from lset_b200.csrc import build as _build
 
-                build()
+            if not _build.is_current():
+                if os.environ.get("LSET_B200_NO_BUILD"):
+                    raise NativeError(f"{_LIB_PATH} is missing or older than its sources and "
+                                      f"LSET_B200_NO_BUILD is set")
+                _build.ensure_built()
             _lib = ctypes.CDLL(str(_LIB_PATH))
     return _lib
 

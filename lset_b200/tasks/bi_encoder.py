@@ -60,22 +60,38 @@ class BiEncoderTask(nn.Module):
         self.top_k = top_k
         self.dp_group = dp_group
         self.joint_encode = joint_encode
+        # optional module applied to the pooled embedding before normalisation (``ModelSpec.
+        # post_pooling_fn``: EmbeddingGemma's dense projection); frozen, not part of the state dict
+        self.__dict__["post_pooling"] = None
         self.logit_scale = (LogitScale.from_temperature(temperature, learnable=True,
                                                         max_scale=max_scale)
                             if learnable_scale else None)
+
+    def set_post_pooling(self, module) -> None:
+        """Install (or clear) the post-pooling projection without registering it as a submodule."""
+        self.__dict__["post_pooling"] = module
 
     # ------------------------------------------------------------------ encoding
     def _norm_flag(self):
         return self.normalize and self.matryoshka_dims is None
 
     def encode(self, model: nn.Module, batch: dict) -> torch.Tensor:
+        proj = self.post_pooling
+        norm = self._norm_flag() and proj is None
         if "cu_seqlens" in batch:
             out = model.forward_packed(batch["input_ids"], batch["position_ids"],
                                        batch["cu_seqlens"], batch["max_seqlen"])
-            return packed_pool(out["hidden_states"], batch["cu_seqlens"], self.pooling,
-                               self._norm_flag())
-        out = model(batch["input_ids"], batch["attention_mask"])
-        return pool(out["hidden_states"], batch["attention_mask"], self.pooling, self._norm_flag())
+            emb = packed_pool(out["hidden_states"], batch["cu_seqlens"], self.pooling, norm)
+        else:
+            out = model(batch["input_ids"], batch["attention_mask"])
+            emb = pool(out["hidden_states"], batch["attention_mask"], self.pooling, norm)
+        if proj is not None:
+            from ..ops.pooling import normalize
+
+            emb = proj(emb)
+            if self._norm_flag():
+                emb = normalize(emb)
+        return emb
 
     def encode_many(self, model: nn.Module, batches):
         """Embeddings for several batches; packed ones share a single forward pass."""

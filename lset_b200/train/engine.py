@@ -135,6 +135,7 @@ class TrainingEngine:
         self.packed = packed
         self.use_lora = lora or qlora
         self.step_timeout_s = step_timeout_s
+        self.save_timeout_s = max(600.0, 20.0 * float(step_timeout_s or 0.0))
         self.needs_dist_cleanup = False
 
         # ---------------------------------------------------------------- process group / device
@@ -223,6 +224,10 @@ class TrainingEngine:
             pooling=pool_name, temperature=temperature, matryoshka_dims=matryoshka_dims, top_k=top_k,
             learnable_scale=learnable_temperature, cascade=cascade, cascade_d_small=cascade_d_small,
             cascade_K_prime=cascade_K_prime, dp_group=self.dp_group)
+        if spec.post_pooling_fn is not None and model_path is not None:
+            proj = spec.post_pooling_fn(model_path)
+            if proj is not None:
+                self.task.set_post_pooling(proj.to(self.device, self.compute_dtype))
         self.task.to(self.device)
 
         # ---------------------------------------------------------------- sharded runtime + optimizer
@@ -409,6 +414,8 @@ class TrainingEngine:
                     self.task_store.load_master(extra["task"])
                     self.task_optimizer.load_state_dict(extra["task_optimizer"])
             self.micro_step = start
+            if self.watchdog is not None:
+                self.watchdog.beat()       # loading a checkpoint is not idle time
         step = start
         last_loss = None
         self.logger.reset_throughput()
@@ -471,6 +478,20 @@ class TrainingEngine:
         return last_loss
 
     def save(self, step: int) -> str:
+        if self.device.type == "cuda":
+            from ..ops import _native as nv
+
+            # a kernel that gave up a bounded wait leaves a non-zero status word: such a state is
+            # never written out (synchronising read; every rank checks before the collectives)
+            nv.check_status(self.device)
+        if self.watchdog is None:
+            return self._save(step)
+        # gathering and writing a large model takes longer than a step: the save runs under its
+        # own, larger idle limit instead of tripping the step watchdog on every attempt
+        with self.watchdog.extended(self.save_timeout_s):
+            return self._save(step)
+
+    def _save(self, step: int) -> str:
         extra = {"scheduler": self.scheduler.state_dict(), "epoch": self.epoch,
                  "rng": torch.get_rng_state(), "micro_step": self.micro_step,
                  "batch_in_epoch": self._batch_in_epoch}

@@ -33,6 +33,25 @@ class StepWatchdog:
     def beat(self) -> None:
         self._last = time.monotonic()
 
+    def extended(self, limit_s: float):
+        """Context manager for a phase that legitimately takes longer than a step (writing a
+        checkpoint, loading one): inside it the idle limit is ``limit_s``; the clock restarts on
+        entry and on exit."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def scope():
+            prev = self.limit_s
+            self.limit_s = max(float(limit_s), prev)
+            self.beat()
+            try:
+                yield
+            finally:
+                self.beat()
+                self.limit_s = prev
+
+        return scope()
+
     def start(self) -> None:
         if self._thread is not None:
             return

@@ -298,3 +298,44 @@ def test_runtime_options_and_reference_env_switches(monkeypatch):
     finally:
         for k, v in saved.items():
             setattr(ro.options, k, v)
+
+
+def test_gemma_post_pooling_projection_is_applied_between_pooling_and_normalisation(tmp_path):
+    """``2_Dense`` / ``3_Dense`` next to a checkpoint become the spec's post-pooling module; the
+    task and the chunked encoder apply it before the L2 normalisation."""
+    from safetensors.torch import save_file
+
+    from lset_b200.eval.chunked_encoder import encode_chunked
+    from lset_b200.models import GemmaConfig, get_model_spec
+    from lset_b200.tasks.bi_encoder import BiEncoderTask
+
+    torch.manual_seed(0)
+    H = 32
+    w_up, w_down = torch.randn(48, H) * 0.2, torch.randn(24, 48) * 0.2
+    for sub, w in (("2_Dense", w_up), ("3_Dense", w_down)):
+        (tmp_path / sub).mkdir()
+        save_file({"linear.weight": w}, str(tmp_path / sub / "model.safetensors"))
+    spec = get_model_spec("embeddinggemma")
+    proj = spec.post_pooling_fn(tmp_path)
+    assert proj is not None and proj.out_features == 24
+    assert spec.post_pooling_fn(tmp_path / "2_Dense") is None      # no dense layers there
+    cfg = GemmaConfig(vocab_size=128, hidden_size=H, intermediate_size=64, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=1, head_dim=16,
+                      query_pre_attn_scalar=16, layer_types=["full_attention"])
+    model = spec.model_cls(cfg).eval()
+    ids = torch.randint(1, 128, (3, 10))
+    mask = torch.ones(3, 10, dtype=torch.long)
+    mask[1, 6:] = 0
+    plain = BiEncoderTask(pooling="mean", normalize=False)
+    task = BiEncoderTask(pooling="mean", normalize=True)
+    task.set_post_pooling(proj)
+    assert "post_pooling" not in dict(task.named_modules())
+    with torch.no_grad():
+        pooled = plain.encode(model, {"input_ids": ids, "attention_mask": mask})
+        emb = task.encode(model, {"input_ids": ids, "attention_mask": mask})
+    want = torch.nn.functional.normalize(pooled @ w_up.t() @ w_down.t(), dim=-1)
+    assert emb.shape == (3, 24) and torch.allclose(emb, want, atol=1e-5)
+    texts = ["a", "b"]
+    toks = lambda ts: [[5, 6, 7, 8][: 2 + i] for i, _ in enumerate(ts)]
+    out = encode_chunked(model, toks, None, texts, device="cpu", pooling="mean", post_pooling=proj)
+    assert out.shape == (2, 24) and abs(float((out[0] ** 2).sum()) - 1.0) < 1e-4

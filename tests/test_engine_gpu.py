@@ -43,6 +43,16 @@ def test_gpu_matches_cpu_oracle_and_learns(packed):
     gg, gc = _flat(gpu), _flat(cpu)
     cos = torch.nn.functional.cosine_similarity(gg, gc, dim=0).item()
     assert cos > 0.98, cos
+    # group by group (one per layer plus the root group), so that a wrong gradient in a small
+    # parameter set (norm weights, q/k norms) cannot hide behind the large matrices
+    for a, b in zip(gpu.store.groups, cpu.store.groups):
+        ga, gb = a.flat_grad.float().cpu(), b.flat_grad.float().cpu()
+        rel = ((ga - gb).norm() / gb.norm().clamp_min(1e-12)).item()
+        assert rel < 3e-2, (a.name, rel)
+        for p, o in zip(b.params, b.offsets):   # and every parameter on its own, more loosely
+            pa, pb = ga[o:o + p.numel()], gb[o:o + p.numel()]
+            prel = ((pa - pb).norm() / pb.norm().clamp_min(1e-12)).item()
+            assert prel < 6e-2, (a.name, tuple(p.shape), prel)
     gpu.optimizer_step()
     losses = [float(gpu.train_step(_batch(0, 8, packed))) for _ in range(8)]
     assert losses[-1] < losses[0], losses
@@ -111,3 +121,43 @@ def test_other_families_train_on_gpu(name, cfg):
     gpu.optimizer_step()
     losses = [float(gpu.train_step(_batch(0, 8))) for _ in range(6)]
     assert losses[-1] < losses[0], (name, losses)
+
+
+def test_step_after_a_bounded_wait_timeout_changes_nothing_and_is_not_saved(tmp_path):
+    """A kernel that gives up a bounded wait leaves a non-zero status word. The optimizer sees it on
+    the device (no host sync) and applies nothing: parameters, master weights and moments stay bit
+    for bit; ``save`` refuses to write such a state. The wait that runs out here is the probe
+    kernel's, on a flag that nothing sets; nothing faults and the context stays usable."""
+    import ctypes
+    import os
+
+    eng = _engine(output_dir=str(tmp_path))
+    eng.train_step(_batch(0, 8))                       # a normal step first: moments are non-zero
+    eng.forward_backward(_batch(8, 16), True)
+    lib = nv.load()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    word = nv.status_word(eng.device)
+    rc = lib.lb_bounded_wait_probe(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(1),
+                                   ctypes.c_ulonglong(100_000_000), ctypes.c_void_p(word.data_ptr()),
+                                   ctypes.c_void_p(waited.data_ptr()),
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    snap = [(g.flat_param.clone(), g.master.clone(), g.exp_avg.clone(), g.exp_avg_sq.clone())
+            for g in eng.store.groups]
+    eng.optimizer.step()
+    torch.cuda.synchronize()
+    assert int(word.item()) == 4
+    for g, (p, m, a, b) in zip(eng.store.groups, snap):
+        assert torch.equal(g.flat_param, p) and torch.equal(g.master, m), g.name
+        assert torch.equal(g.exp_avg, a) and torch.equal(g.exp_avg_sq, b), g.name
+    with pytest.raises(nv.NativeError):
+        eng.save(1)
+    assert not os.path.exists(tmp_path / "step_1" / "meta.pt")
+    # the status word was cleared by the check: the next step trains again
+    eng.optimizer.zero_grad()
+    before = eng.store.groups[0].master.clone()
+    eng.train_step(_batch(0, 8))
+    torch.cuda.synchronize()
+    assert not torch.equal(before, eng.store.groups[0].master)
+    nv.check_status()

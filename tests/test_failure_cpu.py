@@ -101,3 +101,25 @@ def test_watchdog_exit_code_for_launcher():
     r = subprocess.run([sys.executable, "-c", code], cwd=os.path.dirname(os.path.dirname(__file__)),
                        capture_output=True, text=True, timeout=30)
     assert r.returncode == 75 and "watchdog" in r.stderr
+
+
+def test_watchdog_gives_a_slow_save_its_own_limit():
+    """A phase that is known to be slow (a checkpoint save) runs under an extended idle limit; the
+    step limit applies again afterwards."""
+    import time
+
+    from lset_b200.train.watchdog import StepWatchdog
+
+    fired = []
+    wd = StepWatchdog(0.2, on_timeout=fired.append, poll_s=0.02, exit_process=False)
+    wd.start()
+    try:
+        with wd.extended(5.0):
+            time.sleep(0.5)            # two and a half step limits: a slow save
+        assert not fired and wd.limit_s == 0.2
+        time.sleep(0.1)
+        assert not fired               # the clock restarted when the save ended
+        time.sleep(0.4)
+        assert fired                   # and the step limit is back in force
+    finally:
+        wd.stop()

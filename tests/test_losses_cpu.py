@@ -2,6 +2,7 @@
 LogitScale, and the bi-encoder task."""
 import math
 
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -72,7 +73,12 @@ def test_matryoshka_and_logit_scale():
     assert math.isclose(s().item(), 50.0, rel_tol=1e-5) and s.log_scale.requires_grad
     s.log_scale.data.fill_(10.0)
     assert s().item() == s.max_scale
-    assert not LogitScale(20.0).log_scale.requires_grad
+    assert not LogitScale(20.0, learnable=False).log_scale.requires_grad
+    assert LogitScale(20.0, 50.0).max_scale == 50.0      # positional order: init, max, learnable
+    with pytest.raises(ValueError):
+        LogitScale(0.0)
+    with pytest.raises(ValueError):
+        LogitScale.from_temperature(-1.0)
 
 
 def test_task_joint_encode_equals_separate():

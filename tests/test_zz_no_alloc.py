@@ -49,11 +49,15 @@ def _run_both(lib, N, H, with_res, w_off, seed):
     dw = torch.empty(H, dtype=torch.float32, device=dev)
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]     # the driver's own count of free device bytes
     rc = lib.lb_rms_norm_bwd_noalloc(_p(dy), _p(dres), _p(x), _p(w), _p(rstd), _p(dx), _p(dw),
                                      c_int(1), c_int(0), c_int(N), c_int(H), c_float(w_off), stream)
     assert rc == 0, lib.lb_noalloc_strerror(rc)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    # the caching allocator's counter would not see a raw cudaMalloc inside the library; the
+    # driver's free-byte count does (the kernels were loaded by the regular call above)
+    assert torch.cuda.mem_get_info()[0] >= free_before
     return dx, dx_ref, dw, dw_ref
 
 
