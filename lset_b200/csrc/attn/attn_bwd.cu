@@ -16,6 +16,7 @@
 //
 // Counterpart of the flash_attn / varlen_attn backward used by the reference through autograd
 // (lset/models/decoder/qwen3/attention.py:203-234).
+#include "../common/api.h"
 #include "../common/ptx.cuh"
 #include "../common/row.cuh"
 #include "../common/tma_desc.h"
@@ -653,6 +654,11 @@ extern "C" int lb_attn_bwd(const void* dO, long long lddo, const void* q, long l
   AttnBwdArgs a{seq_start, seq_end, nullptr, lse, delta, (bf16*)dq, lddq, (bf16*)dk, lddk, (bf16*)dv, lddv,
                 T, Hq, Hk, softmax_scale, softmax_scale * kLog2eF, causal, status};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (hd != 128 && hd != 64) return -3;
+  // gradient rows of tokens behind the last sequence are written by no kernel below
+  if (int rc = lb_attn_zero_tail(plan_q, cap_q, T, dq, lddq, Hq * hd, dk, lddk, Hk * hd, dv, lddv,
+                                 Hk * hd, stream))
+    return rc;
   if (hd == 128)
     return launch_bwd<128>(dO, lddo, q, ldq, k, ldk, v, ldv, o, ldo, delta, plan_q, cap_q, plan_kv,
                            cap_kv, a, st);

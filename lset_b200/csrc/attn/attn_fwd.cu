@@ -380,7 +380,34 @@ __global__ void attn_plan_kernel(const int* __restrict__ seq_start,
     if (threadIdx.x == blockDim.x - 1) s_base += scan[threadIdx.x];
     __syncthreads();
   }
-  if (threadIdx.x == 0) plan[0] = s_base < capacity ? s_base : capacity;
+  if (threadIdx.x == 0) {
+    plan[0] = s_base < capacity ? s_base : capacity;
+    // second spare word (the first is the forward kernel's work counter): one past the last token
+    // that belongs to a sequence. Tokens behind it (a stream padded to a fixed budget) are
+    // written by no attention kernel; the launchers clear those rows.
+    plan[1 + 2 * capacity + 1] = seq_end[B - 1];
+  }
+}
+
+// Rows [*end, T) of up to three [T, w] bf16 matrices := 0 (nothing to do when *end >= T).
+__global__ void __launch_bounds__(256)
+    attn_zero_tail_kernel(const int* __restrict__ end_ptr, int T, bf16* p0, long long ld0, int w0,
+                          bf16* p1, long long ld1, int w1, bf16* p2, long long ld2, int w2) {
+  const int end = *end_ptr;
+  if (end >= T || end < 0) return;
+  bf16* ps[3] = {p0, p1, p2};
+  const long long lds[3] = {ld0, ld1, ld2};
+  const int ws[3] = {w0, w1, w2};
+  for (int m = 0; m < 3; ++m) {
+    if (ps[m] == nullptr) continue;
+    const int vec = ws[m] / 8;
+    const long long total = 1LL * (T - end) * vec;
+    for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += 1LL * gridDim.x * blockDim.x) {
+      const long long r = end + i / vec, c = (i % vec) * 8;
+      *reinterpret_cast<uint4*>(ps[m] + r * lds[m] + c) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
 }
 
 template <int HD>
@@ -417,6 +444,18 @@ using namespace lb;
 
 // plan: int32 [1 + 2 * capacity + 1] (the last word is scratch for the attention kernels);
 // capacity >= ceil(T / tile_tokens) + B always suffices.
+// Clears the rows behind the last sequence of a stream (see attn_plan_kernel). plan / capacity as
+// passed to lb_attn_plan; widths in elements, multiples of 8; unused matrices null.
+extern "C" int lb_attn_zero_tail(const int* plan, int capacity, int T, void* p0, long long ld0,
+                                 int w0, void* p1, long long ld1, int w1, void* p2, long long ld2,
+                                 int w2, void* stream) {
+  if (T <= 0) return 0;
+  if ((w0 | w1 | w2) & 7) return -3;
+  attn_zero_tail_kernel<<<64, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      plan + 1 + 2 * capacity + 1, T, (bf16*)p0, ld0, w0, (bf16*)p1, ld1, w1, (bf16*)p2, ld2, w2);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 extern "C" int lb_attn_plan(const int* seq_start, const int* seq_end, int B, int tile_tokens,
                             int* plan, int capacity, void* stream) {
   if (B <= 0) return -3;
@@ -449,12 +488,16 @@ extern "C" int lb_attn_fwd(const void* q, long long ldq, const void* k, long lon
   rc = make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * hd, (uint64_t)T, (uint64_t)ldv * 2, 64, kAttnKvBlock,
                     true);
   if (rc) return rc;
-  // the plan buffer carries one spare word behind its 1 + 2 * max_tiles entries
+  // the plan buffer carries two spare words behind its 1 + 2 * max_tiles entries: this kernel's
+  // work counter and the end of the stream's last sequence
   unsigned* counter = reinterpret_cast<unsigned*>(const_cast<int*>(plan)) + 1 + 2 * max_tiles;
   AttnFwdArgs a{seq_start, seq_end, plan, counter, (bf16*)o, ldo, lse, T, Hq, Hk,
                 softmax_scale * kLog2eF, causal, status};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), st) != cudaSuccess) return -12;
+  if (hd != 128 && hd != 64 && hd != 256) return -3;
+  rc = lb_attn_zero_tail(plan, max_tiles, T, o, ldo, Hq * hd, nullptr, 0, 0, nullptr, 0, 0, stream);
+  if (rc) return rc;
   if (hd == 128) return launch_fwd<128>(tmQ, tmK, tmV, a, max_tiles, st);
   if (hd == 64) return launch_fwd<64>(tmQ, tmK, tmV, a, max_tiles, st);
   if (hd == 256) return launch_fwd<256>(tmQ, tmK, tmV, a, max_tiles, st);

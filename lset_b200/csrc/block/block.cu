@@ -42,17 +42,6 @@ int scale_bf16(__nv_bfloat16* x, long long n, float s, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// Split of the token contraction that fills the SMs for a [n_out, k_in] weight gradient.
-int wgrad_splits(int n_out, int k_in, int tokens) {
-  const int tiles = ((n_out + 127) / 128) * ((k_in + 255) / 256);
-  const int kb = tokens >= 64 ? (tokens + 63) / 64 : 1;
-  if (tiles >= 148) return 1;
-  const int by_k = kb >= 8 ? kb / 8 : 1;
-  const int by_sm = (2 * 148 + tiles - 1) / tiles;
-  const int s = by_k < by_sm ? by_k : by_sm;
-  return s < 1 ? 1 : s;
-}
-
 struct Saved {
   __nv_bfloat16 *x1, *res1, *qkv, *qr, *kr, *o, *x2, *gu, *h;
   float *rstd1, *rstd2, *q_rstd, *k_rstd, *lse;
@@ -178,14 +167,14 @@ int lin_wgrad(const LbLinear& l, const __nv_bfloat16* dy, long long lddy, const 
               const LbStreamCtx* c) {
   if (l.wgrad != nullptr)
     LB_TRY(lb_gemm_bf16(dy, x, l.wgrad, l.n_out, l.k_in, T, lddy, ldx, l.k_in, 1, 1, 1, 1, nullptr,
-                        wgrad_splits(l.n_out, l.k_in, T), 0, c->status, c->stream));
+                        0 /*auto*/, 0, c->status, c->stream));
   if (l.lora_r > 0) {
     if (l.lora_a_grad != nullptr)
       LB_TRY(lb_gemm_bf16(us, x, l.lora_a_grad, l.lora_r, l.k_in, T, l.lora_r, ldx, l.k_in, 1, 1, 1,
-                          1, nullptr, wgrad_splits(l.lora_r, l.k_in, T), 0, c->status, c->stream));
+                          1, nullptr, 0, 0, c->status, c->stream));
     if (l.lora_b_grad != nullptr)
       LB_TRY(lb_gemm_bf16(dy, ts, l.lora_b_grad, l.n_out, l.lora_r, T, lddy, l.lora_r, l.lora_r, 1,
-                          1, 1, 1, nullptr, wgrad_splits(l.n_out, l.lora_r, T), 0, c->status,
+                          1, 1, 1, nullptr, 0, 0, c->status,
                           c->stream));
   }
   return 0;
@@ -218,7 +207,7 @@ extern "C" size_t lb_block_work_bytes(const LbBlockDesc* d, int T) {
 
 extern "C" int lb_block_fwd_launches(const LbBlockDesc* d, const LbStreamCtx* c, int has_residual) {
   (void)has_residual;
-  int n = 5;  // two norms, rope, attention, glu
+  int n = 6;  // two norms, rope, attention (tail clear + kernel), glu
   for (int i = 0; i < 7; ++i) {
     const LbLinear* l = linear_at(d, i);
     if (l != nullptr) n += lin_fwd_launches(*l);
@@ -227,7 +216,7 @@ extern "C" int lb_block_fwd_launches(const LbBlockDesc* d, const LbStreamCtx* c,
 }
 
 extern "C" int lb_block_bwd_launches(const LbBlockDesc* d, const LbStreamCtx* c) {
-  int n = 1 + 3 + 1;  // glu, attention (delta, dq, dkv), rope
+  int n = 1 + 4 + 1;  // glu, attention (tail clear, delta, dq, dkv), rope
   n += d->ln1_wgrad != nullptr ? 2 : 1;
   n += d->ln2_wgrad != nullptr ? 2 : 1;
   if (d->qk_norm && d->qn_wgrad != nullptr) n += d->kn_wgrad == d->qn_wgrad + d->hd ? 1 : 3;

@@ -39,6 +39,9 @@ int lb_glu_bwd(int kind, const void* dout, long long ld_dout, const void* gate, 
                void* stream);
 
 // attn/
+int lb_attn_zero_tail(const int* plan, int capacity, int T, void* p0, long long ld0, int w0,
+                      void* p1, long long ld1, int w1, void* p2, long long ld2, int w2,
+                      void* stream);
 int lb_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                 long long ldv, const int* seq_start, const int* seq_end, const int* plan,
                 int max_tiles, void* o, long long ldo, float* lse, int T, int Hq, int Hk, int hd,

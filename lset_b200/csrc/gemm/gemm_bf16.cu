@@ -20,6 +20,7 @@
 // Replaces cuBLAS behind nn.Linear in the reference (lset/models/decoder/qwen3/attention.py:102-104,
 // lset/models/decoder/qwen3/mlp.py:28).
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "../common/ptx.cuh"
 #include "../common/tma_desc.h"
@@ -32,6 +33,20 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kGemmThreads = 192;
 constexpr int kGatherThreads = 256;  // + 2 pull warps
+
+// Number of epilogue warps. The plain store / reduce epilogue of the bf16 kernel runs on eight
+// (two per tensor-memory lane quarter, each taking half of the tile's columns): at K = 1024 the
+// main loop of a 128 x 256 tile lasts about as long as four warps need to drain it, and the drain
+// then bounds the kernel. The loss / GLU epilogues, the 8-bit kernel and the peer-gather variants
+// (which already carry two pull warps) keep four.
+template <int EPI, int GATHER, int F8>
+constexpr int epi_warps() {
+  return (EPI == 0 /*EPI_STORE*/ && GATHER == 0 && F8 == 0) ? 8 : 4;
+}
+template <int EPI, int GATHER, int F8>
+constexpr int gemm_threads() {
+  return GATHER ? kGatherThreads : 64 + 32 * epi_warps<EPI, GATHER, F8>();
+}
 
 struct GemmArgs {
   int M, N, K;
@@ -95,13 +110,14 @@ struct GemmArgs {
   const float* f8_sb;
   int f8_sa_stride, f8_sb_stride;
   int f8_a_e5m2, f8_b_e5m2;
+  int dbg;  // TEMP diagnostic: 1 = epilogue without global stores, 2 = epilogue without any work
   int* status;
 };
 
 enum { EPI_STORE = 0, EPI_LSE = 1, EPI_PGRAD = 2, EPI_GLU = 3 };
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int BN>
+template <int BN, int EW = 4, int F8 = 0>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
@@ -111,10 +127,13 @@ struct Cfg {
   // "one 128-byte row segment per 8 lanes" for global memory: 32 x 32 fp32 (row stride 33 words)
   // for the fp32 reductions, 32 rows x 64 bf16 columns (row stride 144 bytes) for bf16 stores;
   // both strides are conflict-free for the lane-per-row writes and the 8-lanes-per-row reads
-  static constexpr int EPI_STAGE_WORDS = 32 * 36;
-  static constexpr int EPI_STAGE_BYTES = 4 * EPI_STAGE_WORDS * 4;
+  // With eight epilogue warps the bf16 staging block is 32 rows x 32 columns (row stride 80
+  // bytes, also conflict-free) and is flushed after every chunk, so that the blocks of all warps
+  // still fit beside the four operand stages.
+  static constexpr int EPI_STAGE_WORDS = EW == 8 ? 32 * 33 : 32 * 36;
+  static constexpr int EPI_STAGE_BYTES = EW * EPI_STAGE_WORDS * 4;
   // per epilogue warp: the BN per-column dequantisation factors of the current tile (8-bit GEMM)
-  static constexpr int EPI_SCALE_BYTES = 4 * 256 * 4;
+  static constexpr int EPI_SCALE_BYTES = F8 ? 4 * 256 * 4 : 0;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
                                     EPI_STAGE_BYTES + EPI_SCALE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
@@ -134,11 +153,12 @@ __device__ __forceinline__ void red_add8_bf16(void* dst, const uint4& v) {
 }
 
 template <int A_MN, int B_MN, int BN, typename OutT, int EPI, int GATHER = 0, int F8 = 0>
-__global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB2, GemmArgs g) {
-  using C = Cfg<BN>;
+  constexpr int EW = epi_warps<EPI, GATHER, F8>();
+  using C = Cfg<BN, EW, F8>;
   // 8-bit operands: K-major only; a k-block is still 128 bytes of every row, i.e. 128 elements,
   // and the shared-memory tiles, swizzle and descriptors are byte-for-byte those of the bf16 form.
   static_assert(!F8 || (!A_MN && !B_MN && GATHER == 0 && EPI == EPI_STORE), "fp8: plain TN GEMM");
@@ -164,7 +184,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], 32 * EW);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -407,8 +427,11 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..5, or 2..9)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    // eight warps: warps 2..5 take the first half of the tile's 32-column chunks, 6..9 the second
+    [[maybe_unused]] const int half = (warp - 2) >> 2;
+    constexpr int kChunks = BN / 32 / (EW / 4);
     OutT* Cout = reinterpret_cast<OutT*>(g.C);
     int it = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
@@ -425,6 +448,11 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         break;
       }
       tc_fence_after();
+      if (g.dbg == 2) {
+        tc_fence_before();
+        mbar_arrive(&tempty[acc]);
+        continue;
+      }
       if constexpr (EPI == EPI_GLU) {
         // gate chunk c and up chunk c of the tile -> gate_up (both halves) and h = act(gate) * up.
         // Values are rounded to bf16 before the activation, as the stand-alone GLU kernel sees them.
@@ -542,7 +570,8 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = (EW == 8 ? half * kChunks : 0); c < (EW == 8 ? (half + 1) * kChunks : BN / 32);
+           ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
@@ -658,7 +687,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
             if constexpr (sizeof(OutT) == 2) {
               // this lane's 32 columns go to its row of the staging block (flushed below)
               uint8_t* srow = reinterpret_cast<uint8_t*>(epi_stage + (warp - 2) * C::EPI_STAGE_WORDS) +
-                              lane * 144 + (c & 1) * 64;
+                              (EW == 8 ? lane * 80 : lane * 144 + (c & 1) * 64);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 pk;
@@ -683,7 +712,35 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
             }
           }
         }
-        if constexpr (sizeof(OutT) == 2 && EPI != EPI_LSE) {
+        if constexpr (sizeof(OutT) == 2 && EPI != EPI_LSE && EW == 8) {
+          // The warp writes its 32 x 32 block out after every chunk: 4 lanes cover one 64-byte row
+          // segment, a store instruction fills eight of them.
+          __syncwarp();
+          const uint8_t* sblk =
+              reinterpret_cast<const uint8_t*>(epi_stage + (warp - 2) * C::EPI_STAGE_WORDS);
+          const int rr = lane >> 2, cc = lane & 3;
+          const int colb = n0 + c * 32 + cc * 8;
+          if (colb < g.N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int lr = i * 8 + rr;
+              const int grow = m0 + q * 32 + lr;
+              if (grow < m_limit) {
+                const uint4 pk = *reinterpret_cast<const uint4*>(sblk + lr * 80 + cc * 16);
+                if (g.c_rows_per_peer > 0) {
+                  // reduce-scatter in bf16: the row's owner accumulates over NVLink
+                  OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
+                               static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
+                  red_add8_bf16(base + colb, pk);
+                } else if (g.dbg != 1) {
+                  *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
+                }
+              }
+            }
+          }
+          __syncwarp();
+        }
+        if constexpr (sizeof(OutT) == 2 && EPI != EPI_LSE && EW != 8) {
           // After every second 32-column chunk the warp writes its 32 x 64 block out: 8 lanes cover
           // one 128-byte row segment, so each store instruction fills four whole lines.
           if (c & 1) {
@@ -704,7 +761,7 @@ __global__ void __launch_bounds__(GATHER ? kGatherThreads : kGemmThreads, 1)
                     OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
                                  static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
                     red_add8_bf16(base + colb, pk);
-                  } else {
+                  } else if (g.dbg != 1) {
                     *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
                   }
                 }
@@ -789,7 +846,7 @@ template <int A_MN, int B_MN, int BN, typename OutT, int EPI = EPI_STORE, int GA
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, int grid,
            cudaStream_t stream, const CUtensorMap* tmA2 = nullptr,
            const CUtensorMap* tmB2 = nullptr) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, epi_warps<EPI, GATHER, F8>(), F8>;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN, OutT, EPI, GATHER, F8>;
   static bool configured = false;
   if (!configured) {
@@ -798,9 +855,34 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, in
       return -10;
     configured = true;
   }
-  kern<<<grid, GATHER ? kGatherThreads : kGemmThreads, C::SMEM_BYTES, stream>>>(
+  kern<<<grid, gemm_threads<EPI, GATHER, F8>(), C::SMEM_BYTES, stream>>>(
       tmA, tmB, tmA2 != nullptr ? *tmA2 : tmA, tmB2 != nullptr ? *tmB2 : tmB, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Split of the contraction for a product whose output tiles alone do not fill the SMs evenly
+// (the weight gradients: few tiles, a contraction over all tokens). Cost model in units of one
+// k-block of tensor-core work: every wave of `sms` items takes max(kb_per, kEpi), where kEpi is
+// the fp32 reduction epilogue of an item, hidden behind the next item's main loop only when that
+// is at least as long. More splits mean more reduction traffic, so a candidate must win by 2 %.
+int auto_splits(long long tiles, int kb_total, int sms) {
+  constexpr int kEpi = 32, kMinKb = 32;
+  if (kb_total < 2 * kMinKb) return 1;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 32; ++s) {
+    const int kb_per = (kb_total + s - 1) / s;
+    if (s > 1 && kb_per < kMinKb) break;
+    const int se = (kb_total + kb_per - 1) / kb_per;
+    const long long items = tiles * se;
+    const long long waves = (items + sms - 1) / sms;
+    const double cost = double(waves) * (kb_per > kEpi ? kb_per : kEpi) + kEpi;
+    if (cost < best_cost * 0.98) {
+      best = se;
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
 template <int A_MN, int B_MN, int BN>
@@ -817,7 +899,9 @@ int launch_out(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g
 //   a_mn = 0: A is [M, K] row-major with row stride lda; a_mn = 1: A is stored [K, M], stride lda.
 //   b_mn = 0: B is [N, K] row-major with row stride ldb; b_mn = 1: B is stored [K, N], stride ldb.
 //   out_fp32: C is float (else bf16), row stride ldc. accumulate (fp32 only): C += product.
-//   splits: split of K (fp32 accumulate only; >1 forces accumulate). bn: 0 = auto, 128 or 256.
+//   splits: split of K (fp32 accumulate only; >1 forces accumulate; 0 = chosen here, see
+//   auto_splits: the caller must then pass accumulate = 1 and an initialised C).
+//   bn: 0 = auto, 128 or 256.
 // All leading dimensions and N must be multiples of 8 elements; base pointers 16-byte aligned.
 // Returns 0 or a negative code; device-side timeouts are reported through *status (device int).
 static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K,
@@ -847,6 +931,9 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   }
   const int tiles_n = (N + bn - 1) / bn;
   const int kb_total = (K + BK - 1) / BK;
+  if (splits == 0)
+    splits = (out_fp32 && accumulate && !scatter)
+                 ? auto_splits(1LL * tiles_m * tiles_n, kb_total, sms) : 1;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   int kb_per = (kb_total + splits - 1) / splits;
@@ -878,6 +965,11 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   g.splits = splits;
   g.kb_per_split = kb_per;
   g.status = status;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("LB_GEMM_DBG"); dbg = e ? atoi(e) : 0; }
+    g.dbg = dbg;
+  }
   if (c_peers != nullptr && c_rows_per_peer > 0) {
     if (c_world > 8) return -3;
     for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);
@@ -938,6 +1030,8 @@ extern "C" int lb_gemm_fp8(const void* A, const void* B, void* C, int M, int N, 
   }
   const int tiles_n = (N + bn - 1) / bn;
   const int kb_total = (K + BKE - 1) / BKE;
+  if (splits == 0)
+    splits = (out_fp32 && accumulate) ? auto_splits(1LL * tiles_m * tiles_n, kb_total, sms) : 1;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   const int kb_per = (kb_total + splits - 1) / splits;

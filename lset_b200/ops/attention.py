@@ -55,8 +55,9 @@ class AttnPlan:
         if hit is not None:
             return hit
         cap = (self.T + tile_tokens - 1) // tile_tokens + self.B
-        # one spare word behind the entries: the work counter of the persistent forward kernel
-        plan = torch.empty(1 + 2 * cap + 1, dtype=torch.int32, device=self.seq_start.device)
+        # two spare words behind the entries: the work counter of the persistent forward kernel and
+        # the end of the last sequence (rows behind it are cleared by the attention launchers)
+        plan = torch.empty(1 + 2 * cap + 2, dtype=torch.int32, device=self.seq_start.device)
         rc = nv.load().lb_attn_plan(nv.c_void_p(self.seq_start.data_ptr()),
                                     nv.c_void_p(self.seq_end.data_ptr()), nv.c_int(self.B),
                                     nv.c_int(tile_tokens), nv.c_void_p(plan.data_ptr()),
@@ -114,7 +115,7 @@ def _native_fwd(q, k, v, plan: AttnPlan, causal, scale):
         nv.c_int(Hq), nv.c_int(Hk), nv.c_int(hd), nv.c_float(scale), nv.c_int(int(causal)),
         nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
     nv.check_rc(rc, "lb_attn_fwd")
-    nv.count_launch()
+    nv.count_launch(2)
     return o, lse
 
 
@@ -140,7 +141,7 @@ def _native_bwd(do, q, k, v, o, lse, plan: AttnPlan, causal, scale, dq, dk, dv):
         nv.c_int(hd), nv.c_float(scale), nv.c_int(int(causal)),
         nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
     nv.check_rc(rc, "lb_attn_bwd")
-    nv.count_launch(3)
+    nv.count_launch(4)
 
 
 def _unit_inner(t):

@@ -163,10 +163,11 @@ def matmul_fp8(a: Fp8Tensor, b: Fp8Tensor, *, out: Optional[torch.Tensor] = None
         raise TypeError("output must be bf16 or fp32")
     if out_dtype != torch.float32:
         splits = 1
+    auto = splits == 0      # the launcher picks the split (it may reduce into ``out``)
     if out is None:
-        alloc = torch.zeros if (accumulate or splits > 1) else torch.empty
+        alloc = torch.zeros if (accumulate or splits != 1) else torch.empty
         out = alloc(M, N, dtype=out_dtype, device=a.data.device)
-    elif splits > 1 and not accumulate:
+    elif splits != 1 and not accumulate:
         out.zero_()
     if M == 0 or N == 0:
         return out
@@ -179,7 +180,7 @@ def matmul_fp8(a: Fp8Tensor, b: Fp8Tensor, *, out: Optional[torch.Tensor] = None
         nv.c_int(int(a.e5m2)), nv.c_int(int(b.e5m2)),
         nv.c_void_p(a.inv_scale.data_ptr()), nv.c_int(int(a.inv_scale.numel() > 1)),
         nv.c_void_p(b.inv_scale.data_ptr()), nv.c_int(int(b.inv_scale.numel() > 1)),
-        nv.c_int(int(out_dtype == torch.float32)), nv.c_int(int(accumulate or splits > 1)),
+        nv.c_int(int(out_dtype == torch.float32)), nv.c_int(int(accumulate or splits > 1 or auto)),
         nv.c_void_p(nv.ptr(bias)), nv.c_int(splits), nv.c_int(0),
         nv.c_void_p(nv.status_word(a.data.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
     if rc != 0:

@@ -32,7 +32,8 @@ def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat
 
     a: ``[M, K]`` (``[K, M]`` when ``a_mn``), b: ``[N, K]`` (``[K, N]`` when ``b_mn``); 2-D bf16
     with unit inner stride. ``out`` may be given (fp32 with ``accumulate=True`` adds into it).
-    ``splits > 1`` splits the contraction and reduces with fp32 atomics (fp32 output only).
+    ``splits > 1`` splits the contraction and reduces with fp32 atomics (fp32 output only);
+    ``splits=0`` lets the launcher choose the split from the tile count and the contraction length.
     """
     if a.dim() != 2 or b.dim() != 2:
         raise ValueError("matmul_abt takes 2-D operands")
@@ -59,14 +60,15 @@ def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat
         b = b.contiguous()
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("output must be bf16 or fp32")
-    if splits > 1 and out_dtype != torch.float32:
+    if splits != 1 and out_dtype != torch.float32:
         splits = 1
+    auto = splits == 0
     if out is None:
-        if accumulate or splits > 1:
+        if accumulate or splits != 1:
             out = torch.zeros(M, N, dtype=out_dtype, device=a.device)
         else:
             out = torch.empty(M, N, dtype=out_dtype, device=a.device)
-    elif splits > 1 and not accumulate:
+    elif splits != 1 and not accumulate:
         out.zero_()
     if M == 0 or N == 0:
         return out
@@ -82,7 +84,7 @@ def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat
         nv.c_int(M), nv.c_int(N), nv.c_int(K),
         nv.c_ll(a.stride(0)), nv.c_ll(b.stride(0)), nv.c_ll(out.stride(0)),
         nv.c_int(int(a_mn)), nv.c_int(int(b_mn)), nv.c_int(int(out_dtype == torch.float32)),
-        nv.c_int(int(accumulate or splits > 1)), nv.c_void_p(nv.ptr(bias)), nv.c_int(splits),
+        nv.c_int(int(accumulate or splits > 1 or auto)), nv.c_void_p(nv.ptr(bias)), nv.c_int(splits),
         nv.c_int(bn), nv.c_void_p(nv.status_word(a.device).data_ptr()),
         nv.c_void_p(nv.stream_ptr()),
     )
@@ -93,12 +95,10 @@ def matmul_abt(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat
 
 
 def wgrad_splits(n_out: int, k_in: int, tokens: int) -> int:
-    """Split of the token contraction that fills the 148 SMs for a ``[n_out, k_in]`` weight grad."""
-    tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
-    kb = max(1, (tokens + 63) // 64)
-    if tiles >= 148:
-        return 1
-    return max(1, min(kb // 8 if kb >= 8 else 1, (2 * 148 + tiles - 1) // tiles))
+    """Split of the token contraction of a ``[n_out, k_in]`` weight gradient: 0 = chosen by the
+    launcher (``auto_splits`` in csrc/gemm/gemm_bf16.cu: whole waves of work items over the SMs,
+    items long enough to hide their reduction epilogue)."""
+    return 0
 
 
 class _Linear(torch.autograd.Function):

@@ -2,8 +2,10 @@
 captures under ``profiles/`` are taken from).
 
     python -m lset_b200.utils.kernel_bench gemm  --m 23040 --n 4096 --k 1024 [--form fprop|dgrad|wgrad]
+                                                 [--ref torch]   (torch.matmul / cuBLAS alongside)
     python -m lset_b200.utils.kernel_bench fp8   --m 23040 --n 4096 --k 1024 [--what gemm|cast|linear]
     python -m lset_b200.utils.kernel_bench attn  --seqs 64 --len 320 --hq 16 --hk 8 --hd 128 [--bwd]
+                                                 [--ref flash]   (flash_attn_varlen_func alongside)
     python -m lset_b200.utils.kernel_bench norm  --rows 23040 --h 1024 [--bwd]
     python -m lset_b200.utils.kernel_bench rope  --rows 23040 --hq 16 --hk 8 --hd 128 [--bwd]
     python -m lset_b200.utils.kernel_bench glu   --rows 23040 --i 3072 [--bwd]
@@ -67,7 +69,18 @@ def bench_gemm(a):
     ms = _time(fn, a.iters)
     flops = 2.0 * M * N * K
     byt = 2.0 * (M * K + N * K + M * N)
-    return dict(kernel=f"gemm_{a.form}", M=M, N=N, K=K, ms=ms, **roofline(ms, flops, byt))
+    out = dict(kernel=f"gemm_{a.form}", M=M, N=N, K=K, ms=ms, **roofline(ms, flops, byt))
+    if a.ref == "torch":
+        # the library GEMM (cuBLAS through torch.matmul) on the same operands, same timing method
+        if a.form == "fprop":
+            ref = lambda: torch.matmul(x, w.t())  # noqa: E731
+        elif a.form == "dgrad":
+            ref = lambda: torch.matmul(dy, w)  # noqa: E731
+        else:
+            ref = lambda: torch.matmul(dy.t(), x)  # noqa: E731
+        out["torch_matmul_ms"] = _time(ref, a.iters)
+        out["torch_over_ours"] = out["torch_matmul_ms"] / ms
+    return out
 
 
 def bench_fp8(a):
@@ -118,8 +131,27 @@ def bench_attn(a):
         fn = lambda: varlen_attention(q, k, v, plan, a.causal)  # noqa: E731
         flops = 4.0 * pairs * a.hq * a.hd
     ms = _time(fn, a.iters)
-    return dict(kernel="attn_bwd" if a.bwd else "attn_fwd", seqs=a.seqs, len=a.len, Hq=a.hq, Hk=a.hk,
-                hd=a.hd, causal=a.causal, ms=ms, **roofline(ms, flops, 0.0))
+    out = dict(kernel="attn_bwd" if a.bwd else "attn_fwd", seqs=a.seqs, len=a.len, Hq=a.hq, Hk=a.hk,
+               hd=a.hd, causal=a.causal, ms=ms, **roofline(ms, flops, 0.0))
+    if a.ref == "flash":
+        # flash-attn's varlen kernels (what the reference calls) on the same tensors
+        try:
+            from flash_attn import flash_attn_varlen_func
+        except Exception as exc:  # pragma: no cover - optional package
+            out["flash_attn"] = f"unavailable: {exc!r}"[:120]
+            return out
+        qf, kf, vf = (t.detach().clone().requires_grad_(a.bwd) for t in (q, k, v))
+        run = lambda: flash_attn_varlen_func(qf, kf, vf, cu, cu, a.len, a.len,  # noqa: E731
+                                             causal=bool(a.causal))
+        if a.bwd:
+            of = run()
+            gf = _r(T, a.hq, a.hd)
+            ref = lambda: torch.autograd.grad(of, (qf, kf, vf), gf, retain_graph=True)  # noqa: E731
+        else:
+            ref = lambda: run()  # noqa: E731
+        out["flash_attn_ms"] = _time(ref, a.iters)
+        out["flash_over_ours"] = out["flash_attn_ms"] / ms
+    return out
 
 
 def bench_norm(a):
@@ -262,7 +294,8 @@ def main(argv=None):
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=23040); g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=1024); g.add_argument("--form", default="fprop")
-    g.add_argument("--bn", type=int, default=0); g.add_argument("--splits", type=int, default=2)
+    g.add_argument("--bn", type=int, default=0); g.add_argument("--splits", type=int, default=0)
+    g.add_argument("--ref", choices=["none", "torch"], default="none")
     f = sub.add_parser("fp8")
     f.add_argument("--m", type=int, default=23040); f.add_argument("--n", type=int, default=4096)
     f.add_argument("--k", type=int, default=1024); f.add_argument("--what", default="gemm")
@@ -272,6 +305,7 @@ def main(argv=None):
     t.add_argument("--hq", type=int, default=16); t.add_argument("--hk", type=int, default=8)
     t.add_argument("--hd", type=int, default=128); t.add_argument("--bwd", action="store_true")
     t.add_argument("--bidirectional", dest="causal", action="store_false")
+    t.add_argument("--ref", choices=["none", "flash"], default="none")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=23040); n.add_argument("--h", type=int, default=1024)
     n.add_argument("--bwd", action="store_true")

@@ -85,3 +85,29 @@ def test_padded_plan(left):
     nv.check_status()
     ref = attention_ref(q.float(), k.float(), v.float(), plan.seq_start, True, seq_end=plan.seq_end)
     assert (o.float() - ref).abs().max().item() < 3e-2
+
+
+def test_stream_padded_past_the_last_sequence():
+    """A packed stream padded to a fixed token budget: the tokens behind the last sequence belong
+    to no sequence. Their output and gradient rows are cleared (no kernel writes them), and what
+    they hold on input does not reach the rows of real tokens."""
+    lens, pad = [70, 190, 33], 150
+    Hq, Hk, hd = 8, 4, 128
+    q, k, v, cu, plan = _make(lens, Hq, Hk, hd, seed=5)
+    T = sum(lens)
+    big = lambda h: (torch.randn(pad, h, hd, device="cuda") * 50).to(torch.bfloat16)  # noqa: E731
+    qp, kp, vp = (torch.cat([t, big(t.shape[1])]).requires_grad_() for t in (q, k, v))
+    plan_p = AttnPlan(cu, max(lens), T + pad)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    o = varlen_attention(q, k, v, plan, True)
+    g = torch.randn_like(o)
+    o.backward(g)
+    # poison the allocator's free blocks so that "never written" shows up as garbage
+    junk = torch.full((T + pad, Hq, hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    del junk
+    op = varlen_attention(qp, kp, vp, plan_p, True)
+    op.backward(torch.cat([g, torch.zeros(pad, Hq, hd, device="cuda", dtype=g.dtype)]))
+    nv.check_status()
+    assert torch.equal(op[:T], o) and not op[T:].any()
+    for a, b in ((qp.grad, q.grad), (kp.grad, k.grad), (vp.grad, v.grad)):
+        assert torch.equal(a[:T], b) and not a[T:].any()
