@@ -137,6 +137,9 @@ class DistributedSection:
     dp_size: int = 1
     tp_size: int = 1
     async_tp: bool = False  # sequence-parallel TP with collectives fused into the GEMMs (no torch.compile needed)
+    # extension: shard the layers' parameters and gradients over the data-parallel ranks as well
+    # (ZeRO-3; the default keeps a resident bf16 replica and shards gradients + optimizer state)
+    reshard_after_forward: bool = False
     max_restarts: int = 0  # extension: passed to the launcher; resume from the newest checkpoint
     step_timeout_s: float = 0.0  # extension: watchdog limit for one step (0 = off)
 

@@ -36,7 +36,7 @@ struct PeerPtrs {
 
 __global__ void __launch_bounds__(256)
     reduce_shard_kernel(PeerPtrs grads, int world, int rank, long long lo, long long n, float scale,
-                        float* __restrict__ out, float* __restrict__ sumsq_partial) {
+                        float* __restrict__ out, float* __restrict__ sumsq_partial, int accumulate) {
   __shared__ float sred[8];
   float ss = 0.f;
   const long long n4 = n / 4;
@@ -56,6 +56,13 @@ __global__ void __launch_bounds__(256)
     acc.y *= scale;
     acc.z *= scale;
     acc.w *= scale;
+    if (accumulate) {  // micro-steps of gradient accumulation add up in the shard
+      const float4 o = reinterpret_cast<const float4*>(out)[i];
+      acc.x += o.x;
+      acc.y += o.y;
+      acc.z += o.z;
+      acc.w += o.w;
+    }
     reinterpret_cast<float4*>(out)[i] = acc;
     ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
@@ -65,6 +72,7 @@ __global__ void __launch_bounds__(256)
       for (int k = 0; k < world; ++k)
         a += static_cast<const float*>(grads.p[(rank + k) % world])[lo + i];
       a *= scale;
+      if (accumulate) a += out[i];
       out[i] = a;
       ss += a * a;
     }
@@ -145,6 +153,20 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(AdamPushArgs a) {
   }
 }
 
+// dst[r * n16 + i] = shard of rank r (16-byte vectors), own shard first, then the peers in
+// rank-rotated order so that the ranks do not all read the same peer at the same time.
+__global__ void __launch_bounds__(256)
+    gather_shards_kernel(PeerPtrs shards, int world, int rank, long long n16, uint4* __restrict__ dst) {
+  for (int k = 0; k < world; ++k) {
+    const int p = (rank + k) % world;
+    const uint4* src = static_cast<const uint4*>(shards.p[p]);
+    uint4* out = dst + 1LL * p * n16;
+    for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+         i += 1LL * gridDim.x * blockDim.x)
+      out[i] = src[i];
+  }
+}
+
 int comm_grid(long long n4) {
   long long g = (n4 + 255) / 256;
   const long long cap = 1LL * row_num_sms() * 4;
@@ -161,18 +183,33 @@ extern "C" int lb_reduce_shard_partial_rows() { return row_num_sms() * 4; }
 
 // grad_ptrs: host array of `world` device pointers (fp32 full gradient buffers, own included).
 // out: fp32 [n]; sumsq: device scalar that receives += sum(out^2); scratch: partial_rows floats.
-// lo must be a multiple of 4 elements.
+// lo must be a multiple of 4 elements. accumulate: out += result (the sum of squares is then that of
+// the accumulated values).
 extern "C" int lb_reduce_shard_f32(const void* const* grad_ptrs, int world, int rank, long long lo,
                                    long long n, float scale, float* out, float* scratch,
-                                   float* sumsq, void* stream) {
+                                   float* sumsq, int accumulate, void* stream) {
   if (n <= 0) return 0;
   if (world < 1 || world > kMaxPeers || (lo & 3)) return -3;
   PeerPtrs pp;
   for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(grad_ptrs[i]);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = comm_grid(n / 4);
-  reduce_shard_kernel<<<grid, 256, 0, st>>>(pp, world, rank, lo, n, scale, out, scratch);
+  reduce_shard_kernel<<<grid, 256, 0, st>>>(pp, world, rank, lo, n, scale, out, scratch, accumulate);
   if (sumsq != nullptr) sumsq_fold_kernel<<<1, 256, 0, st>>>(scratch, grid, sumsq);
+  return launch_rc();
+}
+
+// Parameter all-gather over peer memory (sharded-parameter mode): every rank holds one shard of
+// `bytes` bytes (a multiple of 16) in symmetric memory; dst receives all of them in rank order.
+// Plain peer loads; the caller orders "shards final on every rank" before this launch.
+extern "C" int lb_gather_shards(const void* const* shard_ptrs, int world, int rank, long long bytes,
+                                void* dst, void* stream) {
+  if (bytes <= 0) return 0;
+  if (world < 1 || world > kMaxPeers || (bytes & 15)) return -3;
+  PeerPtrs pp;
+  for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(shard_ptrs[i]);
+  gather_shards_kernel<<<comm_grid(bytes / 16), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pp, world, rank, bytes / 16, static_cast<uint4*>(dst));
   return launch_rc();
 }
 

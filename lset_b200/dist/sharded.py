@@ -13,8 +13,16 @@ compute parameters, fp32 gradient reduction and fp32 optimizer state) built for 
   reduction only happens on the boundary micro-step;
 * step: global-norm clipping with the coefficient kept on the device, one fused AdamW kernel per
   group that also writes the new bf16 shard, then an all-gather of the shards that the next
-  forward waits for per layer. With 180 GB per GPU the bf16 replica stays resident (no re-gather
-  in backward); ``reshard_after_forward`` is accepted for interface parity and ignored.
+  forward waits for per layer. With 180 GB per GPU the bf16 replica stays resident by default (no
+  re-gather in backward).
+* ``reshard_after_forward=True`` selects the parameter-sharded mode (ZeRO-3, what the reference's
+  ``fully_shard`` does per layer, lset/distributed/parallel.py:129-160): a layer group keeps only
+  its 1/W bf16 shard; the full parameters of a layer live in one of two rotating buffers, gathered
+  (peer loads over NVLink, or NCCL) on the side stream one layer ahead of the forward and again one
+  layer ahead of the backward; the layer's fp32 gradients are written into one of two rotating
+  buffers and reduced into the 1/W gradient shard as soon as its backward is done. Parameter,
+  gradient and optimizer memory of the layers then fall with the data-parallel size. The root
+  group (embeddings, final norm) stays resident.
 
 Collectives go through ``torch.distributed`` (NCCL on GPUs, gloo on CPU for tests) unless the
 symmetric-memory kernels of ``lset_b200.dist.symm`` are enabled, which fuse the gradient
@@ -44,8 +52,14 @@ class FlatGroup:
     """One communication / optimizer unit: the trainable parameters of a set of modules."""
 
     def __init__(self, name: str, params: Sequence[nn.Parameter], world: int, rank: int,
-                 compute_dtype: torch.dtype, device: torch.device, group=None, use_symm: bool = False):
+                 compute_dtype: torch.dtype, device: torch.device, group=None, use_symm: bool = False,
+                 shard_params: bool = False):
         self.name = name
+        # parameter-sharded mode: only the 1/W slice of parameters and gradients is kept here; the
+        # store binds the parameters to a rotating full buffer while the layer runs
+        self.sharded = bool(shard_params) and world > 1
+        self.pslot = self.gslot = None
+        self.has_grad = False
         self.params = list(params)
         self.world, self.rank = world, rank
         offs, n = [], 0
@@ -63,7 +77,24 @@ class FlatGroup:
         full_master = torch.zeros(self.numel, dtype=torch.float32, device=device)
         for p, o in zip(self.params, offs):
             full_master[o:o + p.numel()] = p.data.detach().reshape(-1).to(device, torch.float32)
-        self.symm_param = self.symm_grad = None
+        self.symm_param = self.symm_grad = self.symm_shard = None
+        if self.sharded:
+            if use_symm and compute_dtype == torch.bfloat16:
+                from . import symm
+
+                self.symm_shard = symm.try_alloc(self.shard_numel, compute_dtype, device, group)
+            self.param_shard = (self.symm_shard.local if self.symm_shard is not None else
+                                torch.empty(self.shard_numel, dtype=compute_dtype, device=device))
+            self.param_shard.copy_(full_master[self.lo:self.hi].to(compute_dtype))
+            self.flat_param = self.flat_grad = None
+            self.master = full_master[self.lo:self.hi].clone()
+            del full_master
+            self.exp_avg = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.exp_avg_sq = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+            self.reduce_event = self.gather_event = None
+            self.reduced = False
+            return
         if use_symm and compute_dtype == torch.bfloat16:
             from . import symm
 
@@ -98,8 +129,21 @@ class FlatGroup:
         fp32 accumulator."""
         for p in self.params:
             if p.grad is not None:
-                p.main_grad.add_(p.grad.to(torch.float32))
+                if getattr(p, "main_grad", None) is not None:
+                    p.main_grad.add_(p.grad.to(torch.float32))
                 p.grad = None
+
+    def bind_params(self, buf: torch.Tensor) -> None:
+        """Point the parameters at their places in a full bf16 buffer."""
+        for p, o in zip(self.params, self.offsets):
+            n = p.numel()
+            p.data = buf[o:o + n].view(p.shape)
+
+    def bind_grads(self, buf: torch.Tensor) -> None:
+        for p, o in zip(self.params, self.offsets):
+            n = p.numel()
+            p.main_grad = buf[o:o + n].view(p.shape)
+            register_main_grad(p)
 
 
 class ParamStore:
@@ -124,6 +168,14 @@ class ParamStore:
         from . import symm as _symm
 
         self.use_symm = _symm.enabled(self.world, self.device)
+        self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+        # parameter-sharded mode: layer groups only, every parameter trainable (module backward
+        # hooks drive the gathers; a frozen first layer would not fire them), no tensor parallelism
+        frozen = any(not p.requires_grad for p in module.parameters())
+        self.zero3 = bool(reshard_after_forward) and self.world > 1 and self.tp_world == 1 and not frozen
+        if reshard_after_forward and self.world > 1 and not self.zero3:
+            print("[lset_b200] reshard_after_forward needs tp_size == 1 and no frozen parameters; "
+                  "keeping the resident-replica mode", flush=True)
         self.groups: List[FlatGroup] = []
         claimed = set()
         layers = list(layer_modules) if layer_modules is not None else list(getattr(module, "layers", []))
@@ -142,7 +194,8 @@ class ParamStore:
                 sel = [p for p in ps if kind(p) == tag]
                 if sel:
                     g = FlatGroup(name + tag, sel, self.world, self.rank, compute_dtype, self.device,
-                                  dp_group, self.use_symm)
+                                  dp_group, self.use_symm,
+                                  shard_params=self.zero3 and name != "root")
                     g.tp_sharded = tag == ".tp"
                     # replicated parameter whose per-rank gradient is only a part of the total
                     # (per-head norm weights; everything token-sharded under sequence parallelism)
@@ -160,7 +213,8 @@ class ParamStore:
         rest = [p for p in module.parameters() if p.requires_grad and id(p) not in claimed]
         if rest:
             self.groups.extend(make_groups("root", rest))
-        self.use_symm = self.use_symm and all(g.symm_grad is not None for g in self.groups)
+        self.use_symm = self.use_symm and all(
+            (g.symm_shard if g.sharded else g.symm_grad) is not None for g in self.groups)
         # squared norm of the reduced shards: [0] replicated parameters, [1] tensor-parallel shards
         self.sumsq = torch.zeros(2, dtype=torch.float32, device=self.device)
         # frozen parameters and buffers: just move / cast, they stay replicated
@@ -172,25 +226,168 @@ class ParamStore:
         self.overlap = overlap and self.device.type == "cuda" and self.world > 1
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
         self._hooks = []
-        self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+        if self.zero3:
+            self._init_pools()
         if self.world > 1 or self.tp_world > 1:
             self._install_hooks()
+
+    # ------------------------------------------------------------------ parameter-sharded mode
+    def _init_pools(self) -> None:
+        """Two rotating full-size buffers for parameters and two for gradients (the largest layer
+        group sets their size). The gradient buffers are read by the peers' reduce kernels, so
+        they are symmetric allocations when the peer-memory path is on."""
+        sharded = [g for g in self.groups if g.sharded]
+        n = max(g.numel for g in sharded)
+        self._pbuf = [torch.empty(n, dtype=self.compute_dtype, device=self.device) for _ in range(2)]
+        self._pfree = [None, None]       # event after which a parameter buffer may be overwritten
+        self._powner = [None, None]      # group whose parameters the buffer holds (valid contents)
+        self._gsymm = [None, None]
+        if self.use_symm:
+            from . import symm as _symm
+
+            self._gsymm = [_symm.try_alloc(n, torch.float32, self.device, self.dp_group)
+                           for _ in range(2)]
+            if any(b is None for b in self._gsymm):
+                self.use_symm = False
+        self._gbuf = [b.local if (self.use_symm and b is not None) else
+                      torch.zeros(n, dtype=torch.float32, device=self.device) for b in self._gsymm]
+        self._gfree = [None, None]
+        self._gowner = [None, None]
+        self._order = {id(g): i for i, g in enumerate(sharded)}
+        self._sharded = sharded
+        for g in sharded:                # valid shapes from the start; contents arrive with a gather
+            g.bind_params(self._pbuf[0])
+            for p in g.params:
+                p.main_grad = None
+                p.grad = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.dp_group)   # every rank's shards are in place before any gather
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+
+    def _materialize(self, g: FlatGroup, wait: bool = True) -> None:
+        """Make the full parameters of a sharded group available: reuse a buffer that still holds
+        them, or gather the shards of all ranks into a free one on the side stream. ``wait`` makes
+        the current stream wait for the gather (a prefetch passes False)."""
+        if g.pslot is None:
+            slot = next((i for i in range(2) if self._powner[i] is g), None)
+            if slot is None:
+                busy = {x.pslot for x in self._sharded if x.pslot is not None}
+                slot = next((i for i in range(2) if i not in busy), None)
+                if slot is None:
+                    return                      # both buffers in use: gathered on demand later
+                self._gather_into(g, slot)
+            g.pslot = slot
+            self._powner[slot] = g
+            g.bind_params(self._pbuf[slot])
+        if wait and g.gather_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(g.gather_event)
+            g.gather_event = None
+
+    def _gather_into(self, g: FlatGroup, slot: int) -> None:
+        dst = self._pbuf[slot][:g.numel]
+        cur = self._stream()
+        side = self.comm_stream
+        if side is not None:
+            side.wait_stream(cur)
+            if self._pfree[slot] is not None:
+                side.wait_event(self._pfree[slot])
+        ctx = torch.cuda.stream(side) if side is not None else _null_context()
+        with ctx:
+            if self.use_symm:
+                rc = nv.load().lb_gather_shards(
+                    g.symm_shard.c_ptr_array(), nv.c_int(self.world), nv.c_int(self.rank),
+                    nv.c_ll(g.shard_numel * g.param_shard.element_size()),
+                    nv.c_void_p(dst.data_ptr()), nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_gather_shards")
+                nv.count_launch()
+            elif dst.is_cuda:
+                dist.all_gather_into_tensor(dst, g.param_shard, group=self.dp_group)
+            else:
+                parts = [torch.empty_like(g.param_shard) for _ in range(self.world)]
+                dist.all_gather(parts, g.param_shard, group=self.dp_group)
+                dst.copy_(torch.cat(parts))
+            if side is not None:
+                g.gather_event = torch.cuda.Event()
+                g.gather_event.record(side)
+        self._pfree[slot] = None
+
+    def _release_params(self, g: FlatGroup) -> None:
+        """The layer is done with its parameters: the buffer may be reused once the work queued so
+        far has run (its contents stay valid until then and are reused if nobody took it)."""
+        if g.pslot is None:
+            return
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._pfree[g.pslot] = ev
+        g.pslot = None
+
+    def _acquire_grads(self, g: FlatGroup) -> None:
+        """Bind a zeroed full gradient buffer to the group for its backward."""
+        if g.gslot is not None:
+            return
+        busy = {x.gslot for x in self._sharded if x.gslot is not None}
+        slot = next((i for i in range(2) if i not in busy), None)
+        if slot is None:
+            raise RuntimeError("parameter-sharded mode: more than two layers in backward at once")
+        if self._gfree[slot] is not None and self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).wait_event(self._gfree[slot])
+            self._gfree[slot] = None
+        buf = self._gbuf[slot][:g.numel]
+        buf.zero_()
+        g.gslot = slot
+        g.reduced = False
+        g.bind_grads(buf)
+
+    def _neighbour(self, g: FlatGroup, step: int) -> Optional[FlatGroup]:
+        i = self._order[id(g)] + step
+        return self._sharded[i] if 0 <= i < len(self._sharded) else None
 
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self) -> None:
         for layer, gs in self._groups_of_layer:
 
             def after_backward(_mod, _gin, _gout, gs=gs):
-                if self.requires_gradient_sync:
-                    for g in gs:
+                for g in gs:
+                    # sharded groups reduce on every micro-step (their full gradient buffer is
+                    # handed on to the next layer); resident ones only on the boundary step
+                    if g.sharded or self.requires_gradient_sync:
                         self._reduce_group(g)
+                    if g.sharded:
+                        self._release_params(g)
 
             def before_forward(_mod, _args, gs=gs):
                 for g in gs:
-                    self._wait_gather(g)
+                    if g.sharded:
+                        self._materialize(g)
+                        nxt = self._neighbour(g, +1)
+                        if nxt is not None:
+                            self._materialize(nxt, wait=False)   # next layer, one layer ahead
+                    else:
+                        self._wait_gather(g)
+
+            def after_forward(_mod, _args, _out, gs=gs):
+                for g in gs:
+                    if g.sharded:
+                        self._release_params(g)
+
+            def before_backward(_mod, _gout, gs=gs):
+                for g in gs:
+                    if g.sharded:
+                        self._materialize(g)
+                        self._acquire_grads(g)
+                        prv = self._neighbour(g, -1)
+                        if prv is not None:
+                            self._materialize(prv, wait=False)
 
             self._hooks.append(layer.register_full_backward_hook(after_backward))
             self._hooks.append(layer.register_forward_pre_hook(before_forward))
+            if any(g.sharded for g in gs):
+                self._hooks.append(layer.register_forward_hook(after_forward))
+                self._hooks.append(layer.register_full_backward_pre_hook(before_backward))
 
     def set_requires_gradient_sync(self, flag: bool) -> None:
         """False on non-boundary micro-steps of gradient accumulation (gradients only accumulate)."""
@@ -201,6 +398,9 @@ class ParamStore:
         if g.reduced:
             return
         g.collect_autograd_grads()
+        if g.sharded:
+            self._reduce_sharded(g)
+            return
         if getattr(g, "tp_partial", False) and self.tp_world > 1:
             dist.all_reduce(g.flat_grad, op=dist.ReduceOp.SUM, group=self.tp_group)
         if self.world == 1:
@@ -216,6 +416,51 @@ class ParamStore:
             self._reduce_scatter(g)
         g.reduced = True
 
+    def _reduce_sharded(self, g: FlatGroup) -> None:
+        """Reduce the group's full gradient buffer into its 1/W shard (averaged, added to what
+        earlier micro-steps left there) and hand the buffer back."""
+        if g.gslot is None:
+            return
+        slot = g.gslot
+        buf = self._gbuf[slot][:g.numel]
+        side = self.comm_stream
+        if side is not None:
+            side.wait_stream(torch.cuda.current_stream(self.device))
+        ctx = torch.cuda.stream(side) if side is not None else _null_context()
+        with ctx:
+            if self.use_symm:
+                # every rank's buffer complete before anyone reads it; everyone done reading before
+                # anyone zeroes it for another layer
+                self._barrier("reduce").sync()
+                lib = nv.load()
+                scr = scratch("reduce_shard", lib.lb_reduce_shard_partial_rows(), self.device)
+                rc = lib.lb_reduce_shard_f32(
+                    self._gsymm[slot].c_ptr_array(), nv.c_int(self.world), nv.c_int(self.rank),
+                    nv.c_ll(g.lo), nv.c_ll(g.shard_numel), nv.c_float(1.0 / self.world),
+                    nv.c_void_p(g.grad_shard.data_ptr()), nv.c_void_p(scr.data_ptr()),
+                    nv.c_void_p(0), nv.c_int(int(g.has_grad)), nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_reduce_shard_f32")
+                nv.count_launch()
+                self._barrier("reduce_done").sync()
+            elif buf.is_cuda:
+                tmp = torch.empty_like(g.grad_shard)
+                dist.reduce_scatter_tensor(tmp, buf, op=dist.ReduceOp.AVG, group=self.dp_group)
+                g.grad_shard.add_(tmp) if g.has_grad else g.grad_shard.copy_(tmp)
+            else:
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.dp_group)
+                part = buf[g.lo:g.hi] / self.world
+                g.grad_shard.add_(part) if g.has_grad else g.grad_shard.copy_(part)
+            if side is not None:
+                ev = torch.cuda.Event()
+                ev.record(side)
+                g.reduce_event = ev
+                self._gfree[slot] = ev
+        g.has_grad = True
+        g.gslot = None
+        g.reduced = True
+        for p in g.params:
+            p.main_grad = None
+
     def _reduce_scatter(self, g: FlatGroup) -> None:
         if self.use_symm:
             # All ranks' gradients for this group must be complete before anyone reads them: a
@@ -227,10 +472,11 @@ class ParamStore:
                 g.symm_grad.c_ptr_array(), nv.c_int(self.world), nv.c_int(self.rank), nv.c_ll(g.lo),
                 nv.c_ll(g.shard_numel), nv.c_float(1.0 / self.world),
                 nv.c_void_p(g.grad_shard.data_ptr()), nv.c_void_p(scr.data_ptr()),
-                nv.c_void_p(self.sumsq.data_ptr() + (4 if getattr(g, "tp_sharded", False) else 0)),
-                nv.c_void_p(nv.stream_ptr()))
+                nv.c_void_p(0 if self.zero3 else
+                            self.sumsq.data_ptr() + (4 if getattr(g, "tp_sharded", False) else 0)),
+                nv.c_int(0), nv.c_void_p(nv.stream_ptr()))
             nv.check_rc(rc, "lb_reduce_shard_f32")
-            nv.count_launch(2)
+            nv.count_launch(1 if self.zero3 else 2)
             return
         if g.flat_grad.is_cuda:
             dist.reduce_scatter_tensor(g.grad_shard, g.flat_grad, op=dist.ReduceOp.AVG,
@@ -262,6 +508,11 @@ class ParamStore:
         if not self.requires_gradient_sync:
             return
         for g in reversed(self.groups):
+            if g.sharded:
+                if g.gslot is not None:       # backward reached the layer but not its input
+                    self._reduce_group(g)
+                    self._release_params(g)
+                continue
             if not g.reduced:
                 self._reduce_group(g)
 
@@ -275,13 +526,18 @@ class ParamStore:
         """All-gather the updated bf16 shards (after an optimizer step)."""
         if self.world == 1:
             return
+        if self.zero3:
+            self._powner = [None, None]     # the gathered copies are stale now
         if self.use_symm:
             # adamw_push already stored the new shards into every rank's buffer; one barrier
-            # orders "all pushes done" before the next forward on every rank.
+            # orders "all pushes done" (and, in the parameter-sharded mode, "all shards updated")
+            # before the next forward on every rank.
             self._barrier("gather").sync()
             return
         hooked = {id(g) for _, gs in self._groups_of_layer for g in gs}
         for g in self.groups:
+            if g.sharded:
+                continue                    # gathered layer by layer in the next forward
             if self.comm_stream is not None:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(self.comm_stream):
@@ -311,9 +567,28 @@ class ParamStore:
     # ------------------------------------------------------------------ utilities
     def zero_grad(self) -> None:
         for g in self.groups:
-            g.flat_grad.zero_()
+            if g.sharded:
+                g.has_grad = False          # the next reduction overwrites the shard
+            else:
+                g.flat_grad.zero_()
             g.reduced = False
         self.sumsq.zero_()
+
+    def memory_report(self) -> dict:
+        """Bytes this rank holds for trainable parameters, gradients and optimizer state."""
+        nb = lambda t: t.numel() * t.element_size()  # noqa: E731
+        rep = {"param_bytes": 0, "grad_bytes": 0, "optim_bytes": 0, "pool_bytes": 0,
+               "sharded_groups": sum(1 for g in self.groups if g.sharded), "world": self.world}
+        for g in self.groups:
+            rep["param_bytes"] += nb(g.param_shard) if g.sharded else nb(g.flat_param)
+            if not g.sharded:
+                rep["grad_bytes"] += nb(g.flat_grad)
+            if g.sharded or g.grad_shard is not g.flat_grad:
+                rep["grad_bytes"] += nb(g.grad_shard)
+            rep["optim_bytes"] += nb(g.master) + nb(g.exp_avg) + nb(g.exp_avg_sq)
+        if self.zero3:
+            rep["pool_bytes"] = sum(nb(b) for b in self._pbuf) + sum(nb(b) for b in self._gbuf)
+        return rep
 
     def trainable_parameters(self):
         for g in self.groups:
@@ -366,8 +641,17 @@ class ParamStore:
                 if t is not None:
                     full[o:o + p.numel()] = t.reshape(-1).to(self.device, torch.float32)
             g.master.copy_(full[g.lo:g.hi])
-            g.flat_param.copy_(full.to(self.compute_dtype))
+            if g.sharded:
+                g.param_shard.copy_(full[g.lo:g.hi].to(self.compute_dtype))
+            else:
+                g.flat_param.copy_(full.to(self.compute_dtype))
+        if self.zero3:
+            self._powner = [None, None]
 
+
+import contextlib as _contextlib
+
+_null_context = _contextlib.nullcontext
 
 _HAS_FUSED_CPU_ADAMW = hasattr(torch, "_fused_adamw_")
 
@@ -413,7 +697,7 @@ class ShardedAdamW:
         native = st.device.type == "cuda"
         parts = self._parts
         parts.zero_()
-        if st.use_symm:
+        if st.use_symm and not st.zero3:
             parts.copy_(st.sumsq)  # accumulated by the reduce kernels
         else:
             for g in st.groups:
@@ -467,8 +751,8 @@ class ShardedAdamW:
             self._coef[0] = torch.clamp(self.grad_clip / (norm[0] + 1e-6), max=1.0) \
                 if self.grad_clip > 0 else 1.0
         for g in st.groups:
-            pshard = g.flat_param[g.lo:g.hi]
-            if st.use_symm:
+            pshard = g.param_shard if g.sharded else g.flat_param[g.lo:g.hi]
+            if st.use_symm and not g.sharded:
                 rc = nv.load().lb_adamw_push(
                     nv.c_void_p(g.master.data_ptr()), nv.c_void_p(g.grad_shard.data_ptr()),
                     nv.c_void_p(g.exp_avg.data_ptr()), nv.c_void_p(g.exp_avg_sq.data_ptr()),

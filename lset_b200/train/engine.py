@@ -114,7 +114,7 @@ class TrainingEngine:
                  step_timeout_s: float = 0.0, device: Optional[str] = None, seed: int = 42,
                  max_seq_length: int = 512, tokenizer=None, num_workers: int = 0,
                  jsonl_log: bool = False, init_std: float = 0.02, init_on_device: bool = False,
-                 max_inflight_steps: int = 2):
+                 max_inflight_steps: int = 2, reshard_after_forward: bool = False):
         if cuda_graph:
             from .cuda_graph import validate_cuda_graph_config
 
@@ -233,7 +233,8 @@ class TrainingEngine:
         # ---------------------------------------------------------------- sharded runtime + optimizer
         self.store = ParamStore(model, dp_group=self.dp_group if world > 1 else None,
                                 compute_dtype=self.compute_dtype, device=self.device,
-                                tp_group=self.tp_group)
+                                tp_group=self.tp_group,
+                                reshard_after_forward=reshard_after_forward)
         if self.task.logit_scale is not None:
             self.task_store = ParamStore(self.task, layer_modules=[], dp_group=None,
                                          compute_dtype=torch.float32, device=self.device)

@@ -40,7 +40,7 @@ def engine_kwargs(config: LSETConfig, max_steps: int) -> dict:
         cascade_d_small=t.cascade_d_small, cascade_K_prime=t.cascade_K_prime,
         activation_checkpoint=config.activation_checkpoint.enabled,
         ac_mode=config.activation_checkpoint.mode, ac_ratio=config.activation_checkpoint.ratio,
-        async_tp=d.async_tp, pooling=config.model.pooling, padding_side=config.model.padding_side,
+        async_tp=d.async_tp, reshard_after_forward=d.reshard_after_forward, pooling=config.model.pooling, padding_side=config.model.padding_side,
         fused_projections=config.model.fused_projections, length_sorted=config.data.length_sorted,
         learnable_temperature=t.learnable_temperature, weight_decay=t.weight_decay,
         step_timeout_s=d.step_timeout_s, seed=t.seed, max_seq_length=config.data.max_seq_length,

@@ -83,8 +83,10 @@ def main():
     from lset_b200.models.layers import init_normal_
     from lset_b200.models.parallel_plan import decoder_tp_plan
 
+    # whole heads per rank at every world size
     cfg = Qwen3Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                      num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+                      num_attention_heads=max(4, 2 * world), num_key_value_heads=max(2, world),
+                      head_dim=64)
     torch.manual_seed(0)
     ref = Qwen3Decoder(cfg, fused_projections=True)
     init_normal_(ref, 0.05)

@@ -36,7 +36,6 @@ def main():
         losses.append(float(global_loss_value(loss, eng.dp_group)))
         norms.append(float(eng.optimizer.grad_norm()))
     nv.check_status()
-    eng.store.wait_all_gathers()
     torch.cuda.synchronize()
     fp = [float(g.flat_param.float().double().sum()) for g in eng.store.groups]
     fp2 = [float(g.flat_param.float().double().pow(2).sum()) for g in eng.store.groups]

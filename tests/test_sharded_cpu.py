@@ -4,6 +4,7 @@ import os
 import socket
 import tempfile
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -89,3 +90,51 @@ def test_two_ranks_match_single_process():
     rt = got["roundtrip"]
     assert rt["step"] == 1 and rt["moved"] > 1e-4 and rt["back"] < 1e-6 and rt["m_back"] < 1e-7, rt
     assert rt["steps_seen"] == 1        # the optimizer's step counter came back with the state
+
+
+def _zero3_worker(rank, world, port, out_dir, zero3):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = _engine(world, reshard_after_forward=zero3, gradient_accumulation_steps=2)
+    losses = []
+    for s in range(4):                      # two optimizer steps of two micro-steps each
+        lo = (s % 2) * 8 + rank * 4
+        loss = eng.train_step(_batch(lo, lo + 4)).clone()
+        dist.all_reduce(loss)
+        losses.append(float(loss))
+    masters = {n: t.clone() for n, t in eng.store.named_master_tensors()}
+    # evaluation forward after training: the layers gather their parameters on demand
+    with torch.no_grad():
+        b = _batch(0, 4)["query"]
+        hid = eng.model.forward_packed(b["input_ids"], b["position_ids"], b["cu_seqlens"],
+                                       b["max_seqlen"])["hidden_states"].clone()
+    if rank == 0:
+        torch.save({"losses": losses, "masters": masters, "hidden": hid,
+                    "memory": eng.store.memory_report(), "zero3": eng.store.zero3},
+                   os.path.join(out_dir, f"z{int(zero3)}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_parameter_sharded_mode_matches_resident_mode():
+    """``reshard_after_forward`` (layers keep 1/W of parameters and gradients; full copies live in
+    rotating buffers gathered per layer) trains exactly like the resident-replica mode, gradient
+    accumulation included, and holds about half the layer state per rank at two ranks."""
+    out_dir = tempfile.mkdtemp()
+    for zero3 in (False, True):
+        mp.spawn(_zero3_worker, args=(2, _free_port(), out_dir, zero3), nprocs=2, join=True)
+    a = torch.load(os.path.join(out_dir, "z0.pt"), weights_only=False)
+    b = torch.load(os.path.join(out_dir, "z1.pt"), weights_only=False)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        os.environ.pop(k, None)
+    assert not a["zero3"] and b["zero3"]
+    assert a["losses"] == pytest.approx(b["losses"], abs=1e-5)
+    for n, t in a["masters"].items():
+        assert torch.allclose(t, b["masters"][n], atol=1e-6), n
+    assert torch.allclose(a["hidden"], b["hidden"], atol=1e-5)
+    ma, mb = a["memory"], b["memory"]
+    assert mb["sharded_groups"] == 2 and ma["sharded_groups"] == 0
+    # the root group (embeddings) stays resident in both; everything else halves
+    assert mb["param_bytes"] < ma["param_bytes"] and mb["grad_bytes"] < ma["grad_bytes"]
+    assert mb["optim_bytes"] == ma["optim_bytes"]
