@@ -932,8 +932,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   const int tiles_n = (N + bn - 1) / bn;
   const int kb_total = (K + BK - 1) / BK;
   if (splits == 0)
-    splits = (out_fp32 && accumulate && !scatter)
-                 ? auto_splits(1LL * tiles_m * tiles_n, kb_total, sms) : 1;
+    splits = (out_fp32 && accumulate) ? auto_splits(1LL * tiles_m * tiles_n, kb_total, sms) : 1;
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   int kb_per = (kb_total + splits - 1) / splits;

@@ -4,9 +4,11 @@ Forward: each rank publishes its passage embeddings in a symmetric buffer; one k
 peers' rows over NVLink (two extra warps per CTA) into a local ``[W * B, D]`` buffer while the
 tcgen05 tiles of ``Q · Kᵀ`` consume them in pull order with an online logsumexp — the all-gather is
 fused into the similarity GEMM, and no score matrix is written. Backward: the softmax gradient is
-recomputed as a bf16 ``W``, ``dQ = W · K`` stays local, and ``dK = Wᵀ · Q`` is produced by a GEMM
-whose epilogue adds every row straight into its *owner's* fp32 buffer with ``red.global.add`` over
-NVLink — the reduce-scatter is fused into the GEMM.
+recomputed as a bf16 ``W`` one column panel at a time (a panel never spans two ranks' passages and
+is capped at 64 MB), ``dQ`` accumulates ``W · K`` over the panels locally,
+and each panel's ``dK = Wᵀ · Q`` is produced by a GEMM whose epilogue adds every row straight into
+its *owner's* fp32 buffer with ``red.global.add`` over NVLink — the reduce-scatter is fused into
+the GEMM.
 
 Ranks are ordered with two device barriers per step (passages published and accumulators cleared;
 all dK contributions landed): one-warp kernels with a bounded wait on flags in symmetric memory,
@@ -111,27 +113,46 @@ class _CrossRankInfoNCE(torch.autograd.Function):
         N = W * n_local
         lib = nv.load()
         coef = (g.float() * (inv_t / float(W * B))).reshape(1).contiguous()
+        from ..ops.loss import panel_cols
+
         Bp = (B + 7) // 8 * 8
-        Wm = torch.empty(Bp, N, dtype=torch.bfloat16, device=q.device)
+        step = min(n_local, panel_cols(B, N))
+        Wm = torch.empty(Bp, step, dtype=torch.bfloat16, device=q.device)
         if Bp != B:
             Wm[B:].zero_()
-        rc = lib.lb_infonce_pgrad(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(buf.k_all.data_ptr()),
-            nv.c_ll(D), nv.c_int(B), nv.c_int(N), nv.c_int(D), nv.c_float(inv_t),
-            nv.c_ll(rank * n_local), nv.c_void_p(lse.data_ptr()), nv.c_void_p(coef.data_ptr()),
-            nv.c_void_p(Wm.data_ptr()), nv.c_ll(N), nv.c_void_p(nv.status_word(q.device).data_ptr()),
-            nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_infonce_pgrad")
-        dq = matmul_abt(Wm[:B], buf.k_all, b_mn=True)
-        # dK: every rank adds its contribution into the owners' buffers (cleared in forward)
         qp = q if Bp == B else torch.cat([q, q.new_zeros(Bp - B, D)])
-        rc = lib.lb_gemm_bf16_scatter(
-            nv.c_void_p(Wm.data_ptr()), nv.c_void_p(qp.data_ptr()), buf.dk_sym.c_ptr_array(),
-            nv.c_int(W), nv.c_int(n_local), nv.c_int(N), nv.c_int(D), nv.c_int(Bp), nv.c_ll(N),
-            nv.c_ll(D), nv.c_ll(D), nv.c_int(1), nv.c_int(1), nv.c_int(1), nv.c_int(0),
-            nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_gemm_bf16_scatter")
-        nv.count_launch(2)
+        status = nv.status_word(q.device).data_ptr()
+        dq32 = None
+        for pk in range(W):
+            peer = (rank + pk) % W                    # own passages first, then the peers in turn
+            for s0 in range(0, n_local, step):
+                n = min(step, n_local - s0)
+                c0 = peer * n_local + s0              # first global column of the panel
+                Wp = Wm if n == step else Wm[:, :n]
+                k_panel = buf.k_all[c0:c0 + n]
+                rc = lib.lb_infonce_pgrad(
+                    nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
+                    nv.c_void_p(k_panel.data_ptr()), nv.c_ll(D), nv.c_int(B), nv.c_int(n),
+                    nv.c_int(D), nv.c_float(inv_t), nv.c_ll(rank * n_local - c0),
+                    nv.c_void_p(lse.data_ptr()), nv.c_void_p(coef.data_ptr()),
+                    nv.c_void_p(Wp.data_ptr()), nv.c_ll(Wp.stride(0)), nv.c_void_p(status),
+                    nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_infonce_pgrad")
+                if dq32 is None:
+                    dq32 = matmul_abt(Wp[:B], k_panel, b_mn=True, out_dtype=torch.float32)
+                else:
+                    matmul_abt(Wp[:B], k_panel, b_mn=True, out=dq32, accumulate=True)
+                # dK of the panel: every rank adds its contribution into the owner's buffer
+                # (cleared in forward), rows s0 .. s0 + n of that rank's passages
+                owner = (ctypes.c_void_p * 1)(buf.dk_sym.peer_ptrs[peer] + 4 * s0 * D)
+                rc = lib.lb_gemm_bf16_scatter(
+                    nv.c_void_p(Wp.data_ptr()), nv.c_void_p(qp.data_ptr()), owner,
+                    nv.c_int(1), nv.c_int(n), nv.c_int(n), nv.c_int(D), nv.c_int(Bp),
+                    nv.c_ll(Wp.stride(0)), nv.c_ll(D), nv.c_ll(D), nv.c_int(1), nv.c_int(1),
+                    nv.c_int(0), nv.c_int(0), nv.c_void_p(status), nv.c_void_p(nv.stream_ptr()))
+                nv.check_rc(rc, "lb_gemm_bf16_scatter")
+                nv.count_launch(3)
+        dq = dq32.to(q.dtype)
         buf.order_ranks()                      # every contribution has landed
         dk = buf.dk_sym.local.view(n_local, D).to(torch.bfloat16)
         return dq, dk, None, None

@@ -48,6 +48,61 @@ def similarity(q: torch.Tensor, k: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------------------
+# Backward of the streaming losses in column panels.
+#
+# The probability gradient W = (softmax - target) * coef is needed as a bf16 operand of two more
+# products (dQ = W · K, dK = Wᵀ · Q). It is never held as a whole [Q, K] matrix: the passages are
+# walked in panels of columns, the panel's W is recomputed from the saved row LSE, dK of the panel
+# is complete after one product, and dQ accumulates over the panels in fp32. A panel's W is capped
+# at PANEL_BYTES (half of the 126 MB L2, so the two products that read it find it there); score
+# matrices below the cap take a single panel. Extra memory: the cap plus the fp32 accumulator of dQ.
+# ------------------------------------------------------------------------------------------------
+PANEL_BYTES = 64 << 20
+PANEL_MIN_COLS = 1024       # narrower panels leave the dK product too few tiles
+
+
+def panel_cols(M: int, N: int) -> int:
+    """Columns per panel for M query rows: as many as fit PANEL_BYTES of bf16, a multiple of 256
+    (the loss kernels' column tile; keeps label rows 16-byte aligned), at least PANEL_MIN_COLS."""
+    Mp = (M + 7) // 8 * 8
+    cols = max(PANEL_MIN_COLS, (PANEL_BYTES // (2 * Mp)) // 256 * 256)
+    return min(N, cols)
+
+
+def streamed_loss_backward(launch_pgrad, q, k, need_dq: bool, need_dk: bool):
+    """``launch_pgrad(c0, c1, W)`` fills ``W [Mp, c1 - c0]`` (bf16, rows past M zero) for the
+    passage columns ``[c0, c1)``. Returns ``(dq, dk)`` in the inputs' dtype."""
+    M, D = q.shape
+    N = k.shape[0]
+    Mp = (M + 7) // 8 * 8
+    step = panel_cols(M, N)
+    single = step >= N
+    qp = q if Mp == M else torch.cat([q, q.new_zeros(Mp - M, D)])
+    dq = dk = dq32 = None
+    if need_dk:
+        dk = torch.empty(N, D, dtype=k.dtype, device=k.device)
+    W = torch.empty(Mp, step, dtype=torch.bfloat16, device=q.device)
+    if Mp != M:
+        W[M:].zero_()
+    for c0 in range(0, N, step):
+        c1 = min(N, c0 + step)
+        Wp = W if c1 - c0 == step else W[:, :c1 - c0]
+        launch_pgrad(c0, c1, Wp)
+        if need_dq:
+            if single:
+                dq = matmul_abt(Wp[:M], k, b_mn=True)                       # [M, D] = W · K
+            elif dq32 is None:
+                dq32 = matmul_abt(Wp[:M], k[c0:c1], b_mn=True, out_dtype=torch.float32)
+            else:
+                matmul_abt(Wp[:M], k[c0:c1], b_mn=True, out=dq32, accumulate=True)
+        if need_dk:
+            matmul_abt(Wp, qp, a_mn=True, b_mn=True, out=dk[c0:c1])         # [n, D] = Wᵀ · Q
+    if need_dq and dq is None:
+        dq = dq32.to(q.dtype)
+    return dq, dk
+
+
+# ------------------------------------------------------------------------------------------------
 # Streaming InfoNCE: scores never materialise in fp32; see lb_infonce_fwd / lb_infonce_pgrad.
 # ------------------------------------------------------------------------------------------------
 class _FusedInfoNCE(torch.autograd.Function):
@@ -80,24 +135,23 @@ class _FusedInfoNCE(torch.autograd.Function):
         M, D = q.shape
         N = k.shape[0]
         coef = (g.float() * (inv_t / denom)).reshape(1).contiguous()
-        Mp = (M + 7) // 8 * 8
-        W = torch.empty(Mp, N, dtype=torch.bfloat16, device=q.device)
-        if Mp != M:
-            W[M:].zero_()
-        rc = nv.load().lb_infonce_pgrad(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
-            nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(N), nv.c_int(D), nv.c_float(inv_t),
-            nv.c_ll(target_offset), nv.c_void_p(lse.data_ptr()), nv.c_void_p(coef.data_ptr()),
-            nv.c_void_p(W.data_ptr()), nv.c_ll(N), nv.c_void_p(nv.status_word(q.device).data_ptr()),
-            nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_infonce_pgrad")
-        nv.count_launch()
-        dq = dk = None
-        if ctx.needs_input_grad[0]:
-            dq = matmul_abt(W[:M], k, b_mn=True)                                # [M, D] = W · K
-        if ctx.needs_input_grad[1]:
-            qp = q if Mp == M else torch.cat([q, q.new_zeros(Mp - M, D)])
-            dk = matmul_abt(W, qp, a_mn=True, b_mn=True)                        # [N, D] = Wᵀ · Q
+        lib = nv.load()
+        status = nv.status_word(q.device).data_ptr()
+
+        def pgrad(c0, c1, W):
+            # columns [c0, c1): the passages start at row c0, the target column moves by -c0
+            rc = lib.lb_infonce_pgrad(
+                nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
+                nv.c_void_p(k.data_ptr() + c0 * k.stride(0) * k.element_size()),
+                nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(c1 - c0), nv.c_int(D), nv.c_float(inv_t),
+                nv.c_ll(target_offset - c0), nv.c_void_p(lse.data_ptr()),
+                nv.c_void_p(coef.data_ptr()), nv.c_void_p(W.data_ptr()), nv.c_ll(W.stride(0)),
+                nv.c_void_p(status), nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_infonce_pgrad")
+            nv.count_launch()
+
+        dq, dk = streamed_loss_backward(pgrad, q, k, ctx.needs_input_grad[0],
+                                        ctx.needs_input_grad[1])
         return dq, dk, None, None, None
 
 
@@ -153,27 +207,26 @@ class _FusedLabelLoss(torch.autograd.Function):
         M, D = q.shape
         N = k.shape[0]
         coef = (g.float() * inv_t).reshape(1).contiguous()
-        Mp = (M + 7) // 8 * 8
-        W = torch.empty(Mp, N, dtype=torch.bfloat16, device=q.device)
-        if Mp != M:
-            W[M:].zero_()
-        rc = nv.load().lb_label_loss_pgrad(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
-            nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(N), nv.c_int(D), nv.c_float(inv_t),
-            nv.c_void_p(labels8.data_ptr()), nv.c_ll(labels8.stride(0)),
-            nv.c_void_p(tw.data_ptr() if tw is not None else None),
-            nv.c_ll(tw.stride(0) if tw is not None else 0), nv.c_void_p(row_scale.data_ptr()),
-            nv.c_void_p(row_w.data_ptr()), nv.c_int(0), nv.c_void_p(lse.data_ptr()),
-            nv.c_void_p(coef.data_ptr()), nv.c_void_p(W.data_ptr()), nv.c_ll(N),
-            nv.c_void_p(nv.status_word(q.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_label_loss_pgrad")
-        nv.count_launch()
-        dq = dk = None
-        if ctx.needs_input_grad[0]:
-            dq = matmul_abt(W[:M], k, b_mn=True)
-        if ctx.needs_input_grad[1]:
-            qp = q if Mp == M else torch.cat([q, q.new_zeros(Mp - M, D)])
-            dk = matmul_abt(W, qp, a_mn=True, b_mn=True)
+        lib = nv.load()
+        status = nv.status_word(q.device).data_ptr()
+
+        def pgrad(c0, c1, W):
+            # panel starts are multiples of 256 columns: the int8 label rows stay 16-byte aligned
+            rc = lib.lb_label_loss_pgrad(
+                nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
+                nv.c_void_p(k.data_ptr() + c0 * k.stride(0) * k.element_size()),
+                nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(c1 - c0), nv.c_int(D), nv.c_float(inv_t),
+                nv.c_void_p(labels8.data_ptr() + c0), nv.c_ll(labels8.stride(0)),
+                nv.c_void_p(tw.data_ptr() + 4 * c0 if tw is not None else None),
+                nv.c_ll(tw.stride(0) if tw is not None else 0), nv.c_void_p(row_scale.data_ptr()),
+                nv.c_void_p(row_w.data_ptr()), nv.c_int(0), nv.c_void_p(lse.data_ptr()),
+                nv.c_void_p(coef.data_ptr()), nv.c_void_p(W.data_ptr()), nv.c_ll(W.stride(0)),
+                nv.c_void_p(status), nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_label_loss_pgrad")
+            nv.count_launch()
+
+        dq, dk = streamed_loss_backward(pgrad, q, k, ctx.needs_input_grad[0],
+                                        ctx.needs_input_grad[1])
         return dq, dk, None, None, None, None, None
 
 
@@ -295,26 +348,24 @@ class _FusedMpNce(torch.autograd.Function):
         M, D = q.shape
         N = k.shape[0]
         coef = (g.float() * inv_t).reshape(1).contiguous()
-        Mp = (M + 7) // 8 * 8
-        W = torch.empty(Mp, N, dtype=torch.bfloat16, device=q.device)
-        if Mp != M:
-            W[M:].zero_()
-        rc = nv.load().lb_label_loss_pgrad(
-            nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(k.data_ptr()),
-            nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(N), nv.c_int(D), nv.c_float(inv_t),
-            nv.c_void_p(labels8.data_ptr()), nv.c_ll(labels8.stride(0)), nv.c_void_p(None),
-            nv.c_ll(0), nv.c_void_p(aux.data_ptr()), nv.c_void_p(row_w.data_ptr()), nv.c_int(1),
-            nv.c_void_p(neg_lse.data_ptr()), nv.c_void_p(coef.data_ptr()), nv.c_void_p(W.data_ptr()),
-            nv.c_ll(N), nv.c_void_p(nv.status_word(q.device).data_ptr()),
-            nv.c_void_p(nv.stream_ptr()))
-        nv.check_rc(rc, "lb_label_loss_pgrad")
-        nv.count_launch()
-        dq = dk = None
-        if ctx.needs_input_grad[0]:
-            dq = matmul_abt(W[:M], k, b_mn=True)
-        if ctx.needs_input_grad[1]:
-            qp = q if Mp == M else torch.cat([q, q.new_zeros(Mp - M, D)])
-            dk = matmul_abt(W, qp, a_mn=True, b_mn=True)
+        lib = nv.load()
+        status = nv.status_word(q.device).data_ptr()
+
+        def pgrad(c0, c1, W):
+            rc = lib.lb_label_loss_pgrad(
+                nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)),
+                nv.c_void_p(k.data_ptr() + c0 * k.stride(0) * k.element_size()),
+                nv.c_ll(k.stride(0)), nv.c_int(M), nv.c_int(c1 - c0), nv.c_int(D), nv.c_float(inv_t),
+                nv.c_void_p(labels8.data_ptr() + c0), nv.c_ll(labels8.stride(0)), nv.c_void_p(None),
+                nv.c_ll(0), nv.c_void_p(aux.data_ptr()), nv.c_void_p(row_w.data_ptr()), nv.c_int(1),
+                nv.c_void_p(neg_lse.data_ptr()), nv.c_void_p(coef.data_ptr()),
+                nv.c_void_p(W.data_ptr()), nv.c_ll(W.stride(0)), nv.c_void_p(status),
+                nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_label_loss_pgrad")
+            nv.count_launch()
+
+        dq, dk = streamed_loss_backward(pgrad, q, k, ctx.needs_input_grad[0],
+                                        ctx.needs_input_grad[1])
         return dq, dk, None, None, None, None
 
 

@@ -39,15 +39,31 @@ def test_similarity_grads():
     assert (q.grad.float() - ref_dq).abs().max() < 3e-2 * ref_dq.abs().max()
 
 
-def test_no_score_matrix_in_fp32():
-    M, N, D = 2048, 4096, 1024
-    q, k = _emb(M, D, 4).requires_grad_(), _emb(N, D, 5).requires_grad_()
+def _extra_bytes(fn, q, k):
+    """Peak memory of forward + backward beyond what was allocated before and the two gradient
+    tensors that remain afterwards."""
     torch.cuda.synchronize()
     torch.cuda.reset_peak_memory_stats()
     base = torch.cuda.memory_allocated()
-    fused_infonce(q, k, 0.02).backward()
+    fn().backward()
     torch.cuda.synchronize()
-    assert torch.cuda.max_memory_allocated() - base < M * N * 4  # below one fp32 score matrix
+    grads = sum(t.grad.numel() * t.grad.element_size() for t in (q, k))
+    return torch.cuda.max_memory_allocated() - base - grads
+
+
+def test_no_score_matrix_in_any_precision():
+    """The backward walks the passages in column panels: the bf16 probability gradient exists for
+    one panel (capped at 64 MB, here an eighth of the score matrix) at a time, next to the fp32
+    accumulator of dQ."""
+    M, N, D = 8192, 32768, 256
+    q, k = _emb(M, D, 4).requires_grad_(), _emb(N, D, 5).requires_grad_()
+    extra = _extra_bytes(lambda: fused_infonce(q, k, 0.02), q, k)
+    assert extra < M * N * 2 // 8 + M * D * 4 + (8 << 20), extra
+    # and the panelled backward still matches the oracle
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    torch.nn.functional.cross_entropy(qr @ kr.t() / 0.02, torch.arange(M, device="cuda")).backward()
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad)):
+        assert (a.float() - b).abs().max() < 3e-2 * (b.abs().max() + 1e-6)
 
 
 def _eager_label_loss(q, k, labels, T, scores=None):
@@ -106,15 +122,12 @@ def test_label_loss_dispatches_to_streaming_kernels():
     labels = torch.zeros(Q, K, device="cuda")
     labels[torch.arange(Q), torch.arange(Q)] = 1.0
     before = nv.launches()
-    torch.cuda.synchronize()
-    torch.cuda.reset_peak_memory_stats()
-    base = torch.cuda.memory_allocated()
-    contrastive_loss(q, k, labels, 0.02).backward()
-    torch.cuda.synchronize()
+    extra = _extra_bytes(lambda: contrastive_loss(q, k, labels, 0.02), q, k)
     assert nv.launches() > before
-    # int8 labels, masks and the bf16 probability gradient, but never fp32 score-sized temporaries
-    # (the eager formulation holds at least three of them)
-    assert torch.cuda.max_memory_allocated() - base < 2 * Q * K * 4
+    # int8 labels and masks derived from the label matrix ([Q, K] bytes each) and one column panel
+    # of the bf16 probability gradient, but no score-sized fp32 or bf16 temporary (the eager
+    # formulation holds at least three fp32 ones)
+    assert extra < 6 * Q * K + Q * K * 2 + Q * 256 * 4 + (4 << 20), extra
 
 
 def _eager_dense_loss(q, k, labels, scale, loss_type):
@@ -138,6 +151,45 @@ def _eager_dense_loss(q, k, labels, scale, loss_type):
     else:
         per_q = lsum * lse - (l * s).sum(1)
     return per_q[keep].sum() / keep.sum().clamp(min=1)
+
+
+@pytest.fixture
+def small_panels(monkeypatch):
+    """Makes the backward of the streaming losses walk several column panels at test sizes."""
+    from lset_b200.ops import loss as loss_ops
+
+    monkeypatch.setattr(loss_ops, "PANEL_BYTES", 256 * 1024)
+    monkeypatch.setattr(loss_ops, "PANEL_MIN_COLS", 256)
+
+
+def test_panelled_backward_of_infonce_and_label_losses(small_panels):
+    """Several panels, a ragged last one, a target offset: same gradients as one panel."""
+    from lset_b200.losses.contrastive import contrastive_loss
+    from lset_b200.ops import loss as loss_ops
+
+    M, N, D = 520, 1800, 256
+    assert loss_ops.panel_cols(M, N) == 256
+    q, k = _emb(M, D, 20).requires_grad_(), _emb(N, D, 21).requires_grad_()
+    fused_infonce(q, k, 0.05, target_offset=700).backward()
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    F.cross_entropy(qr @ kr.t() / 0.05, torch.arange(M, device="cuda") + 700).backward()
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad)):
+        assert (a.float() - b).abs().max() < 3e-2 * (b.abs().max() + 1e-6)
+    labels = torch.zeros(M, N, device="cuda")
+    labels[torch.arange(M), torch.arange(M) + 1000] = 1.0
+    labels[:, 300:320] = -1
+    q.grad = k.grad = None
+    contrastive_loss(q, k, labels, 0.05).backward()
+    qr.grad = kr.grad = None
+    _eager_label_loss(qr, kr, labels, 0.05).backward()
+    nv.check_status()
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad)):
+        assert (a.float() - b).abs().max() < 3e-2 * (b.abs().max() + 1e-6)
+
+
+@pytest.mark.parametrize("loss_type", ["multi", "soft", "cross"])
+def test_fused_dense_loss_types_in_panels(small_panels, loss_type):
+    test_fused_dense_loss_types(loss_type, 512, 2048, 1024, False)
 
 
 @pytest.mark.parametrize("loss_type", ["multi", "soft", "cross"])
