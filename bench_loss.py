@@ -72,19 +72,23 @@ def main():
     from lset_b200.ops.loss import fused_infonce
     from lset_b200.utils.tracing import NVLINK_GBS_PER_DIRECTION, load_peaks
 
-    # the reference's CUDA loss extension looks for CuTe headers at ~/workspace/cutlass/include
-    cutlass_home = os.path.expanduser("~/workspace/cutlass")
-    if rank == 0 and not os.path.exists(os.path.join(cutlass_home, "include")):
-        import importlib.util
+    # The reference's CUDA loss extension is compiled on first use (torch's JIT extension loader)
+    # and looks for the CuTe headers under ~/workspace/cutlass/include. The image carries them
+    # inside the flashinfer package instead: hand that directory to nvcc through its environment
+    # hook, which leaves the reference's own build code untouched.
+    import importlib.util
 
-        spec = importlib.util.find_spec("flashinfer")
-        src = os.path.join(os.path.dirname(spec.origin), "data", "cutlass") if spec else None
-        if src and os.path.isdir(os.path.join(src, "include")):
-            os.makedirs(os.path.dirname(cutlass_home), exist_ok=True)
-            try:
-                os.symlink(src, cutlass_home)
-            except OSError:
-                pass
+    spec = importlib.util.find_spec("flashinfer")
+    cute = os.path.join(os.path.dirname(spec.origin), "data", "cutlass", "include") if spec else ""
+    if os.path.isdir(cute):
+        os.environ["NVCC_APPEND_FLAGS"] = (os.environ.get("NVCC_APPEND_FLAGS", "") + f" -I{cute}").strip()
+    build_log = []
+
+    class _Capture(__import__("logging").Handler):
+        def emit(self, record):
+            build_log.append(record.getMessage())
+
+    __import__("logging").getLogger("lset.kernels.experimental.loss_sm100").addHandler(_Capture())
     dist.barrier()
     ref = {}
     if not args.no_reference and os.path.isdir(os.path.join(REPO, "baseline", "_ref", "lset")):
@@ -96,11 +100,18 @@ def main():
 
             ref = {"gather": gather_with_grad, "triton": fused_dense_loss, "eager": ref_infonce}
             try:
-                from lset.kernels.experimental.loss_sm100 import fused_dense_loss_sm100
+                from lset.kernels.experimental import loss_sm100 as ref_sm100
 
-                ref["cuda"] = fused_dense_loss_sm100
+                # build (or load from the JIT cache) now, rank by rank, and keep the reason if the
+                # build fails: the wrapper itself only logs a warning and then fails on first use
+                for r in range(world):
+                    if r == rank and ref_sm100._load_sm100_extension() is None:
+                        ref["cuda_err"] = ("build failed: " + " | ".join(build_log))[:400]
+                    dist.barrier()
+                if "cuda_err" not in ref:
+                    ref["cuda"] = ref_sm100.fused_dense_loss_sm100
             except Exception as exc:  # pragma: no cover
-                ref["cuda_err"] = repr(exc)[:120]
+                ref["cuda_err"] = repr(exc)[:200]
         except Exception as exc:  # pragma: no cover
             ref = {"err": repr(exc)[:200]}
     peaks = load_peaks()
