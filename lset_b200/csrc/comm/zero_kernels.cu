@@ -40,31 +40,50 @@ __global__ void __launch_bounds__(256)
   __shared__ float sred[8];
   float ss = 0.f;
   const long long n4 = n / 4;
-  for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n4;
-       i += 1LL * gridDim.x * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+  // Four independent 16-byte loads per thread and peer are issued before any is consumed: with
+  // one load in flight per thread the NVLink round trip, not the link, sets the rate.
+  constexpr int U = 4;
+  const long long stride = 1LL * gridDim.x * blockDim.x;
+  for (long long i0 = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += U * stride) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < world; ++k) {
       const int p = (rank + k) % world;  // start with the local copy, then walk the peers
-      const float4 v = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + lo)[i];
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
+      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + lo);
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        v[u] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[u].x += v[u].x;
+        acc[u].y += v[u].y;
+        acc[u].z += v[u].z;
+        acc[u].w += v[u].w;
+      }
     }
-    acc.x *= scale;
-    acc.y *= scale;
-    acc.z *= scale;
-    acc.w *= scale;
-    if (accumulate) {  // micro-steps of gradient accumulation add up in the shard
-      const float4 o = reinterpret_cast<const float4*>(out)[i];
-      acc.x += o.x;
-      acc.y += o.y;
-      acc.z += o.z;
-      acc.w += o.w;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n4) break;
+      float4 a = acc[u];
+      a.x *= scale;
+      a.y *= scale;
+      a.z *= scale;
+      a.w *= scale;
+      if (accumulate) {  // micro-steps of gradient accumulation add up in the shard
+        const float4 o = reinterpret_cast<const float4*>(out)[i];
+        a.x += o.x;
+        a.y += o.y;
+        a.z += o.z;
+        a.w += o.w;
+      }
+      reinterpret_cast<float4*>(out)[i] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
     }
-    reinterpret_cast<float4*>(out)[i] = acc;
-    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
   if (blockIdx.x == 0) {
     for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
@@ -161,9 +180,17 @@ __global__ void __launch_bounds__(256)
     const int p = (rank + k) % world;
     const uint4* src = static_cast<const uint4*>(shards.p[p]);
     uint4* out = dst + 1LL * p * n16;
-    for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n16;
-         i += 1LL * gridDim.x * blockDim.x)
-      out[i] = src[i];
+    constexpr int U = 4;   // loads in flight per thread (NVLink round trips overlap)
+    const long long stride = 1LL * gridDim.x * blockDim.x;
+    for (long long i0 = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i0 < n16; i0 += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < n16) v[u] = src[i0 + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < n16) out[i0 + u * stride] = v[u];
+    }
   }
 }
 

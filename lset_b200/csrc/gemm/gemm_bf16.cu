@@ -99,6 +99,10 @@ struct GemmArgs {
   unsigned* flags;            // [world * tiles_per_peer], value == epoch when the tile is local
   unsigned* chunk_counter;    // work-stealing counter of the pull warps (reset by the host)
   unsigned epoch;
+  // The first copy_ctas CTAs of a gather launch compute no tiles: all of their warps pull. Two
+  // pull warps per computing CTA keep too few bytes in flight to fill NVLink at eight ranks; a
+  // copy CTA keeps 8 warps x 8 KB on the wire.
+  int copy_ctas;
   // ---- peer scatter of C (fp32 accumulate only): row r belongs to rank r / c_rows_per_peer and
   // is reduced into that rank's buffer with red.global.add over NVLink.
   void* c_peers[8];
@@ -203,6 +207,10 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // CTAs that compute tiles are numbered 0 .. ncta-1 (a gather launch puts its copy CTAs first)
+  [[maybe_unused]] const int n_copy = GATHER ? g.copy_ctas : 0;
+  const int cta = int(blockIdx.x) - n_copy;
+  const int ncta = int(gridDim.x) - n_copy;
   // GATHER 1: rows of B come from the peers; GATHER 2: rows of A do. n_local = rows per rank.
   constexpr int kGatherRows = GATHER == 2 ? BM : BN;
   constexpr int kPullRows = 16;  // rows per pull item (one warp); divides BM and BN
@@ -244,13 +252,13 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
     return (rows + kPullRows - 1) / kPullRows;
   };
 
-  if (warp == 0) {
+  if (warp == 0 && cta >= 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < total && ok; tile += ncta) {
         const int split = tile / (tiles_m * tiles_n);
         const int mn = tile - split * (tiles_m * tiles_n);
         int m0, n0, chunk;
@@ -321,7 +329,7 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 && cta >= 0) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = F8 ? umma_idesc_f8(BM, BN, g.f8_a_e5m2, g.f8_b_e5m2)
@@ -330,7 +338,7 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+      for (int tile = cta; tile < total && ok; tile += ncta, ++it) {
         const int split = tile / (tiles_m * tiles_n);
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
@@ -372,8 +380,9 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
       }
     }
     __syncwarp();
-  } else if (GATHER && warp >= 6) {
-    // ------------------------------------------------------------------ pull warps (6, 7)
+  } else if (GATHER && (warp >= 6 || cta < 0)) {
+    // ------------------------------------------------------------------ pull warps (6, 7; every
+    // warp of a copy CTA)
     if constexpr (GATHER) {
       constexpr int kItemsPerTile = kGatherRows / kPullRows;
       const int items_total = g.world * tiles_per_peer * kItemsPerTile;
@@ -434,7 +443,7 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
     constexpr int kChunks = BN / 32 / (EW / 4);
     OutT* Cout = reinterpret_cast<OutT*>(g.C);
     int it = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+    for (int tile = cta; tile < total; tile += ncta, ++it) {
       const int split = tile / (tiles_m * tiles_n);
       const int mn = tile - split * (tiles_m * tiles_n);
       int m0, n0, chunk;
@@ -1437,6 +1446,29 @@ extern "C" int lb_label_loss_pgrad(const void* q, long long ldq, const void* k, 
 // flags: [world * ceil(n_local / 256)] zero-initialised once; counter: one u32; epoch: 1, 2, 3, …
 // on successive calls that use these flags (a flag counts the 16-row items pulled so far).
 // part/lse layout as in lb_infonce_fwd with tiles = world * ceil(n_local / 256).
+namespace lb {
+namespace {
+// Grid of a gather launch: the CTAs that compute tiles plus the copy CTAs in front of them (16 of
+// the SMs, more when the product has fewer tiles than SMs). Copy CTAs are only worth their SMs
+// when the transfer is a sizeable part of the kernel: pulling `pull_bytes` at ~700 GB/s must take
+// more than half of what the product's `flops` take at ~1.4 PFLOP/s. Otherwise (and on a single
+// rank) the two pull warps of every computing CTA keep up.
+int gather_grid(long long total, int sms, int world, double pull_bytes, double flops,
+                int* copy_ctas) {
+  const bool comm_heavy = pull_bytes / 700e9 > 0.5 * flops / 1.4e15;
+  if (world <= 1 || !comm_heavy) {
+    *copy_ctas = 0;
+    return (int)(total < sms ? total : sms);
+  }
+  const int compute = (int)(total < sms - 16 ? total : sms - 16);
+  int copy = sms - compute;
+  if (copy > 48) copy = 48;
+  *copy_ctas = copy;
+  return compute + copy;
+}
+}  // namespace
+}  // namespace lb
+
 extern "C" long long lb_infonce_xrank_scratch_floats(int M, int n_local, int world) {
   return 2LL * world * ((n_local + 255) / 256) * M + M;
 }
@@ -1458,7 +1490,8 @@ extern "C" int lb_infonce_fwd_xrank(const void* q, long long ldq, const void* co
   const int chunks = world * tiles_per_peer;
   const long long total = 1LL * ((M + BM - 1) / BM) * chunks;
   const int sms = num_sms();
-  grid = (int)(total < sms ? total : sms);
+  grid = gather_grid(total, sms, world, 2.0 * (world - 1) * n_local * D, 2.0 * M * N * D,
+                     &g.copy_ctas);
   g.scale = inv_temperature;
   g.part = scratch;
   g.pos = scratch + 2LL * chunks * M;
@@ -1529,7 +1562,8 @@ extern "C" int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const vo
   const int tiles_per_peer = (rows_local + BM - 1) / BM;
   const long long total = 1LL * world * tiles_per_peer * ((N + bn - 1) / bn);
   const int sms = num_sms();
-  const int grid = (int)(total < sms ? total : sms);
+  const int grid = gather_grid(total, sms, world, 2.0 * (world - 1) * rows_local * K,
+                               2.0 * M * N * K, &g.copy_ctas);
   if (cudaMemsetAsync(counter, 0, sizeof(unsigned), stream) != cudaSuccess) return -12;
   if (b_mn)
     return bn == 256 ? launch<0, 1, 256, __nv_bfloat16, EPI_STORE, 2>(tmA, tmB, g, grid, stream)
