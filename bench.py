@@ -333,7 +333,8 @@ def run_ours(args):
         init_on_device=args.config != "qwen3-0.6b",
         fp8=args.fp8 is not None, fp8_recipe=args.fp8 or "rowwise",
         # the 8B model at this batch keeps several GB of activations per layer: recompute them
-        activation_checkpoint=bool(preset.get("ac", False)), ac_mode=ac_mode)
+        activation_checkpoint=bool(preset.get("ac", False)), ac_mode=ac_mode,
+        reshard_after_forward=args.reshard_after_forward)
     device = engine.device
     n_batches = W + K
     # ranks of one tensor-parallel group see the same batch
@@ -397,6 +398,9 @@ def run_ours(args):
                             "host_blocked_on_gpu_ms_per_step": round(wait_ms, 2),
                             "fused_projections": preset["lora_r"] == 0,
                             "activation_checkpoint": ac_mode if preset.get("ac") else "off",
+                            "parameter_sharding": ("layers sharded (ZeRO-3)" if engine.store.zero3
+                                                   else "resident replica (ZeRO-2)"),
+                            "memory": engine.store.memory_report(),
                             "native_library": str(nv.lib_path().name)}, preset)
         if args.fp8 is not None:
             # a side measurement, not the headline: linear layers on the 8-bit tensor-core GEMM
@@ -596,6 +600,9 @@ def main():
     ap.add_argument("--config", choices=sorted(PRESETS), default="qwen3-0.6b")
     ap.add_argument("--fp8", choices=["tensorwise", "rowwise", "rowwise_with_gw_hp"], default=None,
                     help="side measurement: FP8 linear layers (the headline number is bf16)")
+    ap.add_argument("--reshard-after-forward", action="store_true",
+                    help="side measurement: shard the layers' parameters and gradients as well "
+                         "(ZeRO-3); the headline keeps the resident bf16 replica")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -7,7 +7,7 @@
 //               block in smem) -> dQ += dS·K
 //   dK/dV     one 256-thread CTA per (sequence, 128-row KV tile, KV head), walking (query block,
 //             head) pairs through a 3-deep TMA ring, with Sᵀ/dPᵀ double-buffered in TMEM so the
-//             products of step i+1 run while step i is in the softmax-gradient math:
+//             score products of step i+1 run while step i is in the softmax-gradient math:
 //               Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (TMEM) -> Pᵀ, dSᵀ (bf16, smem) -> dV += Pᵀ·dO, dK += dSᵀ·Q
 // In both kernels thread t owns accumulator row t % 128 and half (t / 128) of the 64 columns.
 // The Q / dO / K / V tiles are loaded once by TMA and serve both as K-major operands (contraction
@@ -504,6 +504,10 @@ __global__ void __launch_bounds__(kBwdThreads)
       }
     }
     tc_fence_after();
+    // The score products of the next step go to the tensor pipe now: their TMEM buffer was last
+    // read by step i - 1, and they then run under this step's softmax-gradient math instead of
+    // behind this step's accumulation products.
+    if (tid == 0 && i + 1 < n_inner) issue_scores(i + 1);
     float pt[32], dst[32];
     ld_row32(tmem_row + sb * 128 + half * 32, pt);
     ld_row32(tmem_row + sb * 128 + 64 + half * 32, dst);
@@ -552,8 +556,6 @@ __global__ void __launch_bounds__(kBwdThreads)
                   umma_smem_desc(qa + ks * 2048, 64 * 128, 1024), idesc_acc,
                   (i > 0 || ks > 0) ? 1u : 0u);
       umma_commit(bar_acc);
-      // run the next step's score products behind this step's accumulation
-      if (i + 1 < n_inner) issue_scores(i + 1);
     }
   }
   if (!failed && n_inner > 0) {

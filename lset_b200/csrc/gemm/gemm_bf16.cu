@@ -913,6 +913,23 @@ int launch_out(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g
 //   bn: 0 = auto, 128 or 256.
 // All leading dimensions and N must be multiples of 8 elements; base pointers 16-byte aligned.
 // Returns 0 or a negative code; device-side timeouts are reported through *status (device int).
+extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                 int out_fp32, int accumulate, int splits, int* status,
+                                 void* stream_);
+extern "C" int lb_gemm_2cta_pairs();
+
+// LSET_B200_GEMM_2CTA=1 routes the plain products (no bias, no peer scatter, at least one
+// 256 x 256 tile) to the CTA-pair kernel of gemm_2cta.cu.
+static int use_2cta() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LSET_B200_GEMM_2CTA");
+    v = e != nullptr ? atoi(e) : 0;
+  }
+  return v;
+}
+
 static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K,
                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
                           int out_fp32, int accumulate, const void* bias, int splits, int bn,
@@ -930,6 +947,16 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
 
   const int tiles_m = (M + BM - 1) / BM;
   const int sms = num_sms();
+  if (use_2cta() && bias == nullptr && !scatter && bn == 0 && M >= 256 && N >= 256) {
+    int s2 = splits;
+    if (s2 == 0) {
+      const long long t2 = 1LL * ((M + 255) / 256) * ((N + 255) / 256);
+      s2 = (out_fp32 && accumulate)
+               ? auto_splits(t2, (K + BK - 1) / BK, lb_gemm_2cta_pairs()) : 1;
+    }
+    return lb_gemm_bf16_2cta(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, s2,
+                             status, stream_);
+  }
   if (bn != 128 && bn != 256) {
     auto eff = [&](int b) {
       const long long t = 1LL * tiles_m * ((N + b - 1) / b);
