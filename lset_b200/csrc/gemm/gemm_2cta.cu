@@ -17,10 +17,9 @@
 //
 // Barriers. full[s] (leader): armed by the leader's producer with the bytes of both CTAs' loads of
 // stage s; the peer's loads name it as their completion barrier (the cta_group::2 form of the TMA
-// load allows a barrier in the partner CTA). empty[s]: in the leader, the tcgen05.commit that
-// follows the MMAs of stage s; in the peer, a plain remote mbarrier.arrive that the leader's
-// producer sends on once it has seen its own. tfull[a]: one tcgen05.commit per CTA (the peer's
-// barrier through its cluster address), once per tile. tempty[a] (leader): one arrival per
+// load allows a barrier in the partner CTA). empty[s] and tfull[a], in both CTAs: one
+// tcgen05.commit per CTA after the MMAs of the stage / tile (the peer's barrier through its
+// cluster address). tempty[a] (leader): one arrival per
 // epilogue warp of both CTAs. Every wait is bounded; a CTA that gives up reports through the
 // status word and still meets its partner at the final cluster barrier, so nothing is left
 // waiting.
@@ -74,34 +73,13 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
   return out;
 }
+// Arrival on a barrier of the partner CTA. No data written by this thread is handed over with it
+// (the barriers of this kernel order TMA writes, tensor-core reads and TMEM reads, all of which
+// complete before the arrival is issued), so the default semantics are enough; cluster-scope
+// acquire / release on the per-stage path costs a fence per k-block in the issuing threads.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait on a barrier that another CTA of the cluster arrives on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-#pragma unroll 1
-  for (uint32_t it = 0;; ++it) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((it & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) return false;
-  }
-}
-
 // 2-D tile load into this CTA's shared memory whose completion bytes are counted on `bar_cluster`,
 // a barrier of either CTA of the pair (cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tm,
@@ -222,14 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      long long filled = 0;     // stages filled so far (the first kStages need no hand-back)
       bool ok = true;
-      uint32_t full_leader[kStages], empty_peer[kStages];
-#pragma unroll
-      for (int s = 0; s < kStages; ++s) {
-        full_leader[s] = map_to_cta(&full[s], 0);
-        empty_peer[s] = map_to_cta(&empty[s], 1);
-      }
       for (int tile = pair; tile < total && ok; tile += npairs) {
         const int split = tile / (tiles_m * tiles_n);
         int m0, n0;
@@ -237,20 +208,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int nb = n0 + int(rank) * BNh;          // this CTA's half of the B tile
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
-        for (int kb = kb0; kb < kb1; ++kb, ++filled) {
-          if (!mbar_wait_cluster(&empty[stage], phase ^ 1u)) {
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u)) {
             report_status(g.status, kStatusTimeoutProducer);
             ok = false;
             break;
           }
-          if (leader) {
-            // the MMAs that read this stage (in both CTAs) are done: pass that on to the peer
-            if (filled >= kStages) mbar_arrive_remote(empty_peer[stage]);
-            mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-          }
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          const uint32_t bar = full_leader[stage];
+          const uint32_t bar = map_to_cta(&full[stage], 0);
           const int kc = kb * BK;
           if (A_MN) {
 #pragma unroll
@@ -295,14 +262,14 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
         const int acc = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
-        if (!mbar_wait_cluster(&tempty[acc], aphase ^ 1u)) {
+        if (!mbar_wait(&tempty[acc], aphase ^ 1u)) {
           report_status(g.status, kStatusTimeoutMma);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BNp;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_cluster(&full[stage], phase)) {
+          if (!mbar_wait(&full[stage], phase)) {
             report_status(g.status, kStatusTimeoutMma);
             ok = false;
             break;
@@ -318,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                                         : umma_smem_desc(sb + k * 32, 16, 1024);
             umma2_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma2_commit(&empty[stage]);
+          umma2_commit_both(&empty[stage], 1u);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -343,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       decode(tile - split * (tiles_m * tiles_n), m0, n0);
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
-      if (!mbar_wait_cluster(&tfull[acc], aphase)) {
+      if (!mbar_wait(&tfull[acc], aphase)) {
         report_status(g.status, kStatusTimeoutEpilogue);
         break;
       }

@@ -919,15 +919,22 @@ extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, i
                                  void* stream_);
 extern "C" int lb_gemm_2cta_pairs();
 
-// LSET_B200_GEMM_2CTA=1 routes the plain products (no bias, no peer scatter, at least one
-// 256 x 256 tile) to the CTA-pair kernel of gemm_2cta.cu.
+// The plain products (no bias, no peer scatter, at least one 256 x 256 tile) run on the CTA-pair
+// kernel of gemm_2cta.cu: the same speed per kernel within a few percent, at less shared-memory
+// traffic per FLOP, which under the power cap is worth about 3 % of a training step.
+// LSET_B200_GEMM_2CTA=0 (or lb_gemm_use_2cta(0)) keeps everything on the one-CTA kernel.
+static int g_use_2cta = -1;
 static int use_2cta() {
-  static int v = -1;
-  if (v < 0) {
+  if (g_use_2cta < 0) {
     const char* e = getenv("LSET_B200_GEMM_2CTA");
-    v = e != nullptr ? atoi(e) : 0;
+    g_use_2cta = e != nullptr ? (atoi(e) != 0) : 1;
   }
-  return v;
+  return g_use_2cta;
+}
+// v = 0 / 1 switches the CTA-pair kernel off / on for this process; v < 0 only queries.
+extern "C" int lb_gemm_use_2cta(int v) {
+  if (v >= 0) g_use_2cta = v != 0;
+  return use_2cta();
 }
 
 static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K,
