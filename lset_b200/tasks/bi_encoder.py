@@ -119,13 +119,18 @@ class BiEncoderTask(nn.Module):
         Returns the rank's share of the global mean (the shares sum to the global loss)."""
         W, rank = self._dp()
         Bq, Bd = q_emb.shape[0], d_emb.shape[0]
-        if (W > 1 and n_emb is None and labels is None and self.matryoshka_dims is None
+        if (W > 1 and labels is None and self.matryoshka_dims is None
                 and self.top_k is None and self.logit_scale is None and Bq == Bd):
             from ..dist import xrank_loss
 
-            if xrank_loss.supported(q_emb, d_emb, self.dp_group):
+            # Hard negatives ride along: every rank publishes [its documents; its negatives] as one
+            # block. The softmax runs over all columns whatever their order, and the positive of
+            # local query i is still row i of this rank's block.
+            local_docs = d_emb if n_emb is None else torch.cat([d_emb, n_emb], dim=0)
+            if xrank_loss.supported(q_emb, local_docs, self.dp_group):
                 # gather, similarity GEMM, logsumexp and the dK reduce-scatter fused over NVLink
-                return xrank_loss.cross_rank_infonce(q_emb, d_emb, self.temperature, self.dp_group)
+                return xrank_loss.cross_rank_infonce(q_emb, local_docs, self.temperature,
+                                                     self.dp_group)
         docs = gather_for_local_rows(d_emb, self.dp_group)
         if n_emb is not None:
             docs = torch.cat([docs, gather_for_local_rows(n_emb, self.dp_group)], dim=0)

@@ -46,6 +46,34 @@ def main():
                 "loss_err": abs(loss.item() - share.item()) / max(1e-3, abs(share.item())),
                 "dq_err": ((q.grad.float() - dq_ref).abs().max() / (dq_ref.abs().max() + 1e-9)).item(),
                 "dk_err": ((d.grad.float() - dk_ref).abs().max() / (dk_ref.abs().max() + 1e-9)).item()})
+    # hard negatives through the task: every rank's block is [documents; negatives]
+    from lset_b200.tasks.bi_encoder import BiEncoderTask
+
+    task = BiEncoderTask(temperature=0.02)
+    B, Bn, D = 64, 192, 512
+    torch.manual_seed(7 + rank)
+    q, d, n = (F.normalize(torch.randn(r, D, device=dev), dim=-1).to(torch.bfloat16).requires_grad_()
+               for r in (B, B, Bn))
+    loss = task.loss_from_embeddings(q, d, n)
+    loss.backward()
+    nv.check_status()
+
+    def gathered(t):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.detach())
+        return torch.cat(parts).float().requires_grad_()
+
+    Q, Kd, Kn = gathered(q), gathered(d), gathered(n)
+    logits = Q @ torch.cat([Kd, Kn]).t() / 0.02
+    ce = F.cross_entropy(logits, torch.arange(world * B, device=dev), reduction="none")
+    (ce.sum() / (world * B)).backward()
+    share = ce[rank * B:(rank + 1) * B].sum() / (world * B)
+    rel = lambda a, b: ((a.float() - b).abs().max() / (b.abs().max() + 1e-9)).item()  # noqa: E731
+    cases.append({"B": B, "D": D, "rep": "negatives",
+                  "loss_err": abs(loss.item() - share.item()) / max(1e-3, abs(share.item())),
+                  "dq_err": rel(q.grad, Q.grad[rank * B:(rank + 1) * B]),
+                  "dk_err": max(rel(d.grad, Kd.grad[rank * B:(rank + 1) * B]),
+                                rel(n.grad, Kn.grad[rank * Bn:(rank + 1) * Bn]))})
     if rank == 0:
         with open(out_path, "w") as fh:
             json.dump({"cases": cases}, fh)

@@ -30,6 +30,7 @@ def _check(c, ref, tol=2e-2):
     c = c.float()
     if ref.dim() == 1:
         c, ref = c[None], ref[None]
+    c, ref = c.reshape(-1, c.shape[-1]), ref.reshape(-1, ref.shape[-1])
     err = (c - ref).abs()
     M, N = ref.shape
     Mp, Np = -(-M // 64) * 64, -(-N // 64) * 64
