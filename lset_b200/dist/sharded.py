@@ -348,18 +348,28 @@ class ParamStore:
 
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self) -> None:
+        # Forward passes of a layer that still await their backward. A step may run a layer more
+        # than once before one backward call (queries and documents encoded separately on padded
+        # batches): a resident group is reduced when the last of those passes has been through
+        # backward, not at the first hook that fires.
+        self._pending = {}
         for layer, gs in self._groups_of_layer:
+            self._pending[id(layer)] = 0
 
-            def after_backward(_mod, _gin, _gout, gs=gs):
+            def after_backward(_mod, _gin, _gout, gs=gs, key=id(layer)):
+                left = self._pending[key] = max(0, self._pending[key] - 1)
                 for g in gs:
-                    # sharded groups reduce on every micro-step (their full gradient buffer is
-                    # handed on to the next layer); resident ones only on the boundary step
-                    if g.sharded or self.requires_gradient_sync:
+                    # sharded groups reduce on every pass and micro-step (their full gradient
+                    # buffer is handed on to the next layer); resident ones only on the boundary
+                    # step, after the last pass
+                    if g.sharded or (self.requires_gradient_sync and left == 0):
                         self._reduce_group(g)
                     if g.sharded:
                         self._release_params(g)
 
-            def before_forward(_mod, _args, gs=gs):
+            def before_forward(_mod, _args, gs=gs, key=id(layer)):
+                if torch.is_grad_enabled():
+                    self._pending[key] += 1
                 for g in gs:
                     if g.sharded:
                         self._materialize(g)
@@ -505,6 +515,8 @@ class ParamStore:
         layers whose inputs carry no gradient) and folds stray autograd grads in."""
         for g in self.groups:
             g.collect_autograd_grads()
+        for key in getattr(self, "_pending", ()):
+            self._pending[key] = 0          # passes that never reached backward do not carry over
         if not self.requires_gradient_sync:
             return
         for g in reversed(self.groups):
