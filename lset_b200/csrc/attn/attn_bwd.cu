@@ -9,7 +9,8 @@
 //             head) pairs through a 3-deep TMA ring, with Sᵀ/dPᵀ double-buffered in TMEM so the
 //             score products of step i+1 run while step i is in the softmax-gradient math:
 //               Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (TMEM) -> Pᵀ, dSᵀ (bf16, smem) -> dV += Pᵀ·dO, dK += dSᵀ·Q
-// In both kernels thread t owns accumulator row t % 128 and half (t / 128) of the 64 columns.
+// Thread t owns accumulator row t % 128 and a half (dQ kernel, 256 threads) or a quarter (dK/dV
+// kernel, 512 threads) of the 64 columns of a score block.
 // The Q / dO / K / V tiles are loaded once by TMA and serve both as K-major operands (contraction
 // over head_dim) and as MN-major operands (contraction over tokens); nothing is transposed in
 // memory. Probabilities are recomputed from the forward's LSE.
@@ -95,6 +96,52 @@ __device__ __forceinline__ void st_half_row_bf16_swz(uint8_t* tile, int row, int
     q.z = pack_bf16x2(v[c * 8 + 4], v[c * 8 + 5]);
     q.w = pack_bf16x2(v[c * 8 + 6], v[c * 8 + 7]);
     *reinterpret_cast<uint4*>(tile + swz128_offset(row, half * 4 + c)) = q;
+  }
+}
+
+// 16-column variants for kernels whose threads own a quarter of a 64-column block.
+__device__ __forceinline__ void ld_row16(uint32_t taddr, float (&s)[16]) {
+  uint32_t t0[16];
+  tmem_ld_32x32b_x16(taddr, t0);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < 16; ++c) s[c] = __uint_as_float(t0[c]);
+}
+
+// Write 16 values of one row into columns [16*quarter, 16*quarter+16) of a 128-row x 64-column
+// bf16 tile stored K-major with the 128-byte swizzle.
+__device__ __forceinline__ void st_quarter_row_bf16_swz(uint8_t* tile, int row, int quarter,
+                                                        const float (&v)[16]) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint4 q;
+    q.x = pack_bf16x2(v[c * 8 + 0], v[c * 8 + 1]);
+    q.y = pack_bf16x2(v[c * 8 + 2], v[c * 8 + 3]);
+    q.z = pack_bf16x2(v[c * 8 + 4], v[c * 8 + 5]);
+    q.w = pack_bf16x2(v[c * 8 + 6], v[c * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + swz128_offset(row, quarter * 2 + c)) = q;
+  }
+}
+
+// Store NCOLS (a multiple of 16) accumulator columns of one row as bf16 to dst when `pred`.
+template <int NCOLS>
+__device__ __forceinline__ void store_acc_cols16(uint32_t taddr, bf16* dst, bool pred) {
+#pragma unroll 1
+  for (int c = 0; c < NCOLS / 16; ++c) {
+    uint32_t o[16];
+    tmem_ld_32x32b_x16(taddr + c * 16, o);
+    tmem_ld_wait();
+    if (pred) {
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        uint4 q;
+        q.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+        q.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+        q.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+        q.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+        *reinterpret_cast<uint4*>(dst + c * 16 + v * 8) = q;
+      }
+    }
   }
 }
 
@@ -357,8 +404,13 @@ struct DkvCfg {
   static_assert(256 + 2 * HD <= 512, "head_dim too large for the dK/dV accumulators");
 };
 
+// 512 threads: thread t owns accumulator row t % 128 and a quarter (t / 128) of the 64 columns of
+// a score block. With 256 threads (two warps per scheduler) the softmax-gradient math of a step
+// was bound by instruction latency, not by the tensor pipe.
+constexpr int kDkvThreads = 512;
+
 template <int HD>
-__global__ void __launch_bounds__(kBwdThreads)
+__global__ void __launch_bounds__(kDkvThreads)
     attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     AttnBwdArgs a) {
@@ -395,7 +447,7 @@ __global__ void __launch_bounds__(kBwdThreads)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int half = warp >> 2;
+  const int quarter = warp >> 2;  // which 16 of the 64 score columns this thread handles
   constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
   constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
 
@@ -508,15 +560,15 @@ __global__ void __launch_bounds__(kBwdThreads)
     // read by step i - 1, and they then run under this step's softmax-gradient math instead of
     // behind this step's accumulation products.
     if (tid == 0 && i + 1 < n_inner) issue_scores(i + 1);
-    float pt[32], dst[32];
-    ld_row32(tmem_row + sb * 128 + half * 32, pt);
-    ld_row32(tmem_row + sb * 128 + 64 + half * 32, dst);
+    float pt[16], dst[16];
+    ld_row16(tmem_row + sb * 128 + quarter * 16, pt);
+    ld_row16(tmem_row + sb * 128 + 64 + quarter * 16, dst);
     {
-      const float* lse2 = sStat + sb * 128 + half * 32;
+      const float* lse2 = sStat + sb * 128 + quarter * 16;
       const float* dl = lse2 + 64;
-      const int qbase = qb * 64 + half * 32;
+      const int qbase = qb * 64 + quarter * 16;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
+      for (int c = 0; c < 16; ++c) {
         const int qp = qbase + c;
         const bool valid = row_valid && qp < len && (!a.causal || kvpos <= qp);
         const float p = valid ? exp2f(pt[c] * a.scale_log2 - lse2[c]) : 0.f;
@@ -535,8 +587,8 @@ __global__ void __launch_bounds__(kBwdThreads)
       tc_fence_after();
     }
     if (tid == 0 && i + 2 < n_inner) load_q(i + 2);
-    st_half_row_bf16_swz(sPT, r, half, pt);
-    st_half_row_bf16_swz(sdST, r, half, dst);
+    st_quarter_row_bf16_swz(sPT, r, quarter, pt);
+    st_quarter_row_bf16_swz(sdST, r, quarter, dst);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -568,10 +620,10 @@ __global__ void __launch_bounds__(kBwdThreads)
   if (!failed && n_inner > 0) {
     tc_fence_after();
     const long long tok = 1LL * seq0 + kvpos;
-    store_acc_cols<HD / 2>(tmem_row + C::DV_COL + half * (HD / 2),
-                           a.dV + tok * a.lddv + hk * HD + half * (HD / 2), row_valid);
-    store_acc_cols<HD / 2>(tmem_row + C::DK_COL + half * (HD / 2),
-                           a.dK + tok * a.lddk + hk * HD + half * (HD / 2), row_valid);
+    store_acc_cols16<HD / 4>(tmem_row + C::DV_COL + quarter * (HD / 4),
+                             a.dV + tok * a.lddv + hk * HD + quarter * (HD / 4), row_valid);
+    store_acc_cols16<HD / 4>(tmem_row + C::DK_COL + quarter * (HD / 4),
+                             a.dK + tok * a.lddk + hk * HD + quarter * (HD / 4), row_valid);
   }
   tc_fence_before();
   __syncthreads();
@@ -629,7 +681,7 @@ int launch_bwd(const void* dO, long long lddo, const void* q, long long ldq, con
       configured = true;
     }
     a.plan = plan_kv;
-    kern<<<dim3(cap_kv, a.Hk), kBwdThreads, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
+    kern<<<dim3(cap_kv, a.Hk), kDkvThreads, C::SMEM_BYTES, st>>>(tmQ, tmdO, tmK, tmV, a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

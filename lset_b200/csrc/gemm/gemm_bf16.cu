@@ -31,7 +31,6 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kGemmThreads = 192;
 constexpr int kGatherThreads = 256;  // + 2 pull warps
 
 // Number of epilogue warps. The plain store / reduce epilogue of the bf16 kernel runs on eight
@@ -114,7 +113,6 @@ struct GemmArgs {
   const float* f8_sb;
   int f8_sa_stride, f8_sb_stride;
   int f8_a_e5m2, f8_b_e5m2;
-  int dbg;  // TEMP diagnostic: 1 = epilogue without global stores, 2 = epilogue without any work
   int* status;
 };
 
@@ -457,11 +455,6 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
         break;
       }
       tc_fence_after();
-      if (g.dbg == 2) {
-        tc_fence_before();
-        mbar_arrive(&tempty[acc]);
-        continue;
-      }
       if constexpr (EPI == EPI_GLU) {
         // gate chunk c and up chunk c of the tile -> gate_up (both halves) and h = act(gate) * up.
         // Values are rounded to bf16 before the activation, as the stand-alone GLU kernel sees them.
@@ -741,7 +734,7 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
                   OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
                                static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
                   red_add8_bf16(base + colb, pk);
-                } else if (g.dbg != 1) {
+                } else {
                   *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
                 }
               }
@@ -770,7 +763,7 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
                     OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
                                  static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
                     red_add8_bf16(base + colb, pk);
-                  } else if (g.dbg != 1) {
+                  } else {
                     *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
                   }
                 }
@@ -1007,11 +1000,6 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   g.splits = splits;
   g.kb_per_split = kb_per;
   g.status = status;
-  {
-    static int dbg = -1;
-    if (dbg < 0) { const char* e = getenv("LB_GEMM_DBG"); dbg = e ? atoi(e) : 0; }
-    g.dbg = dbg;
-  }
   if (c_peers != nullptr && c_rows_per_peer > 0) {
     if (c_world > 8) return -3;
     for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);

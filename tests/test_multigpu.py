@@ -12,7 +12,9 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 # every power-of-two rank count the machine offers: peer rotation, flag / epoch arithmetic and
 # the push all-gather behave differently at 2, 4 and 8 ranks
-WORLDS = [w for w in (2, 4, 8) if w <= torch.cuda.device_count()] or [2]
+# (LSET_TEST_WORLDS="4,8" restricts the list, e.g. to split a long run over several invocations)
+_ASKED = [int(w) for w in os.environ.get("LSET_TEST_WORLDS", "2,4,8").split(",") if w.strip()]
+WORLDS = [w for w in _ASKED if w <= torch.cuda.device_count()] or [2]
 needs_two = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 
 
