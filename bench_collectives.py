@@ -69,7 +69,7 @@ def main():
     from lset_b200.dist.sharded import ParamStore, ShardedAdamW
     from lset_b200.ops import _native as nv
     from lset_b200.ops.gemm import matmul_abt
-    from lset_b200.utils.tracing import load_peaks, roofline
+    from lset_b200.utils.tracing import NVLINK_GBS_PER_DIRECTION, load_peaks, roofline
 
     peaks = load_peaks()
     flush = torch.zeros(64 * 1024 * 1024, device=dev)
@@ -146,7 +146,19 @@ def main():
         hbm = 4.0 * n_par / world * world + shard * (4 * 3 * 2 + 2) + 2.0 * n_par
         key = "fused_ms" if symm_on else "nccl_ms"
         if symm_on:
+            # With gradient clipping the update needs the global norm, i.e. the whole reduction,
+            # first: the step is two dependent sweeps, each with its own binding resource.
+            # Sweep 1 (reduce): fp32 shards of the W - 1 peers come in over NVLink; this GPU's
+            # memory serves its own shard, the peers' reads of theirs, and the reduced write.
+            # Sweep 2 (AdamW + push): fp32 gradient, two moments and the master read and written,
+            # the bf16 shard written locally and into W - 1 peers, whose pushes land here.
+            nvl = NVLINK_GBS_PER_DIRECTION * 1e9
+            hbm_bw = peaks["hbm_gbs"] * 1e9
+            p1 = max(4.0 * (world - 1) * shard / nvl, 4.0 * shard * (world + 1) / hbm_bw)
+            p2 = max(2.0 * (world - 1) * shard / nvl, shard * (30.0 + 2.0 * (world - 1)) / hbm_bw)
+            floor_ms = (p1 + p2) * 1e3
             out.append(dict(path="zero_step", params=n_par, symm=bool(store.use_symm), fused_ms=ms,
+                            two_phase_floor_ms=floor_ms, fraction_of_two_phase_floor=floor_ms / ms,
                             **roofline(ms, 0.0, hbm, link, peaks)))
         else:
             out[-1][key] = ms

@@ -77,6 +77,33 @@ struct LbStreamCtx {
   void* stream;
 };
 
+// Tensor parallelism with a token-sharded residual stream (sequence parallelism): the block's
+// input and output hold `rows` tokens of this rank, the column-parallel projections (QKV, gate-up)
+// gather the shards of all ranks inside their GEMM and the row-parallel ones (o_proj, down) reduce
+// and scatter their output from the GEMM epilogue. The descriptor then carries this rank's head
+// and FFN-column counts. Buffers live in symmetric memory owned by the caller: a publication area
+// of width H (two halves used alternately, one use per gathered GEMM) and bf16 accumulators of
+// width H (two halves, one use per reduced GEMM). Each of the forward and the backward call makes
+// exactly two uses of either and four device barriers; the caller advances its counters by those
+// amounts after the call.
+struct LbTpCtx {
+  int world, rank;
+  int rows;                        // token rows of this rank; projections see world * rows tokens
+  int reserved;
+  const void* const* ag_peers[2];  // per half: host array of `world` device pointers
+  void* ag_local[2];               // this rank's half
+  unsigned* ag_flags;              // arrival flags of the pulled row tiles (for this row count)
+  unsigned* ag_counter;            // work counter of the gather GEMM
+  const void* const* rs_peers[2];  // per half: host array of `world` accumulator pointers
+  void* rs_local[2];
+  const void* const* pads;         // device-barrier flag pads of every rank
+  unsigned long long bar_limit_ns;
+  unsigned ag_epoch;               // uses of the publication area before this call
+  unsigned ag_calls;               // uses of these flag words before this call
+  unsigned rs_epoch;               // uses of the accumulators before this call
+  unsigned bar_epoch;              // barriers passed before this call
+};
+
 struct LbBlockIO {
   // forward
   const void* branch;    // [T, H] un-added output of the previous block (or the embeddings)
@@ -89,15 +116,18 @@ struct LbBlockIO {
   const void* d_res_out; // [T, H] gradient of `res_out`, or null
   void* dx;              // [T, H] gradient of `branch` (and of `residual`: they are equal)
   void* work;            // lb_block_work_bytes() bytes, 256-byte aligned
+  const LbTpCtx* tp;     // null: the stream is not token-sharded
 };
 
-// Bytes of the activation arena the forward fills and the backward reads.
-size_t lb_block_saved_bytes(const LbBlockDesc* d, int T, int has_residual);
+// Bytes of the activation arena the forward fills and the backward reads (`tp` may be null; with it
+// T is ignored and the sizes follow world * rows gathered tokens and `rows` local ones).
+size_t lb_block_saved_bytes(const LbBlockDesc* d, int T, int has_residual, const LbTpCtx* tp);
 // Bytes of temporary storage the backward needs.
-size_t lb_block_work_bytes(const LbBlockDesc* d, int T);
+size_t lb_block_work_bytes(const LbBlockDesc* d, int T, const LbTpCtx* tp);
 // Number of kernel launches the two calls issue (for benchmark reporting).
-int lb_block_fwd_launches(const LbBlockDesc* d, const LbStreamCtx* c, int has_residual);
-int lb_block_bwd_launches(const LbBlockDesc* d, const LbStreamCtx* c);
+int lb_block_fwd_launches(const LbBlockDesc* d, const LbStreamCtx* c, int has_residual,
+                          const LbTpCtx* tp);
+int lb_block_bwd_launches(const LbBlockDesc* d, const LbStreamCtx* c, const LbTpCtx* tp);
 
 // Returns 0, or the negative code of the first launcher that failed.
 int lb_block_fwd(const LbBlockDesc* d, const LbStreamCtx* c, const LbBlockIO* io);

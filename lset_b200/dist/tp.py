@@ -92,6 +92,7 @@ def _wrap_forward_sp(module: nn.Module, kind: str, st) -> None:
 
     module.forward = forward
     module._tp_kind = kind
+    module._sp_state = st      # the block runner drives the same buffers when it takes the block
 
 
 def _wrap_forward(module: nn.Module, kind: str, group) -> None:

@@ -110,10 +110,14 @@ class SPState:
                       and symm.enabled(self.world, device))
         self._token = None
 
-    def barrier(self):
+    def token(self):
+        """The group's device barrier (created on first use: a rendezvous of the group)."""
         if self._token is None:
             self._token = symm.DeviceBarrier(self.device, self.group)
-        self._token.sync()
+        return self._token
+
+    def barrier(self):
+        self.token().sync()
 
     def ag_buf(self, rows, K) -> _AGBuf:
         b = self._ag.get(K)

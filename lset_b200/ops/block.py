@@ -9,9 +9,12 @@ block. The kernels, their order and their arguments are those of the op-by-op pa
 produce the same numbers.
 
 Taken for blocks whose projections are plain bf16 ``Linear`` layers (fused, or separate) or LoRA
-wrappers around them, without biases, on a stream that is not token-sharded. Everything else
-(tensor-parallel wrappers, FP8 / NF4 layers, Gemma's sandwich norms, selective activation
-checkpointing, CPU tensors) keeps the op-by-op path.
+wrappers around them, without biases. Tensor-parallel blocks on a token-sharded stream (sequence
+parallelism with the fused all-gather / reduce-scatter GEMMs, fused QKV and gate-up weights, packed
+batches) are taken too: the runner then issues the gathered and the reduced GEMMs and their device
+barriers itself, on the symmetric buffers of the group's ``SPState``, in the order the op-by-op
+path uses. Everything else (all-reduce tensor parallelism, FP8 / NF4 layers, Gemma's sandwich
+norms, selective activation checkpointing, CPU tensors) keeps the op-by-op path.
 
 Replaces the Python block of the reference (lset/models/decoder/qwen3/block.py:23-68).
 """
@@ -61,12 +64,23 @@ class LbStreamCtx(ctypes.Structure):
                 ("rope_scratch", _fp), ("wg_tmp", _fp), ("stream", _vp)]
 
 
+class LbTpCtx(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("rows", ctypes.c_int),
+                ("reserved", ctypes.c_int), ("ag_peers", _vp * 2), ("ag_local", _vp * 2),
+                ("ag_flags", _vp), ("ag_counter", _vp), ("rs_peers", _vp * 2),
+                ("rs_local", _vp * 2), ("pads", _vp), ("bar_limit_ns", ctypes.c_ulonglong),
+                ("ag_epoch", ctypes.c_uint), ("ag_calls", ctypes.c_uint),
+                ("rs_epoch", ctypes.c_uint), ("bar_epoch", ctypes.c_uint)]
+
+
 class LbBlockIO(ctypes.Structure):
     _fields_ = [("branch", _vp), ("residual", _vp), ("out", _vp), ("res_out", _vp),
-                ("saved", _vp), ("d_out", _vp), ("d_res_out", _vp), ("dx", _vp), ("work", _vp)]
+                ("saved", _vp), ("d_out", _vp), ("d_res_out", _vp), ("dx", _vp), ("work", _vp),
+                ("tp", _vp)]
 
 
 _lib = None
+calls = {"dp": 0, "tp": 0}   # block forwards taken by the runner, by stream layout (for tests)
 
 
 def _library():
@@ -77,10 +91,12 @@ def _library():
         lib.lb_block_work_bytes.restype = ctypes.c_size_t
         for fn in (lib.lb_block_fwd, lib.lb_block_bwd):
             fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
-        lib.lb_block_saved_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
-        lib.lb_block_work_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int]
-        lib.lb_block_fwd_launches.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
-        lib.lb_block_bwd_launches.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.lb_block_saved_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_void_p]
+        lib.lb_block_work_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.lb_block_fwd_launches.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                              ctypes.c_void_p]
+        lib.lb_block_bwd_launches.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         _lib = lib
     return _lib
 
@@ -104,6 +120,15 @@ def _plain_linear(m) -> bool:
 
     return (type(m) is Linear and m.bias is None and "forward" not in m.__dict__
             and not hasattr(m, "_tp_kind") and m.weight.dtype == torch.bfloat16
+            and m.weight.is_cuda and m.weight.stride(-1) == 1)
+
+
+def _sp_linear(m, kind: str, st) -> bool:
+    """A bias-free bf16 ``Linear`` that ``apply_tp`` wrapped for the token-sharded stream."""
+    from ..models.layers import Linear
+
+    return (type(m) is Linear and m.bias is None and getattr(m, "_tp_kind", None) == kind
+            and getattr(m, "_sp_state", None) is st and m.weight.dtype == torch.bfloat16
             and m.weight.is_cuda and m.weight.stride(-1) == 1)
 
 
@@ -138,7 +163,15 @@ class BlockPlan:
         qkv_mods = [att.qkv_proj] if att.fused_qkv else [att.q_proj, att.k_proj, att.v_proj]
         gu_mods = [mlp.gate_up_proj] if mlp.fused_gate_up else [mlp.gate_proj, mlp.up_proj]
         mods = qkv_mods + [att.o_proj] + gu_mods + [mlp.down_proj]
-        parts = [_linear_parts(m) for m in mods]
+        # tensor parallelism on a token-sharded stream: every projection carries the group's state
+        self.sp = getattr(att.o_proj, "_sp_state", None)
+        if self.sp is not None:
+            kinds = ("colwise", "rowwise", "colwise", "rowwise")
+            if len(mods) != 4 or not all(_sp_linear(m, k, self.sp) for m, k in zip(mods, kinds)):
+                return
+            parts = [(m.weight, None, None, 0.0) for m in mods]
+        else:
+            parts = [_linear_parts(m) for m in mods]
         if any(p is None for p in parts):
             return
         self.qkv, self.o = parts[:len(qkv_mods)], parts[len(qkv_mods)]
@@ -193,8 +226,8 @@ class BlockPlan:
                 + [att.o_proj]
                 + ([mlp.gate_up_proj] if mlp.fused_gate_up else [mlp.gate_proj, mlp.up_proj])
                 + [mlp.down_proj])
-        return tuple((id(m), "forward" in m.__dict__, m.weight.dtype, m.weight.device, m.training)
-                     for m in mods)
+        return tuple((id(m), "forward" in m.__dict__, id(getattr(m, "_sp_state", None)),
+                      m.weight.dtype, m.weight.device, m.training) for m in mods)
 
     def still_valid(self, block) -> bool:
         return self.signature == self._signature(block)
@@ -247,17 +280,69 @@ def usable(block, branch, ctx) -> bool:
         return False
     if _ac._active is not None or not enabled("block_runner") or _rt.attention_backend == "sdpa":
         return False
-    if ctx.pos.shape[0] != branch.shape[0]:      # token-sharded stream (sequence parallelism)
-        return False
     for name in ("fused_rmsnorm", "fused_residual_rmsnorm", "fused_qk_norm_rope"):
         if not enabled(name):
             return False
     plan = plan_of(block)
     if plan is None:
         return False
+    if plan.sp is None:
+        if ctx.pos.shape[0] != branch.shape[0]:  # a token-sharded stream needs the group's state
+            return False
+    elif not _sp_ready(plan.sp, branch, ctx):
+        return False
     if torch.is_grad_enabled() and plan.desc.hd > 128:
         return False
     return True
+
+
+# --------------------------------------------------------------------------- token-sharded stream
+def _sp_ready(st, branch, ctx) -> bool:
+    """The runner drives the fused tensor-parallel GEMMs only on peer memory with bf16
+    accumulators and the device barrier, for packed batches."""
+    st.bind(branch.device)
+    if not (st.fused and st.rs_bf16 and enabled("tp_block_runner")):
+        return False
+    if ctx.plan.cu_seqlens is None or branch.shape[0] * st.world < ctx.pos.shape[0]:
+        return False
+    return st.token().pad is not None
+
+
+def _tp_struct(st, rows: int, H: int):
+    """The group's symmetric buffers and counters as the runner's struct, plus what to advance
+    after the call. Buffers are created (a rendezvous of the group) on first use or growth; every
+    rank gets here with the same shapes."""
+    buf, rs, tok = st.ag_buf(rows, H), st.rs_buf(rows, H), st.token()
+    fl = buf.flags(rows)
+    t = LbTpCtx()
+    t.world, t.rank, t.rows = st.world, st.rank, rows
+    keep = []
+    for i in range(2):
+        a, b = buf.x_sym[i].c_ptr_array(), rs.acc[i].c_ptr_array()
+        keep += [a, b]
+        t.ag_peers[i] = ctypes.cast(a, ctypes.c_void_p)
+        t.rs_peers[i] = ctypes.cast(b, ctypes.c_void_p)
+        t.ag_local[i] = buf.x_sym[i].local.data_ptr()
+        t.rs_local[i] = rs.acc[i].local.data_ptr()
+    t.ag_flags, t.ag_counter = fl[0].data_ptr(), buf.counter.data_ptr()
+    pads = tok.pad.c_ptr_array()
+    keep.append(pads)
+    t.pads = ctypes.cast(pads, ctypes.c_void_p)
+    t.bar_limit_ns = tok.limit_ns
+    t.ag_epoch, t.ag_calls = st._ag_epoch[H], fl[1]
+    t.rs_epoch, t.bar_epoch = rs.epoch, tok.epoch
+    t._keep = keep
+    return t, (st, H, fl, rs, tok)
+
+
+def _tp_advance(state) -> None:
+    """Each runner call makes two uses of the publication area and of the accumulators and passes
+    four barriers (see ``LbTpCtx`` in csrc/block/block.h)."""
+    st, H, fl, rs, tok = state
+    st._ag_epoch[H] += 2
+    fl[1] += 2
+    rs.epoch += 2
+    tok.epoch += 4
 
 
 # --------------------------------------------------------------------------- stream context
@@ -303,20 +388,28 @@ class _BlockFn(torch.autograd.Function):
         if residual is not None and not residual.is_contiguous():
             residual = residual.contiguous()
         has_res = residual is not None
-        nbytes = lib.lb_block_saved_bytes(ctypes.addressof(d), T, int(has_res))
+        # token-sharded stream: T is this rank's row count and the struct names the group's buffers
+        tp, tp_state = _tp_struct(plan.sp, T, H) if plan.sp is not None else (None, None)
+        tp_ptr = ctypes.addressof(tp) if tp is not None else None
+        nbytes = lib.lb_block_saved_bytes(ctypes.addressof(d), T, int(has_res), tp_ptr)
         saved = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         out = torch.empty(T, H, dtype=branch.dtype, device=dev)
         res_out = torch.empty(T, H, dtype=branch.dtype, device=dev)
         io = LbBlockIO()
+        io.tp = tp_ptr
         io.branch, io.residual = branch.data_ptr(), (residual.data_ptr() if has_res else None)
         io.out, io.res_out, io.saved = out.data_ptr(), res_out.data_ptr(), saved.data_ptr()
         sctx.stream = nv.stream_ptr()
         rc = lib.lb_block_fwd(ctypes.addressof(d), ctypes.addressof(sctx), ctypes.addressof(io))
         if rc != 0:
             nv.check_rc(rc, "lb_block_fwd")
+        if tp is not None:
+            _tp_advance(tp_state)
+        calls["tp" if tp is not None else "dp"] += 1
         n = plan._launches.get(("f", sctx.packed))
         if n is None:
-            n = lib.lb_block_fwd_launches(ctypes.addressof(d), ctypes.addressof(sctx), int(has_res))
+            n = lib.lb_block_fwd_launches(ctypes.addressof(d), ctypes.addressof(sctx), int(has_res),
+                                          tp_ptr)
             plan._launches[("f", sctx.packed)] = n
         nv.count_launch(n)
         ctx.save_for_backward(branch, residual, saved, res_out)
@@ -350,9 +443,12 @@ class _BlockFn(torch.autograd.Function):
                 temps.append(None)
             grads[id(p)] = mg.data_ptr()
         d = plan.fill(grads)
-        work = _work_arena(lib.lb_block_work_bytes(ctypes.addressof(d), T), dev)
+        tp, tp_state = _tp_struct(plan.sp, T, H) if plan.sp is not None else (None, None)
+        tp_ptr = ctypes.addressof(tp) if tp is not None else None
+        work = _work_arena(lib.lb_block_work_bytes(ctypes.addressof(d), T, tp_ptr), dev)
         dx = torch.empty(T, H, dtype=branch.dtype, device=dev)
         io = LbBlockIO()
+        io.tp = tp_ptr
         io.branch = branch.data_ptr()
         io.residual = residual.data_ptr() if residual is not None else None
         io.res_out, io.saved = res_out.data_ptr(), saved.data_ptr()
@@ -363,10 +459,12 @@ class _BlockFn(torch.autograd.Function):
         rc = lib.lb_block_bwd(ctypes.addressof(d), ctypes.addressof(sctx), ctypes.addressof(io))
         if rc != 0:
             nv.check_rc(rc, "lb_block_bwd")
+        if tp is not None:
+            _tp_advance(tp_state)
         key = ("b", sctx.packed, len(grads))
         n = plan._launches.get(key)
         if n is None:
-            n = lib.lb_block_bwd_launches(ctypes.addressof(d), ctypes.addressof(sctx))
+            n = lib.lb_block_bwd_launches(ctypes.addressof(d), ctypes.addressof(sctx), tp_ptr)
             plan._launches[key] = n
         nv.count_launch(n)
         pgrads = tuple(None if t is None else t.to(p.dtype) for t, p in zip(temps, plan.params))

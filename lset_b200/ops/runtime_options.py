@@ -22,6 +22,7 @@ class RuntimeOptions:
     fused_qk_norm_rope: bool = True
     fused_double_rmsnorm: bool = True
     block_runner: bool = True       # whole decoder blocks issued by the native block runner
+    tp_block_runner: bool = True    # ... also tensor-parallel blocks on a token-sharded stream
     fused_glu_gemm: bool = False    # gated-MLP activation in the epilogue of the gate/up GEMM (measured slower: off)
     attention_backend: str = "auto"  # auto | native | sdpa
 
@@ -35,6 +36,7 @@ _ENV = {
     "fused_double_rmsnorm": "LSET_DISABLE_FUSED_DOUBLE_RMSNORM",
     "fused_glu_gemm": "LSET_DISABLE_FUSED_GLU_GEMM",
     "block_runner": "LSET_DISABLE_BLOCK_RUNNER",
+    "tp_block_runner": "LSET_DISABLE_TP_BLOCK_RUNNER",
 }
 
 options = RuntimeOptions()

@@ -1,6 +1,6 @@
 """Worker for engine-level multi-GPU equivalence tests (one rank per GPU under torch.distributed.run).
 
-    mgpu_engine_worker.py OUT DP TP STEPS [zero3] [async_tp]
+    mgpu_engine_worker.py OUT DP TP STEPS [zero3] [async_tp] [no_tp_runner]
 
 Trains a small Qwen3 embedder for STEPS optimizer steps on a fixed global batch sequence (16 pairs
 per step, split over the DP ranks; the ranks of one tensor-parallel group see the same pairs) and
@@ -31,6 +31,10 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     cfg = Qwen3Config(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
                       num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    if "no_tp_runner" in flags:   # tensor-parallel blocks op by op instead of one native call each
+        from lset_b200.ops.runtime_options import configure
+
+        configure(tp_block_runner=False)
     per = GLOBAL_PAIRS // dp
     eng = TrainingEngine("qwen3", None, None, dp_size=dp, tp_size=tp, batch_size=per, lr=1e-3,
                          packed=True, model_config=cfg, fused_projections=True, log_interval=0,
@@ -58,8 +62,10 @@ def main():
     mem = eng.store.memory_report() if hasattr(eng.store, "memory_report") else {}
     if rank == 0:
         with open(out_path, "w") as f:
+            from lset_b200.ops import block as block_ops
+
             json.dump({"losses": losses, "norms": norms, "fingerprint": finger, "memory": mem,
-                       "symm": bool(eng.store.use_symm)}, f)
+                       "symm": bool(eng.store.use_symm), "runner_calls": dict(block_ops.calls)}, f)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -431,3 +431,40 @@ def test_run_eval_with_a_stand_in_for_mteb(tmp_path, monkeypatch, capsys):
     assert set(scores) == {"STSBenchmark", "SICK-R"} and all(-1.0 <= v <= 1.0 for v in scores.values())
     out = capsys.readouterr().out
     assert "STSBenchmark: main_score=" in out and "SICK-R: main_score=" in out
+
+
+@pytest.mark.parametrize("tag,options", [
+    ("padded_ac_accum", ["--distributed.dp_size", "2", "--packing.enabled", "false",
+                         "--activation_checkpoint.enabled", "true",
+                         "--activation_checkpoint.mode", "full",
+                         "--training.gradient_accumulation_steps", "2"]),
+    ("gradcache_lora_tp2", ["--distributed.dp_size", "2", "--distributed.tp_size", "2",
+                            "--grad_cache.enabled", "true", "--grad_cache.token_budget", "150",
+                            "--lora.enabled", "true", "--lora.r", "4"]),
+])
+def test_parameter_sharded_mode_combines_with_other_options(tmp_path, tag, options):
+    """``distributed.reshard_after_forward`` (layers hold 1/W of parameters and gradients) logs
+    the losses of the resident mode when combined with padded batches, activation checkpointing
+    and accumulation, and with GradCache, LoRA and tensor parallelism."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positives": [" ".join(WORDS[(i + j) % 16] for j in range(12))],
+                                 "negatives": [" ".join(WORDS[(i + 3 * j) % 16] for j in range(9))]}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+    logged = {}
+    for mode in ("false", "true"):
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--data.num_hard_negatives", "1",
+                  "--training.batch_size", "4", "--training.max_steps", "4", "--training.lr", "1e-3",
+                  "--packing.enabled", "true", "--checkpoint.save_steps", "0",
+                  "--checkpoint.output_dir", str(tmp_path / f"out_{mode}"),
+                  "--logging.log_interval", "1", "--distributed.reshard_after_forward", mode,
+                  *options])
+        assert r.returncode == 0, r.stderr[-2000:]
+        logged[mode] = [float(tok.split("=")[1]) for line in r.stdout.splitlines()
+                        if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
+    assert len(logged["true"]) >= 2 and logged["true"] == pytest.approx(logged["false"], abs=2e-3), logged

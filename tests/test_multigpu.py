@@ -124,7 +124,14 @@ def test_engine_layouts_train_like_one_gpu(tmp_path):
     one = _run_engine(tmp_path, "one", 1, 1, 0)
     n = torch.cuda.device_count()
     _same_training(one, _run_engine(tmp_path, "dp2", 2, 1, 29661), dp_b=2)
-    _same_training(one, _run_engine(tmp_path, "tp2", 1, 2, 29662, "async_tp"))
+    tp2 = _run_engine(tmp_path, "tp2", 1, 2, 29662, "async_tp")
+    _same_training(one, tp2)
+    # the tensor-parallel blocks went through the native block runner (one call per block and
+    # direction), and they train like the same blocks issued op by op
+    assert tp2["runner_calls"]["tp"] > 0 and one["runner_calls"]["tp"] == 0, tp2["runner_calls"]
+    by_op = _run_engine(tmp_path, "tp2ops", 1, 2, 29666, "async_tp", "no_tp_runner")
+    assert by_op["runner_calls"]["tp"] == 0
+    _same_training(by_op, tp2, tol=1e-2)
     if n >= 4:
         _same_training(one, _run_engine(tmp_path, "dp2tp2", 2, 2, 29663, "async_tp"), dp_b=2)
         _same_training(one, _run_engine(tmp_path, "dp4", 4, 1, 29664), dp_b=4)
