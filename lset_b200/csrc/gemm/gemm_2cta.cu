@@ -50,9 +50,11 @@ constexpr int TMEM_COLS = 2 * BNp;
 
 struct Args2 {
   int M, N, K;
+  int K2;           // contraction length of the second operand pair (0: none); its k-blocks follow
+                    // those of the first pair (rank-r adapter terms appended to the base product)
   void* C;
   long long ldc;
-  int accumulate;   // fp32 output only: C += result (red.global.add)
+  int accumulate;   // C += result (red.global.add: fp32 scalars or packed bf16 pairs)
   int splits, kb_per_split;
   int raster_m_fast;
   int* status;
@@ -136,6 +138,12 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar, uint32_t peer_r
                : "memory");
 }
 
+__device__ __forceinline__ void red_add8_bf16(void* dst, const uint4& v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
                "f"(d)
@@ -145,7 +153,8 @@ __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, 
 template <int A_MN, int B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     Args2 g) {
+                     const __grid_constant__ CUtensorMap tmA2,
+                     const __grid_constant__ CUtensorMap tmB2, Args2 g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -173,6 +182,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (g.K2 > 0) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
   }
   if (warp == 1) {
     tmem_alloc2(tmem_slot, TMEM_COLS);
@@ -186,7 +199,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int tiles_m = (g.M + 2 * BMc - 1) / (2 * BMc);
   const int tiles_n = (g.N + BNp - 1) / BNp;
-  const int kb_total = (g.K + BK - 1) / BK;
+  const int kb_first = (g.K + BK - 1) / BK;                    // k-blocks of the first operand pair
+  const int kb_total = kb_first + (g.K2 + BK - 1) / BK;
   const int total = tiles_m * tiles_n * g.splits;
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -218,20 +232,23 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           const uint32_t bar = map_to_cta(&full[stage], 0);
-          const int kc = kb * BK;
+          const bool second = kb >= kb_first;   // past the first pair: rows beyond K2 read as zero
+          const CUtensorMap* ta = second ? &tmA2 : &tmA;
+          const CUtensorMap* tb = second ? &tmB2 : &tmB;
+          const int kc = (second ? kb - kb_first : kb) * BK;
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BMc / 64; ++c)
-              tma_load_2d_pair(sa + c * (BK * 128), &tmA, bar, m0 + 64 * c, kc);
+              tma_load_2d_pair(sa + c * (BK * 128), ta, bar, m0 + 64 * c, kc);
           } else {
-            tma_load_2d_pair(sa, &tmA, bar, kc, m0);
+            tma_load_2d_pair(sa, ta, bar, kc, m0);
           }
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < BNh / 64; ++c)
-              tma_load_2d_pair(sb + c * (BK * 128), &tmB, bar, nb + 64 * c, kc);
+              tma_load_2d_pair(sb + c * (BK * 128), tb, bar, nb + 64 * c, kc);
           } else {
-            tma_load_2d_pair(sb, &tmB, bar, kc, nb);
+            tma_load_2d_pair(sb, tb, bar, kc, nb);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -342,9 +359,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; i < 4; ++i) {
               const int lr = i * 8 + rr;
               const int grow = m0 + q * 32 + lr;
-              if (grow < g.M)
-                *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) =
-                    *reinterpret_cast<const uint4*>(sblk + lr * 80 + cc * 16);
+              if (grow < g.M) {
+                OutT* dst = Cout + static_cast<long long>(grow) * g.ldc + colb;
+                const uint4 pk = *reinterpret_cast<const uint4*>(sblk + lr * 80 + cc * 16);
+                if (g.accumulate)
+                  red_add8_bf16(dst, pk);
+                else
+                  *reinterpret_cast<uint4*>(dst) = pk;
+              }
             }
           }
           __syncwarp();
@@ -401,8 +423,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 int g_max_pairs = 0;
 
 template <int A_MN, int B_MN, typename OutT>
-int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args2& g, long long total,
-            cudaStream_t stream) {
+int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
+            const CUtensorMap& tmB2, const Args2& g, long long total, cudaStream_t stream) {
   auto kern = gemm_2cta_kernel<A_MN, B_MN, OutT>;
   static bool configured = false;
   if (!configured) {
@@ -435,7 +457,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Args2& g, long
   }
   const int pairs = (int)(total < g_max_pairs ? total : g_max_pairs);
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, g) == cudaSuccess ? 0 : -11;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2, tmB2, g) == cudaSuccess ? 0 : -11;
 }
 
 int sm_count() {
@@ -452,25 +474,26 @@ int sm_count() {
 }  // namespace
 }  // namespace lb
 
-// Same contract as lb_gemm_bf16 without bias and with splits given explicitly (>= 1). Returns
-// -6 for shapes this kernel does not take (the caller then uses the one-CTA kernel).
-extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K,
-                                 long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
-                                 int out_fp32, int accumulate, int splits, int* status,
-                                 void* stream_) {
-  using namespace lb;
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+namespace lb {
+namespace {
+
+// C[M, N] = or += A · op(B) (+ A2 · op(B2) when K2 > 0; A2 is K-major like A, B2 laid out like B).
+int run2(const void* A, const void* B, const void* A2, const void* B2, void* C, int M, int N, int K,
+         int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
+         int a_mn, int b_mn, int out_fp32, int accumulate, int splits, int* status,
+         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return -4;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -3;
-  if (!out_fp32 && ((ldc & 7) || accumulate || splits > 1)) return -5;
-  const int kb_total = (K + BK - 1) / BK;
+  if (!out_fp32 && ((ldc & 7) || splits > 1)) return -5;
+  if (K2 > 0 && (a_mn || splits > 1 || (K2 & 7) || (lda2 & 7) || (ldb2 & 7))) return -5;
+  const int kb_total = (K + BK - 1) / BK + (K2 > 0 ? (K2 + BK - 1) / BK : 0);
   if (splits < 1) splits = 1;
   if (splits > kb_total) splits = kb_total;
   const int kb_per = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per - 1) / kb_per;
   if (splits > 1) accumulate = 1;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
   int rc;
   if (a_mn)
     rc = make_tmap_2d(&tmA, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, true);
@@ -482,12 +505,25 @@ extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, i
   else
     rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BNh, true);
   if (rc) return rc;
+  if (K2 > 0) {
+    rc = make_tmap_2d(&tmA2, A2, 2, (uint64_t)K2, (uint64_t)M, (uint64_t)lda2 * 2, BK, BMc, true);
+    if (rc) return rc;
+    if (b_mn)
+      rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)N, (uint64_t)K2, (uint64_t)ldb2 * 2, 64, BK, true);
+    else
+      rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)K2, (uint64_t)N, (uint64_t)ldb2 * 2, BK, BNh, true);
+    if (rc) return rc;
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
   const int tiles_m = (M + 2 * BMc - 1) / (2 * BMc);
   const int tiles_n = (N + BNp - 1) / BNp;
   Args2 g{};
   g.M = M;
   g.N = N;
   g.K = K;
+  g.K2 = K2 > 0 ? K2 : 0;
   g.C = C;
   g.ldc = ldc;
   g.accumulate = accumulate;
@@ -496,14 +532,38 @@ extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, i
   g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
   g.status = status;
   const long long total = 1LL * tiles_m * tiles_n * splits;
-#define LB2(AM, BMJ)                                                             \
-  (out_fp32 ? launch2<AM, BMJ, float>(tmA, tmB, g, total, stream)               \
-            : launch2<AM, BMJ, __nv_bfloat16>(tmA, tmB, g, total, stream))
+#define LB2(AM, BMJ)                                                                    \
+  (out_fp32 ? launch2<AM, BMJ, float>(tmA, tmB, tmA2, tmB2, g, total, stream)          \
+            : launch2<AM, BMJ, __nv_bfloat16>(tmA, tmB, tmA2, tmB2, g, total, stream))
   if (!a_mn && !b_mn) return LB2(0, 0);
   if (!a_mn && b_mn) return LB2(0, 1);
   if (a_mn && b_mn) return LB2(1, 1);
   return LB2(1, 0);
 #undef LB2
+}
+
+}  // namespace
+}  // namespace lb
+
+// Same contract as lb_gemm_bf16 without bias and with splits given explicitly (>= 1); a bf16
+// output may be accumulated into (packed red.global.add, unsplit only). Returns -5 / -6 for forms
+// this kernel does not take (the caller then uses the one-CTA kernel).
+extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                 int out_fp32, int accumulate, int splits, int* status,
+                                 void* stream_) {
+  return lb::run2(A, B, nullptr, nullptr, C, M, N, K, 0, lda, ldb, 0, 0, ldc, a_mn, b_mn, out_fp32,
+                  accumulate, splits, status, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// Same contract as lb_gemm_bf16_ext without bias: bf16 C = A · op(B) + A2 · op(B2).
+extern "C" int lb_gemm_bf16_2cta_ext(const void* A, const void* B, const void* A2, const void* B2,
+                                     void* C, int M, int N, int K, int K2, long long lda,
+                                     long long ldb, long long lda2, long long ldb2, long long ldc,
+                                     int b_mn, int* status, void* stream_) {
+  if (K2 <= 0) return -4;
+  return lb::run2(A, B, A2, B2, C, M, N, K, K2, lda, ldb, lda2, ldb2, ldc, 0, b_mn, 0, 0, 1, status,
+                  reinterpret_cast<cudaStream_t>(stream_));
 }
 
 // CTA pairs resident at once (the slots of the caller's split heuristic); SMs / 2 until the first

@@ -910,10 +910,15 @@ extern "C" int lb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, i
                                  long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
                                  int out_fp32, int accumulate, int splits, int* status,
                                  void* stream_);
+extern "C" int lb_gemm_bf16_2cta_ext(const void* A, const void* B, const void* A2, const void* B2,
+                                     void* C, int M, int N, int K, int K2, long long lda,
+                                     long long ldb, long long lda2, long long ldb2, long long ldc,
+                                     int b_mn, int* status, void* stream_);
 extern "C" int lb_gemm_2cta_pairs();
 
-// The plain products (no bias, no peer scatter, at least one 256 x 256 tile) run on the CTA-pair
-// kernel of gemm_2cta.cu: the same speed per kernel within a few percent, at less shared-memory
+// The plain products (no bias, no scatter to other GPUs, at least one 256 x 256 tile), those with
+// a second operand pair appended to the contraction and the bf16 accumulation into a local buffer
+// run on the CTA-pair kernel of gemm_2cta.cu: the same speed per kernel within a few percent, at less shared-memory
 // traffic per FLOP, which under the power cap is worth about 3 % of a training step.
 // LSET_B200_GEMM_2CTA=0 (or lb_gemm_use_2cta(0)) keeps everything on the one-CTA kernel.
 static int g_use_2cta = -1;
@@ -947,6 +952,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
 
   const int tiles_m = (M + BM - 1) / BM;
   const int sms = num_sms();
+  if (use_2cta() && bias == nullptr && scatter && c_world == 1 && !out_fp32 && bn == 0 &&
+      M >= 256 && N >= 256)  // "scatter" to this GPU only: C += A · op(B) in bf16
+    return lb_gemm_bf16_2cta(A, B, const_cast<void*>(c_peers[0]), M, N, K, lda, ldb, ldc, a_mn,
+                             b_mn, 0, 1, 1, status, stream_);
   if (use_2cta() && bias == nullptr && !scatter && bn == 0 && M >= 256 && N >= 256) {
     int s2 = splits;
     if (s2 == 0) {
@@ -1284,6 +1293,9 @@ extern "C" int lb_gemm_bf16_ext(const void* A, const void* B, const void* A2, co
   if (K <= 0 || K2 <= 0) return -4;
   if ((N & 7) || (K2 & 7) || (lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7) || (ldc & 7))
     return -3;
+  if (use_2cta() && bias == nullptr && M >= 256 && N >= 256)
+    return lb_gemm_bf16_2cta_ext(A, B, A2, B2, C, M, N, K, K2, lda, ldb, lda2, ldb2, ldc, b_mn,
+                                 status, stream_);
   const int tiles_m = (M + BM - 1) / BM;
   const int bn = N > 128 ? 256 : 128;
   const int tiles_n = (N + bn - 1) / bn;
