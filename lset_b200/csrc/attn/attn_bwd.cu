@@ -298,43 +298,35 @@ __global__ void __launch_bounds__(kBwdThreads)
       failed = true;
     }
   }
+  // One CTA-wide barrier per KV block (before the dQ product is issued). Thread 0 alone waits for
+  // the loads and for the dQ product that frees the K / V slot; every thread waits for the score
+  // products itself; whether a wait ran out anywhere is agreed on at the barrier.
   for (int j = 0; j < nblk && !failed; ++j) {
-    {
-      const bool ok = mbar_wait(bar_kv, j & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutProducer);
-        failed = true;
-        break;
-      }
-    }
+    bool ok = true;
     if (tid == 0) {
-      tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      ok = mbar_wait(bar_kv, j & 1);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
+        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-        const uint32_t boff = (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32;
-        umma_bf16(tmem_base, umma_smem_desc(qa + aoff, 16, 1024), umma_smem_desc(ka + boff, 16, 1024),
-                  idesc_s, ks > 0 ? 1u : 0u);
-      }
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
+          const uint32_t boff = (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32;
+          umma_bf16(tmem_base, umma_smem_desc(qa + aoff, 16, 1024),
+                    umma_smem_desc(ka + boff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        }
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-        const uint32_t boff = (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32;
-        umma_bf16(tmem_base + 64, umma_smem_desc(da + aoff, 16, 1024),
-                  umma_smem_desc(va + boff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_s);
-    }
-    {
-      const bool ok = mbar_wait(bar_s, j & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t aoff = (ks / 4) * (128 * 128) + (ks % 4) * 32;
+          const uint32_t boff = (ks / 4) * (kAttnKvBlock * 128) + (ks % 4) * 32;
+          umma_bf16(tmem_base + 64, umma_smem_desc(da + aoff, 16, 1024),
+                    umma_smem_desc(va + boff, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s);
       }
     }
+    ok = ok && mbar_wait(bar_s, j & 1);
     tc_fence_after();
     float ds[32];
     {
@@ -354,7 +346,11 @@ __global__ void __launch_bounds__(kBwdThreads)
     st_half_row_bf16_swz(sdS, r, half, ds);
     fence_proxy_async_smem();
     tc_fence_before();
-    __syncthreads();
+    if (__syncthreads_or(!ok)) {
+      report_status(a.status, kStatusTimeoutMma);
+      failed = true;
+      break;
+    }
     if (tid == 0) {
       tc_fence_after();
       const uint32_t sa = smem_u32(sdS);
@@ -365,17 +361,22 @@ __global__ void __launch_bounds__(kBwdThreads)
                   umma_smem_desc(ka + ks * 2048, kAttnKvBlock * 128, 1024), idesc_dq,
                   (j > 0 || ks > 0) ? 1u : 0u);
       umma_commit(bar_dq);
-    }
-    // the K block and the dS/V slot are in use until this block's dQ product is done
-    {
-      const bool ok = mbar_wait(bar_dq, j & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
+      // the K block and the dS / V slot are in use until this block's dQ product is done; a wait
+      // that runs out here leaves the next block unloaded, and its wait then fails for everybody
+      if (j + 1 < nblk) {
+        if (mbar_wait(bar_dq, j & 1))
+          load_kv(j + 1);
+        else
+          report_status(a.status, kStatusTimeoutMma);
       }
     }
-    if (tid == 0 && j + 1 < nblk) load_kv(j + 1);
+  }
+  if (!failed) {
+    const bool ok = mbar_wait(bar_dq, (nblk - 1) & 1);
+    if (__syncthreads_or(!ok)) {
+      report_status(a.status, kStatusTimeoutMma);
+      failed = true;
+    }
   }
   if (!failed) {
     tc_fence_after();
@@ -526,6 +527,17 @@ __global__ void __launch_bounds__(kDkvThreads)
   const int kvpos = kv0 + r;
   const bool row_valid = kvpos < len;
   bool failed = false;
+  // lse / delta of a block's 64 queries (read by every row), staged one step ahead
+  auto stage_stats = [&](int i) {
+    if (tid < 64) {
+      const int qp = (qb_start + i / G) * 64 + tid;
+      const int head = hk * G + i % G;
+      const bool v = qp < len;
+      sStat[(i & 1) * 128 + tid] = v ? a.lse[1LL * head * a.T + seq0 + qp] * kLog2eF : 0.f;
+      sStat[(i & 1) * 128 + 64 + tid] = v ? a.delta[1LL * head * a.T + seq0 + qp] : 0.f;
+    }
+  };
+  if (n_inner > 0) stage_stats(0);
   {
     const bool ok = mbar_wait(bar_kv, 0);
     if (__syncthreads_or(!ok)) {
@@ -535,31 +547,19 @@ __global__ void __launch_bounds__(kDkvThreads)
   }
   if (!failed && tid == 0 && n_inner > 0) issue_scores(0);
 
+  // One CTA-wide barrier per step (before the accumulation products are issued). Every thread
+  // waits on the mbarriers itself; whether a wait ran out anywhere is agreed on at that barrier.
   for (int i = 0; i < n_inner && !failed; ++i) {
     const int sb = i & 1;
     const int qbuf = i % C::QBUFS;
     const int qb = qb_start + i / G;
-    const int head = hk * G + i % G;
-    // stage this block's lse / delta (read by every row); visible after the barrier below
-    if (tid < 64) {
-      const int qp = qb * 64 + tid;
-      const bool v = qp < len;
-      sStat[sb * 128 + tid] = v ? a.lse[1LL * head * a.T + seq0 + qp] * kLog2eF : 0.f;
-      sStat[sb * 128 + 64 + tid] = v ? a.delta[1LL * head * a.T + seq0 + qp] : 0.f;
-    }
-    {
-      const bool ok = mbar_wait(&bar_s[sb], (i >> 1) & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
-      }
-    }
+    bool ok = mbar_wait(&bar_s[sb], (i >> 1) & 1);
     tc_fence_after();
     // The score products of the next step go to the tensor pipe now: their TMEM buffer was last
-    // read by step i - 1, and they then run under this step's softmax-gradient math instead of
-    // behind this step's accumulation products.
-    if (tid == 0 && i + 1 < n_inner) issue_scores(i + 1);
+    // read by step i - 1 (complete in every thread before that step's barrier), and they then run
+    // under this step's softmax-gradient math instead of behind this step's accumulation products.
+    if (tid == 0 && ok && i + 1 < n_inner) ok = issue_scores(i + 1);
+    if (i + 1 < n_inner) stage_stats(i + 1);
     float pt[16], dst[16];
     ld_row16(tmem_row + sb * 128 + quarter * 16, pt);
     ld_row16(tmem_row + sb * 128 + 64 + quarter * 16, dst);
@@ -578,20 +578,19 @@ __global__ void __launch_bounds__(kDkvThreads)
     }
     if (i > 0) {
       // previous dV/dK products done: the Pᵀ/dSᵀ tiles and ring slot (i-1) % 3 are free
-      const bool ok = mbar_wait(bar_acc, (i - 1) & 1);
-      if (__syncthreads_or(!ok)) {
-        report_status(a.status, kStatusTimeoutMma);
-        failed = true;
-        break;
-      }
+      ok = mbar_wait(bar_acc, (i - 1) & 1) && ok;
       tc_fence_after();
     }
-    if (tid == 0 && i + 2 < n_inner) load_q(i + 2);
+    if (tid == 0 && ok && i + 2 < n_inner) load_q(i + 2);
     st_quarter_row_bf16_swz(sPT, r, quarter, pt);
     st_quarter_row_bf16_swz(sdST, r, quarter, dst);
     fence_proxy_async_smem();
     tc_fence_before();
-    __syncthreads();
+    if (__syncthreads_or(!ok)) {
+      report_status(a.status, kStatusTimeoutMma);
+      failed = true;
+      break;
+    }
     if (tid == 0) {
       tc_fence_after();
       const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
