@@ -437,7 +437,11 @@ class TrainingEngine:
                     if next(batches, None) is None:
                         break
                 self._batch_in_epoch, skip = skip, 0
-                for batch in batches:
+                # The next batch is collated (and pinned) right after this step's kernels are
+                # enqueued, before the loss is read back: host-side batch preparation runs under
+                # the GPU's work instead of in the gap between two steps.
+                batch = next(batches, None)
+                while batch is not None:
                     if step >= self.max_steps:
                         break
                     made_progress = True
@@ -446,6 +450,7 @@ class TrainingEngine:
                     n_tok = batch_tokens(batch)
                     maybe_fail(step, self.rank)      # host-side fault injection (off unless asked for)
                     loss = self.train_step(batch)
+                    batch = next(batches, None) if step + 1 < self.max_steps else None
                     tp = self.logger.update_throughput(n_pairs * self.dp_size, n_tok * self.dp_size)
                     if self.log_interval and step % self.log_interval == 0:
                         value = float(global_loss_value(loss, self.dp_group))
