@@ -202,7 +202,8 @@ int lin_bwd_launches(const LbLinear& l, bool accumulate) {
 // Running counters of one call. The double-buffering rule of the symmetric areas: use e touches
 // half e & 1 and contains exactly one barrier; a half is rewritten two uses later, after the
 // barrier of the use in between, which every peer joins only after its GEMM of use e is complete
-// in stream order. Accumulator halves are cleared right after they are read.
+// in stream order. A reduce-scatter half is read (its slots summed) right after the barrier of
+// its use and rewritten two uses later under the same rule.
 struct TpRun {
   const LbTpCtx* t;
   unsigned ag_epoch, ag_calls, rs_epoch, bar_epoch;
@@ -246,17 +247,17 @@ int tp_ag_gemm(TpRun& r, const __nv_bfloat16* shard, __nv_bfloat16* x_all, const
                          c->status, c->stream);
 }
 
-// out[rows, N] = reduce_scatter(a[Tp, K] · op(w)): every rank adds its partial rows into the
-// owner's accumulator from the GEMM epilogue; the owner reads and clears it after the barrier.
+// out[rows, N] = reduce_scatter(a[Tp, K] · op(w)): every rank stores its partial rows into its
+// own slot of the owner's area from the GEMM epilogue; the owner sums its slots after the barrier.
 int tp_gemm_rs(TpRun& r, const __nv_bfloat16* a, long long lda, const LbLinear& l, int b_mn,
                __nv_bfloat16* out, int N, int K, const LbStreamCtx* c) {
   const LbTpCtx* t = r.t;
   ++r.rs_epoch;
   const int half = r.rs_epoch & 1;
-  LB_TRY(lb_gemm_bf16_scatter16(a, l.w, t->rs_peers[half], t->world, t->rows, tp_tokens(t), N, K,
-                                lda, l.ldw, N, 0, b_mn, 0, c->status, c->stream));
+  LB_TRY(lb_gemm_bf16_push16(a, l.w, t->rs_peers[half], t->world, t->rows, tp_tokens(t), N, K, lda,
+                             l.ldw, N, 0, b_mn, 0, c->status, c->stream));
   LB_TRY(tp_barrier(r, c));  // every contribution has landed
-  return lb_take_clear(t->rs_local[half], out, (long long)t->rows * N, 0, c->stream);
+  return lb_take_sum(t->rs_local[half], out, (long long)t->rows * N, t->world, c->stream);
 }
 
 bool tp_shape_ok(const LbBlockDesc* d, const LbStreamCtx* c, const LbTpCtx* t) {

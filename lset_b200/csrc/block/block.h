@@ -82,8 +82,8 @@ struct LbStreamCtx {
 // gather the shards of all ranks inside their GEMM and the row-parallel ones (o_proj, down) reduce
 // and scatter their output from the GEMM epilogue. The descriptor then carries this rank's head
 // and FFN-column counts. Buffers live in symmetric memory owned by the caller: a publication area
-// of width H (two halves used alternately, one use per gathered GEMM) and bf16 accumulators of
-// width H (two halves, one use per reduced GEMM). Each of the forward and the backward call makes
+// of width H (two halves used alternately, one use per gathered GEMM) and bf16 reduce-scatter
+// areas of width H with one slot per source rank (two halves, one use per reduced GEMM). Each of the forward and the backward call makes
 // exactly two uses of either and four device barriers; the caller advances its counters by those
 // amounts after the call.
 struct LbTpCtx {
@@ -94,8 +94,8 @@ struct LbTpCtx {
   void* ag_local[2];               // this rank's half
   unsigned* ag_flags;              // arrival flags of the pulled row tiles (for this row count)
   unsigned* ag_counter;            // work counter of the gather GEMM
-  const void* const* rs_peers[2];  // per half: host array of `world` accumulator pointers
-  void* rs_local[2];
+  const void* const* rs_peers[2];  // per half: per destination rank, this rank's slot in its area
+  void* rs_local[2];               // this rank's area: world slots of rows * H elements
   const void* const* pads;         // device-barrier flag pads of every rank
   unsigned long long bar_limit_ns;
   unsigned ag_epoch;               // uses of the publication area before this call

@@ -295,8 +295,52 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// out[i] = sum over w of slots[w * n + i] (bf16 slots, fp32 sum in slot order, bf16 result).
+template <int W>
+__global__ void __launch_bounds__(256)
+    take_sum_kernel(const bf16* __restrict__ slots, bf16* __restrict__ out, long long n8) {
+  for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += 1LL * gridDim.x * blockDim.x) {
+    uint4 part[W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) part[w] = *reinterpret_cast<const uint4*>(slots + (w * n8 + i) * 8);
+    float v[8];
+    unpack8(part[0], v);
+#pragma unroll
+    for (int w = 1; w < W; ++w) {
+      float u[8];
+      unpack8(part[w], u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += u[j];
+    }
+    st16(out + 8 * i, pack8(v));
+  }
+}
+
 }  // namespace
 }  // namespace lb
+
+// slots: world x n bf16 (slot w holds rank w's partial result), out: n bf16; n a multiple of 8.
+extern "C" int lb_take_sum(const void* slots, void* out, long long n, int world, void* stream) {
+  using namespace lb;
+  if (n <= 0) return 0;
+  if ((n & 7) || world < 1 || world > 8) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = comm_grid(n / 8);
+  const bf16* s = reinterpret_cast<const bf16*>(slots);
+  bf16* o = reinterpret_cast<bf16*>(out);
+  switch (world) {
+    case 1: take_sum_kernel<1><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 2: take_sum_kernel<2><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 3: take_sum_kernel<3><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 4: take_sum_kernel<4><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 5: take_sum_kernel<5><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 6: take_sum_kernel<6><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    case 7: take_sum_kernel<7><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+    default: take_sum_kernel<8><<<grid, 256, 0, st>>>(s, o, n / 8); break;
+  }
+  return launch_rc();
+}
 
 // acc: n elements (fp32 when acc_fp32, else bf16), out: n bf16; n a multiple of 8, both 16-byte
 // aligned.

@@ -65,6 +65,9 @@ int lb_gemm_bf16_scatter16(const void* A, const void* B, const void* const* c_pe
                            int rows_per_peer, int M, int N, int K, long long lda, long long ldb,
                            long long ldc, int a_mn, int b_mn, int bn, int* status, void* stream);
 
+int lb_gemm_bf16_push16(const void* A, const void* B, const void* const* c_peers, int world,
+                        int rows_per_peer, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int a_mn, int b_mn, int bn, int* status, void* stream);
 int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const void* B, void* C, int rows_local,
                     int world, int rank, int N, int K, long long lda, long long ldb, long long ldc,
                     int b_mn, const void* bias, unsigned* flags, unsigned* counter, unsigned epoch,
@@ -74,5 +77,6 @@ int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const void* B, void
 int lb_device_barrier(const void* const* pads, int world, int rank, unsigned epoch,
                       unsigned long long limit_ns, int* status, void* stream);
 int lb_take_clear(void* acc, void* out, long long n, int acc_fp32, void* stream);
+int lb_take_sum(const void* slots, void* out, long long n, int world, void* stream);
 
 }  // extern "C"

@@ -106,6 +106,8 @@ struct GemmArgs {
   // is reduced into that rank's buffer with red.global.add over NVLink.
   void* c_peers[8];
   int c_rows_per_peer;        // 0 = C is a single local matrix
+  int c_store;                // bf16 scatter: plain stores (every source rank owns a slot of the
+                              // destination, summed by the owner afterwards) instead of reductions
   // ---- 8-bit float operands (F8 kernels): the accumulator of element (r, c) is multiplied by
   // f8_sa[r * f8_sa_stride] * f8_sb[c * f8_sb_stride] (the operands' dequantisation factors; a
   // stride of 0 is one factor for the whole tensor). Operand formats: 0 = e4m3, 1 = e5m2.
@@ -733,7 +735,10 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
                   // reduce-scatter in bf16: the row's owner accumulates over NVLink
                   OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
                                static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
-                  red_add8_bf16(base + colb, pk);
+                  if (g.c_store)
+                    *reinterpret_cast<uint4*>(base + colb) = pk;
+                  else
+                    red_add8_bf16(base + colb, pk);
                 } else {
                   *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
                 }
@@ -762,7 +767,10 @@ __global__ void __launch_bounds__(gemm_threads<EPI, GATHER, F8>(), 1)
                     // reduce-scatter in bf16: the row's owner accumulates over NVLink
                     OutT* base = reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
                                  static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc;
-                    red_add8_bf16(base + colb, pk);
+                    if (g.c_store)
+                      *reinterpret_cast<uint4*>(base + colb) = pk;
+                    else
+                      red_add8_bf16(base + colb, pk);
                   } else {
                     *reinterpret_cast<uint4*>(Cout + static_cast<long long>(grow) * g.ldc + colb) = pk;
                   }
@@ -939,7 +947,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
                           int out_fp32, int accumulate, const void* bias, int splits, int bn,
                           int* status, void* stream_, const void* const* c_peers, int c_world,
-                          int c_rows_per_peer) {
+                          int c_rows_per_peer, int c_store = 0) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -952,7 +960,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
 
   const int tiles_m = (M + BM - 1) / BM;
   const int sms = num_sms();
-  if (use_2cta() && bias == nullptr && scatter && c_world == 1 && !out_fp32 && bn == 0 &&
+  if (use_2cta() && bias == nullptr && scatter && c_world == 1 && !c_store && !out_fp32 &&
+      bn == 0 &&
       M >= 256 && N >= 256)  // "scatter" to this GPU only: C += A · op(B) in bf16
     return lb_gemm_bf16_2cta(A, B, const_cast<void*>(c_peers[0]), M, N, K, lda, ldb, ldc, a_mn,
                              b_mn, 0, 1, 1, status, stream_);
@@ -1013,6 +1022,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     if (c_world > 8) return -3;
     for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);
     g.c_rows_per_peer = c_rows_per_peer;
+    g.c_store = c_store;
     g.accumulate = 1;
   }
   const long long total = 1LL * tiles_m * tiles_n * splits;
@@ -1240,6 +1250,21 @@ extern "C" int lb_gemm_bf16_scatter16(const void* A, const void* B, const void* 
   if (M != world * rows_per_peer) return -3;
   return gemm_bf16_impl(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, 1, bn,
                         status, stream_, c_peers, world, rows_per_peer);
+}
+
+// Reduce-scatter without reductions on the wire: as lb_gemm_bf16_scatter16, but every output row
+// is *stored* (plain 16-byte stores) at local row r % rows_per_peer of c_peers[r / rows_per_peer].
+// The caller passes, for every destination rank, the address of the slot that belongs to this
+// (source) rank inside that rank's buffer of `world` slots; the owner sums its slots afterwards
+// (lb_take_sum). Stores pack into larger NVLink packets than reductions do, nothing has to be
+// cleared, and the sum has a fixed order.
+extern "C" int lb_gemm_bf16_push16(const void* A, const void* B, const void* const* c_peers,
+                                   int world, int rows_per_peer, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int a_mn, int b_mn, int bn,
+                                   int* status, void* stream_) {
+  if (M != world * rows_per_peer) return -3;
+  return gemm_bf16_impl(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, 1, bn,
+                        status, stream_, c_peers, world, rows_per_peer, 1);
 }
 
 // Gated-MLP input projection with the activation in the epilogue: gate_up [M, 2I] = A · Wᵀ for the

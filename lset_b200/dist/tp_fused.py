@@ -63,15 +63,31 @@ class _AGBuf:
 
 
 class _RSBuf:
-    """Double-buffered accumulators of width N (any row count up to cap), fp32 or bf16."""
+    """Double-buffered reduce-scatter areas of width N (any row count up to cap).
+
+    bf16: every rank holds one slot per source rank; a GEMM *stores* its partial rows for rank r
+    into its own slot of rank r's area and the owner sums the slots (no reductions on the wire,
+    nothing to clear, fixed summation order). fp32: one accumulator that peers add into."""
 
     def __init__(self, cap, N, device, group, dtype=torch.float32):
         self.cap = cap
         self.dtype = dtype
-        self.acc = [symm.SymmBuffer(cap * N, dtype, device, group) for _ in range(2)]
+        self.slots = dist.get_world_size(group) if dtype == torch.bfloat16 else 1
+        self.rank = dist.get_rank(group)
+        self.acc = [symm.SymmBuffer(cap * N * self.slots, dtype, device, group) for _ in range(2)]
         for a in self.acc:
             a.local.zero_()
         self.epoch = 0
+        self._slot_ptrs = {}
+
+    def slot_ptrs(self, half: int, rows: int, N: int):
+        """Per destination rank, the address of this rank's slot in that rank's area (slots are
+        ``rows * N`` elements apart: every rank of the group calls with the same ``rows``)."""
+        key = (half, rows, N)
+        arr = self._slot_ptrs.get(key)
+        if arr is None:
+            arr = self._slot_ptrs[key] = self.acc[half].offset_ptrs(self.rank * rows * N * 2)
+        return arr
 
 
 class SPState:
@@ -205,8 +221,9 @@ def _gemm_rs(st: SPState, a, w, b_mn: bool):
     acc = buf.acc[buf.epoch & 1]
     lib = nv.load()
     if buf.dtype == torch.bfloat16:
-        rc = lib.lb_gemm_bf16_scatter16(
-            nv.c_void_p(a.data_ptr()), nv.c_void_p(w.data_ptr()), acc.c_ptr_array(), nv.c_int(W),
+        rc = lib.lb_gemm_bf16_push16(
+            nv.c_void_p(a.data_ptr()), nv.c_void_p(w.data_ptr()),
+            buf.slot_ptrs(buf.epoch & 1, rows, N), nv.c_int(W),
             nv.c_int(rows), nv.c_int(T), nv.c_int(N), nv.c_int(K), nv.c_ll(a.stride(0)),
             nv.c_ll(w.stride(0)), nv.c_ll(N), nv.c_int(0), nv.c_int(1 if b_mn else 0), nv.c_int(0),
             nv.c_void_p(nv.status_word(a.device).data_ptr()), nv.c_void_p(nv.stream_ptr()))
@@ -220,10 +237,16 @@ def _gemm_rs(st: SPState, a, w, b_mn: bool):
     nv.check_rc(rc, "lb_gemm_bf16_scatter")
     nv.count_launch(1)
     st.barrier()                                          # every contribution has landed
-    # read the reduced rows and leave the accumulator zero for its next use, in one pass
+    # read the reduced rows (fp32 accumulator: and leave it zero for its next use, in one pass)
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
     n = rows * N
-    if n % 8 == 0:
+    if buf.dtype == torch.bfloat16:
+        # sum of the W slots (each written by one rank's GEMM) in fp32, in slot order
+        rc = lib.lb_take_sum(nv.c_void_p(acc.local.data_ptr()), nv.c_void_p(out.data_ptr()),
+                             nv.c_ll(n), nv.c_int(W), nv.c_void_p(nv.stream_ptr()))
+        nv.check_rc(rc, "lb_take_sum")
+        nv.count_launch(1)
+    elif n % 8 == 0:
         rc = lib.lb_take_clear(nv.c_void_p(acc.local.data_ptr()), nv.c_void_p(out.data_ptr()),
                                nv.c_ll(n), nv.c_int(int(buf.dtype == torch.float32)),
                                nv.c_void_p(nv.stream_ptr()))

@@ -113,15 +113,40 @@ class _CrossRankInfoNCE(torch.autograd.Function):
         N = W * n_local
         lib = nv.load()
         coef = (g.float() * (inv_t / float(W * B))).reshape(1).contiguous()
-        from ..ops.loss import panel_cols
+        from ..ops.loss import PANEL_BYTES, panel_cols
 
         Bp = (B + 7) // 8 * 8
+        status = nv.status_word(q.device).data_ptr()
+        qp = q if Bp == B else torch.cat([q, q.new_zeros(Bp - B, D)])
+        if Bp * N * 2 <= PANEL_BYTES:
+            # the whole probability gradient fits one panel: one recompute over every rank's
+            # passages, one dQ product, and one dK product whose epilogue scatters each block of
+            # rows to its owner (three launches whatever the number of ranks)
+            Wm = torch.empty(Bp, N, dtype=torch.bfloat16, device=q.device)
+            if Bp != B:
+                Wm[B:].zero_()
+            rc = lib.lb_infonce_pgrad(
+                nv.c_void_p(q.data_ptr()), nv.c_ll(q.stride(0)), nv.c_void_p(buf.k_all.data_ptr()),
+                nv.c_ll(D), nv.c_int(B), nv.c_int(N), nv.c_int(D), nv.c_float(inv_t),
+                nv.c_ll(rank * n_local), nv.c_void_p(lse.data_ptr()), nv.c_void_p(coef.data_ptr()),
+                nv.c_void_p(Wm.data_ptr()), nv.c_ll(N), nv.c_void_p(status),
+                nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_infonce_pgrad")
+            dq = matmul_abt(Wm[:B], buf.k_all, b_mn=True)
+            rc = lib.lb_gemm_bf16_scatter(
+                nv.c_void_p(Wm.data_ptr()), nv.c_void_p(qp.data_ptr()), buf.dk_sym.c_ptr_array(),
+                nv.c_int(W), nv.c_int(n_local), nv.c_int(N), nv.c_int(D), nv.c_int(Bp), nv.c_ll(N),
+                nv.c_ll(D), nv.c_ll(D), nv.c_int(1), nv.c_int(1), nv.c_int(1), nv.c_int(0),
+                nv.c_void_p(status), nv.c_void_p(nv.stream_ptr()))
+            nv.check_rc(rc, "lb_gemm_bf16_scatter")
+            nv.count_launch(3)
+            buf.order_ranks()                  # every contribution has landed
+            dk = buf.dk_sym.local.view(n_local, D).to(torch.bfloat16)
+            return dq, dk, None, None
         step = min(n_local, panel_cols(B, N))
         Wm = torch.empty(Bp, step, dtype=torch.bfloat16, device=q.device)
         if Bp != B:
             Wm[B:].zero_()
-        qp = q if Bp == B else torch.cat([q, q.new_zeros(Bp - B, D)])
-        status = nv.status_word(q.device).data_ptr()
         dq32 = None
         for pk in range(W):
             peer = (rank + pk) % W                    # own passages first, then the peers in turn

@@ -318,7 +318,7 @@ def _tp_struct(st, rows: int, H: int):
     t.world, t.rank, t.rows = st.world, st.rank, rows
     keep = []
     for i in range(2):
-        a, b = buf.x_sym[i].c_ptr_array(), rs.acc[i].c_ptr_array()
+        a, b = buf.x_sym[i].c_ptr_array(), rs.slot_ptrs(i, rows, H)
         keep += [a, b]
         t.ag_peers[i] = ctypes.cast(a, ctypes.c_void_p)
         t.rs_peers[i] = ctypes.cast(b, ctypes.c_void_p)

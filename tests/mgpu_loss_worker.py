@@ -21,7 +21,13 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
     cases = []
+    from lset_b200.ops import loss as loss_ops
+
+    full_panel = (loss_ops.PANEL_BYTES, loss_ops.PANEL_MIN_COLS)
     for B, D in [(64, 1024), (264, 768), (1024, 256), (64, 1024)]:
+        # small cases take the backward in one pass over every rank's passages; the 1024-row case
+        # is made to walk four column panels per peer (the path of score matrices above the cap)
+        loss_ops.PANEL_BYTES, loss_ops.PANEL_MIN_COLS = (256 * 1024, 256) if B == 1024 else full_panel
         for rep in range(2):
             torch.manual_seed(100 * rank + rep + B)
             q = F.normalize(torch.randn(B, D, device=dev), dim=-1).to(torch.bfloat16).requires_grad_()
@@ -46,6 +52,7 @@ def main():
                 "loss_err": abs(loss.item() - share.item()) / max(1e-3, abs(share.item())),
                 "dq_err": ((q.grad.float() - dq_ref).abs().max() / (dq_ref.abs().max() + 1e-9)).item(),
                 "dk_err": ((d.grad.float() - dk_ref).abs().max() / (dk_ref.abs().max() + 1e-9)).item()})
+    loss_ops.PANEL_BYTES, loss_ops.PANEL_MIN_COLS = full_panel
     # hard negatives through the task: every rank's block is [documents; negatives]
     from lset_b200.tasks.bi_encoder import BiEncoderTask
 
