@@ -6,7 +6,7 @@
 // memory (rows 0..127 from the leader, 128..255 from the peer) and both halves of B, and leaves
 // rows 128 r .. 128 r + 127 of the fp32 accumulator in CTA r's tensor memory. Against the
 // one-CTA kernel (gemm_bf16.cu, 128 x 256 tiles) every CTA stages and reads 32 KB instead of 48 KB
-// of operands per 64-deep k-block for the same tensor-core work, which is what the kernel spends
+// of operands per 64 elements of contraction depth for the same tensor-core work, which is what the kernel spends
 // its power on when the clock is power-limited.
 //
 //   warp 0      TMA producer (own A rows, own half of B, into this CTA's shared memory; the loads
@@ -37,8 +37,14 @@ namespace {
 constexpr int BMc = 128;      // rows of A / C per CTA
 constexpr int BNp = 256;      // columns of C per pair
 constexpr int BNh = 128;      // rows of B staged per CTA
-constexpr int BK = 64;
-constexpr int kStages = 6;
+// A stage is 128 deep: per stage the producer, the MMA issuer and the barriers go through one
+// hand-over (wait, expect, commit) for eight MMAs. With 64-deep stages (six of them, the same
+// bytes in flight) the same kernel was 7-10 % slower: the hand-overs per k-block, not operand
+// delivery, were what kept the tensor pipe waiting.
+constexpr int BK = 128;       // contraction depth of one pipeline stage
+constexpr int kStages = 3;
+constexpr int BKT = 64;       // contraction depth of one TMA box of a K-major operand (one
+                              // 128-byte swizzle row); a stage holds BK / BKT such boxes
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int A_BYTES = BMc * BK * 2;
@@ -241,14 +247,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int c = 0; c < BMc / 64; ++c)
               tma_load_2d_pair(sa + c * (BK * 128), ta, bar, m0 + 64 * c, kc);
           } else {
-            tma_load_2d_pair(sa, ta, bar, kc, m0);
+#pragma unroll
+            for (int h = 0; h < BK / BKT; ++h)
+              tma_load_2d_pair(sa + h * (BMc * 128), ta, bar, kc + BKT * h, m0);
           }
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < BNh / 64; ++c)
               tma_load_2d_pair(sb + c * (BK * 128), tb, bar, nb + 64 * c, kc);
           } else {
-            tma_load_2d_pair(sb, tb, bar, kc, nb);
+#pragma unroll
+            for (int h = 0; h < BK / BKT; ++h)
+              tma_load_2d_pair(sb + h * (BNh * 128), tb, bar, kc + BKT * h, nb);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -296,10 +306,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = A_MN ? umma_smem_desc(sa + k * 2048, BK * 128, 1024)
-                                        : umma_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? umma_smem_desc(sb + k * 2048, BK * 128, 1024)
-                                        : umma_smem_desc(sb + k * 32, 16, 1024);
+            const uint64_t adesc =
+                A_MN ? umma_smem_desc(sa + k * 2048, BK * 128, 1024)
+                     : umma_smem_desc(sa + (k / 4) * (BMc * 128) + (k % 4) * 32, 16, 1024);
+            const uint64_t bdesc =
+                B_MN ? umma_smem_desc(sb + k * 2048, BK * 128, 1024)
+                     : umma_smem_desc(sb + (k / 4) * (BNh * 128) + (k % 4) * 32, 16, 1024);
             umma2_bf16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma2_commit_both(&empty[stage], 1u);
@@ -498,20 +510,20 @@ int run2(const void* A, const void* B, const void* A2, const void* B2, void* C, 
   if (a_mn)
     rc = make_tmap_2d(&tmA, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, true);
   else
-    rc = make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BMc, true);
+    rc = make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BKT, BMc, true);
   if (rc) return rc;
   if (b_mn)
     rc = make_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true);
   else
-    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BNh, true);
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BKT, BNh, true);
   if (rc) return rc;
   if (K2 > 0) {
-    rc = make_tmap_2d(&tmA2, A2, 2, (uint64_t)K2, (uint64_t)M, (uint64_t)lda2 * 2, BK, BMc, true);
+    rc = make_tmap_2d(&tmA2, A2, 2, (uint64_t)K2, (uint64_t)M, (uint64_t)lda2 * 2, BKT, BMc, true);
     if (rc) return rc;
     if (b_mn)
       rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)N, (uint64_t)K2, (uint64_t)ldb2 * 2, 64, BK, true);
     else
-      rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)K2, (uint64_t)N, (uint64_t)ldb2 * 2, BK, BNh, true);
+      rc = make_tmap_2d(&tmB2, B2, 2, (uint64_t)K2, (uint64_t)N, (uint64_t)ldb2 * 2, BKT, BNh, true);
     if (rc) return rc;
   } else {
     tmA2 = tmA;
