@@ -61,6 +61,10 @@ struct Args2 {
   void* C;
   long long ldc;
   int accumulate;   // C += result (red.global.add: fp32 scalars or packed bf16 pairs)
+  // bf16 output rows stored to other GPUs (reduce-scatter by slots): row r goes to local row
+  // r % c_rows_per_peer of c_peers[r / c_rows_per_peer]; 0 rows per peer = plain local C
+  void* c_peers[8];
+  int c_rows_per_peer;
   int splits, kb_per_split;
   int raster_m_fast;
   int* status;
@@ -372,7 +376,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               const int lr = i * 8 + rr;
               const int grow = m0 + q * 32 + lr;
               if (grow < g.M) {
-                OutT* dst = Cout + static_cast<long long>(grow) * g.ldc + colb;
+                OutT* dst =
+                    (g.c_rows_per_peer > 0
+                         ? reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
+                               static_cast<long long>(grow % g.c_rows_per_peer) * g.ldc
+                         : Cout + static_cast<long long>(grow) * g.ldc) +
+                    colb;
                 const uint4 pk = *reinterpret_cast<const uint4*>(sblk + lr * 80 + cc * 16);
                 if (g.accumulate)
                   red_add8_bf16(dst, pk);
@@ -493,7 +502,8 @@ namespace {
 int run2(const void* A, const void* B, const void* A2, const void* B2, void* C, int M, int N, int K,
          int K2, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
          int a_mn, int b_mn, int out_fp32, int accumulate, int splits, int* status,
-         cudaStream_t stream) {
+         cudaStream_t stream, const void* const* c_peers = nullptr, int c_world = 0,
+         int c_rows_per_peer = 0) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return -4;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -3;
@@ -543,6 +553,11 @@ int run2(const void* A, const void* B, const void* A2, const void* B2, void* C, 
   g.kb_per_split = kb_per;
   g.raster_m_fast = tiles_n > tiles_m ? 1 : 0;
   g.status = status;
+  if (c_peers != nullptr && c_rows_per_peer > 0) {
+    if (c_world < 1 || c_world > 8 || out_fp32 || accumulate || splits > 1) return -5;
+    for (int i = 0; i < c_world; ++i) g.c_peers[i] = const_cast<void*>(c_peers[i]);
+    g.c_rows_per_peer = c_rows_per_peer;
+  }
   const long long total = 1LL * tiles_m * tiles_n * splits;
 #define LB2(AM, BMJ)                                                                    \
   (out_fp32 ? launch2<AM, BMJ, float>(tmA, tmB, tmA2, tmB2, g, total, stream)          \
@@ -582,4 +597,16 @@ extern "C" int lb_gemm_bf16_2cta_ext(const void* A, const void* B, const void* A
 // launch has asked the driver.
 extern "C" int lb_gemm_2cta_pairs() {
   return lb::g_max_pairs > 0 ? lb::g_max_pairs : lb::sm_count() / 2;
+}
+
+// bf16 C rows stored into per-rank buffers (see lb_gemm_bf16_push16 in gemm_bf16.cu): row r of the
+// product goes to local row r % rows_per_peer of c_peers[r / rows_per_peer].
+extern "C" int lb_gemm_bf16_2cta_push(const void* A, const void* B, const void* const* c_peers,
+                                      int world, int rows_per_peer, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int a_mn,
+                                      int b_mn, int* status, void* stream_) {
+  if (M != world * rows_per_peer) return -3;
+  return lb::run2(A, B, nullptr, nullptr, nullptr, M, N, K, 0, lda, ldb, 0, 0, ldc, a_mn, b_mn, 0, 0,
+                  1, status, reinterpret_cast<cudaStream_t>(stream_), c_peers, world,
+                  rows_per_peer);
 }

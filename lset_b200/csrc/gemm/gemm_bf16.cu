@@ -922,6 +922,10 @@ extern "C" int lb_gemm_bf16_2cta_ext(const void* A, const void* B, const void* A
                                      void* C, int M, int N, int K, int K2, long long lda,
                                      long long ldb, long long lda2, long long ldb2, long long ldc,
                                      int b_mn, int* status, void* stream_);
+extern "C" int lb_gemm_bf16_2cta_push(const void* A, const void* B, const void* const* c_peers,
+                                      int world, int rows_per_peer, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int a_mn,
+                                      int b_mn, int* status, void* stream_);
 extern "C" int lb_gemm_2cta_pairs();
 
 // The plain products (no bias, no scatter to other GPUs, at least one 256 x 256 tile), those with
@@ -965,6 +969,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
       M >= 256 && N >= 256)  // "scatter" to this GPU only: C += A · op(B) in bf16
     return lb_gemm_bf16_2cta(A, B, const_cast<void*>(c_peers[0]), M, N, K, lda, ldb, ldc, a_mn,
                              b_mn, 0, 1, 1, status, stream_);
+  if (use_2cta() && bias == nullptr && scatter && c_store && !out_fp32 && bn == 0 && M >= 256 &&
+      N >= 256 && c_world <= 8)  // reduce-scatter by slots: rows stored into the owners' areas
+    return lb_gemm_bf16_2cta_push(A, B, c_peers, c_world, c_rows_per_peer, M, N, K, lda, ldb, ldc,
+                                  a_mn, b_mn, status, stream_);
   if (use_2cta() && bias == nullptr && !scatter && bn == 0 && M >= 256 && N >= 256) {
     int s2 = splits;
     if (s2 == 0) {
