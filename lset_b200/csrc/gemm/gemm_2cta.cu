@@ -65,6 +65,17 @@ struct Args2 {
   // r % c_rows_per_peer of c_peers[r / c_rows_per_peer]; 0 rows per peer = plain local C
   void* c_peers[8];
   int c_rows_per_peer;
+  // gather of A rows (GATHER kernels): the rows live in `world` ranks' buffers a_peers[r]
+  // ([n_local, K], row stride lda_peer elements); two extra warps per CTA pull the peers' rows
+  // into a_local ([world * n_local, K], what tmA maps) as items of 16 rows, and flags[c] counts
+  // the items of 128-row chunk c that have landed (it only grows: epoch * items after call epoch).
+  const void* a_peers[8];
+  void* a_local;
+  long long lda_peer;
+  int n_local, world, rank;
+  unsigned* flags;
+  unsigned* chunk_counter;
+  unsigned epoch;
   int splits, kb_per_split;
   int raster_m_fast;
   int* status;
@@ -160,8 +171,10 @@ __device__ __forceinline__ void red_add4(float* dst, float a, float b, float c, 
                : "memory");
 }
 
-template <int A_MN, int B_MN, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+constexpr int kPullWarps = 2;
+
+template <int A_MN, int B_MN, typename OutT, int GATHER = 0>
+__global__ void __launch_bounds__(kThreads + (GATHER ? 32 * kPullWarps : 0), 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB2, Args2 g) {
@@ -207,16 +220,40 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (g.M + 2 * BMc - 1) / (2 * BMc);
+  // gather: tiles are laid out rank by rank (a tile never spans two ranks' rows) and visited own
+  // rank first, then the peers in the order their rows are pulled
+  [[maybe_unused]] const int tiles_per_peer = GATHER ? (g.n_local + 2 * BMc - 1) / (2 * BMc) : 1;
+  [[maybe_unused]] const int chunks_per_peer = GATHER ? (g.n_local + BMc - 1) / BMc : 1;
+  const int tiles_m = GATHER ? g.world * tiles_per_peer : (g.M + 2 * BMc - 1) / (2 * BMc);
   const int tiles_n = (g.N + BNp - 1) / BNp;
   const int kb_first = (g.K + BK - 1) / BK;                    // k-blocks of the first operand pair
   const int kb_total = kb_first + (g.K2 + BK - 1) / BK;
   const int total = tiles_m * tiles_n * g.splits;
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
-  auto decode = [&](int mn, int& m0, int& n0) {
-    m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * (2 * BMc) + int(rank) * BMc;
-    n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BNp;
+  // m0: first row of this CTA's half of the tile; m_limit: rows from there on that belong to the
+  // tile's rank (gather) or exist at all; chunk: flag index of this CTA's rows (gather; -1: none)
+  auto decode = [&](int mn, int& m0, int& n0, int& m_limit, int& chunk) {
+    if constexpr (GATHER) {
+      n0 = (mn % tiles_n) * BNp;
+      const int mi = mn / tiles_n;
+      const int peer = (g.rank + mi / tiles_per_peer) % g.world;
+      const int row_in_peer = (mi % tiles_per_peer) * (2 * BMc) + int(rank) * BMc;
+      m0 = peer * g.n_local + row_in_peer;
+      m_limit = min(g.M, (peer + 1) * g.n_local);
+      chunk = row_in_peer < g.n_local ? peer * chunks_per_peer + row_in_peer / BMc : -1;
+    } else {
+      m0 = (g.raster_m_fast ? mn % tiles_m : mn / tiles_n) * (2 * BMc) + int(rank) * BMc;
+      n0 = (g.raster_m_fast ? mn / tiles_m : mn % tiles_n) * BNp;
+      m_limit = g.M;
+      chunk = -1;
+    }
+  };
+  constexpr int kPullRows = 16;  // rows per pull item (one warp)
+  [[maybe_unused]] auto items_of_chunk = [&](int chunk) {
+    const int t = chunk % chunks_per_peer;
+    const int rows = min(BMc, g.n_local - t * BMc);
+    return (rows + kPullRows - 1) / kPullRows;
   };
 
   if (warp == 0) {
@@ -227,8 +264,34 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int tile = pair; tile < total && ok; tile += npairs) {
         const int split = tile / (tiles_m * tiles_n);
-        int m0, n0;
-        decode(tile - split * (tiles_m * tiles_n), m0, n0);
+        int m0, n0, m_limit, chunk;
+        decode(tile - split * (tiles_m * tiles_n), m0, n0, m_limit, chunk);
+        if constexpr (GATHER) {
+          if (chunk >= 0) {
+            // this CTA's rows of the tile must have been pulled into local memory
+            bool landed = false;
+            const unsigned want = g.epoch * unsigned(items_of_chunk(chunk));
+            const unsigned long long t0 = globaltimer_ns();
+            for (unsigned it2 = 0;; ++it2) {
+              unsigned v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
+                           : "=r"(v)
+                           : "l"(g.flags + chunk)
+                           : "memory");
+              if (v >= want) {
+                landed = true;
+                break;
+              }
+              if ((it2 & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+            }
+            if (!landed) {
+              report_status(g.status, kStatusTimeoutPeer);
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
         const int nb = n0 + int(rank) * BNh;          // this CTA's half of the B tile
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(kb0 + g.kb_per_split, kb_total);
@@ -328,6 +391,58 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     __syncwarp();
+  } else if (GATHER && warp >= 2 + kEpiWarps) {
+    // ------------------------------------------------------------------ pull warps (10, 11)
+    if constexpr (GATHER) {
+      constexpr int kItemsPerChunk = BMc / kPullRows;
+      const int items_total = g.world * chunks_per_peer * kItemsPerChunk;
+      const long long vec_per_row = (2LL * g.K) / 16;
+      for (;;) {
+        unsigned c = 0;
+        if (lane == 0) c = atomicAdd(g.chunk_counter, 1u);
+        c = __shfl_sync(0xffffffffu, c, 0);
+        if (c >= unsigned(items_total)) break;
+        const int chunk_i = int(c) / kItemsPerChunk;    // chunks in consumption order
+        const int sub = int(c) % kItemsPerChunk;
+        const int peer = (g.rank + chunk_i / chunks_per_peer) % g.world;
+        const int t = chunk_i % chunks_per_peer;
+        const int r0 = t * BMc + sub * kPullRows;
+        const int chunk_end = min((t + 1) * BMc, g.n_local);
+        if (r0 >= chunk_end) continue;                  // short last chunk: no such item
+        const int r1 = min(r0 + kPullRows, chunk_end);
+        if (peer != g.rank) {                           // own rows are in place already
+          const char* src = static_cast<const char*>(g.a_peers[peer]);
+          char* dst = static_cast<char*>(g.a_local) + 2LL * peer * g.n_local * g.lda_peer;
+          const long long total_vec = vec_per_row * (r1 - r0);
+          constexpr int kPullDepth = 16;  // 16 x 16 bytes per lane in flight
+          for (long long i0 = 0; i0 < total_vec; i0 += 32 * kPullDepth) {
+            uint4 buf[kPullDepth];
+#pragma unroll
+            for (int u = 0; u < kPullDepth; ++u) {
+              const long long i = i0 + u * 32 + lane;
+              if (i < total_vec) {
+                const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+                buf[u] = *reinterpret_cast<const uint4*>(src + 2LL * rr * g.lda_peer + cc * 16);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kPullDepth; ++u) {
+              const long long i = i0 + u * 32 + lane;
+              if (i < total_vec) {
+                const long long rr = r0 + i / vec_per_row, cc = i % vec_per_row;
+                *reinterpret_cast<uint4*>(dst + 2LL * rr * g.lda_peer + cc * 16) = buf[u];
+              }
+            }
+          }
+          __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          unsigned* fp = g.flags + (peer * chunks_per_peer + t);
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(fp) : "memory");
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;
@@ -339,8 +454,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     int it = 0;
     for (int tile = pair; tile < total; tile += npairs, ++it) {
       const int split = tile / (tiles_m * tiles_n);
-      int m0, n0;
-      decode(tile - split * (tiles_m * tiles_n), m0, n0);
+      int m0, n0, m_limit, chunk;
+      decode(tile - split * (tiles_m * tiles_n), m0, n0, m_limit, chunk);
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aphase)) {
@@ -375,7 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; i < 4; ++i) {
               const int lr = i * 8 + rr;
               const int grow = m0 + q * 32 + lr;
-              if (grow < g.M) {
+              if (grow < m_limit) {
                 OutT* dst =
                     (g.c_rows_per_peer > 0
                          ? reinterpret_cast<OutT*>(g.c_peers[grow / g.c_rows_per_peer]) +
@@ -403,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               for (int i = 0; i < 8; ++i) {
                 const int lr = i * 4 + rr;
                 const int grow = m0 + q * 32 + lr;
-                if (grow < g.M) {
+                if (grow < m_limit) {
                   const float* sp = st + lr * 33 + cc;
                   red_add4(reinterpret_cast<float*>(g.C) + static_cast<long long>(grow) * g.ldc +
                                col0 + cc,
@@ -412,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
             __syncwarp();
-          } else if (row < g.M && col0 < g.N) {
+          } else if (row < m_limit && col0 < g.N) {
             float* fd = reinterpret_cast<float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -443,10 +558,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 // SMs / 2; a persistent grid larger than it would run in two waves.
 int g_max_pairs = 0;
 
-template <int A_MN, int B_MN, typename OutT>
+template <int A_MN, int B_MN, typename OutT, int GATHER = 0>
 int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
             const CUtensorMap& tmB2, const Args2& g, long long total, cudaStream_t stream) {
-  auto kern = gemm_2cta_kernel<A_MN, B_MN, OutT>;
+  auto kern = gemm_2cta_kernel<A_MN, B_MN, OutT, GATHER>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
@@ -455,7 +570,7 @@ int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& t
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kThreads + (GATHER ? 32 * kPullWarps : 0), 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -609,4 +724,52 @@ extern "C" int lb_gemm_bf16_2cta_push(const void* A, const void* B, const void* 
   return lb::run2(A, B, nullptr, nullptr, nullptr, M, N, K, 0, lda, ldb, 0, 0, ldc, a_mn, b_mn, 0, 0,
                   1, status, reinterpret_cast<cudaStream_t>(stream_), c_peers, world,
                   rows_per_peer);
+}
+
+// All-gather fused into the product (see lb_gemm_bf16_ag in gemm_bf16.cu, whose contract this
+// shares, without bias): C[world * rows_local, N] = A_all · op(B), the peers' rows of A_all pulled
+// by two extra warps per CTA while the tiles consume them in pull order. The caller has copied
+// its own rows into a_all and zeroed nothing: `counter` is reset here.
+extern "C" int lb_gemm_bf16_2cta_ag(const void* const* a_peers, void* a_all, const void* B, void* C,
+                                    int rows_local, int world, int rank, int N, int K,
+                                    long long lda, long long ldb, long long ldc, int b_mn,
+                                    unsigned* flags, unsigned* counter, unsigned epoch,
+                                    int* status, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_local <= 0 || N <= 0 || K <= 0)
+    return -3;
+  if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -3;
+  const int M = world * rows_local;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, a_all, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BKT, BMc, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true);
+  else
+    rc = make_tmap_2d(&tmB, B, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BKT, BNh, true);
+  if (rc) return rc;
+  Args2 g{};
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.C = C;
+  g.ldc = ldc;
+  g.splits = 1;
+  g.kb_per_split = (K + BK - 1) / BK;
+  g.status = status;
+  for (int i = 0; i < world; ++i) g.a_peers[i] = a_peers[i];
+  g.a_local = a_all;
+  g.lda_peer = lda;
+  g.n_local = rows_local;
+  g.world = world;
+  g.rank = rank;
+  g.flags = flags;
+  g.chunk_counter = counter;
+  g.epoch = epoch;
+  const long long total =
+      1LL * world * ((rows_local + 2 * BMc - 1) / (2 * BMc)) * ((N + BNp - 1) / BNp);
+  if (cudaMemsetAsync(counter, 0, sizeof(unsigned), stream) != cudaSuccess) return -12;
+  return b_mn ? launch2<0, 1, __nv_bfloat16, 1>(tmA, tmB, tmA, tmB, g, total, stream)
+              : launch2<0, 0, __nv_bfloat16, 1>(tmA, tmB, tmA, tmB, g, total, stream);
 }

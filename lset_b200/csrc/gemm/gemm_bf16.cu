@@ -926,6 +926,11 @@ extern "C" int lb_gemm_bf16_2cta_push(const void* A, const void* B, const void* 
                                       int world, int rows_per_peer, int M, int N, int K,
                                       long long lda, long long ldb, long long ldc, int a_mn,
                                       int b_mn, int* status, void* stream_);
+extern "C" int lb_gemm_bf16_2cta_ag(const void* const* a_peers, void* a_all, const void* B, void* C,
+                                    int rows_local, int world, int rank, int N, int K,
+                                    long long lda, long long ldb, long long ldc, int b_mn,
+                                    unsigned* flags, unsigned* counter, unsigned epoch,
+                                    int* status, void* stream_);
 extern "C" int lb_gemm_2cta_pairs();
 
 // The plain products (no bias, no scatter to other GPUs, at least one 256 x 256 tile), those with
@@ -1598,6 +1603,12 @@ extern "C" int lb_gemm_bf16_ag(const void* const* a_peers, void* a_all, const vo
   if (world < 1 || world > 8 || rows_local <= 0 || N <= 0 || K <= 0) return -3;
   if ((N & 7) || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7)) return -3;
   const int M = world * rows_local;
+  // Compute-heavy products run on the CTA-pair kernel; where the transfer dominates (many ranks,
+  // few output columns) the one-CTA kernel with its copy CTAs stays.
+  if (use_2cta() && bias == nullptr && N >= 256 && rows_local >= 256 &&
+      !(2.0 * (world - 1) * rows_local * K / 700e9 > 0.5 * 2.0 * M * N * K / 1.4e15))
+    return lb_gemm_bf16_2cta_ag(a_peers, a_all, B, C, rows_local, world, rank, N, K, lda, ldb, ldc,
+                                b_mn, flags, counter, epoch, status, stream_);
   const int bn = N > 128 ? 256 : 128;
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, a_all, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
