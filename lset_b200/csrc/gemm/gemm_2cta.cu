@@ -145,11 +145,6 @@ __device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint
 // Arrive on the barrier at this shared-memory offset in both CTAs of the pair once the tcgen05
 // operations issued so far have completed: one commit per CTA, the peer's barrier through its
 // address in the cluster's shared-memory window.
-__device__ __forceinline__ void umma2_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
 __device__ __forceinline__ void umma2_commit_both(uint64_t* bar, uint32_t peer_rank) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
