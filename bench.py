@@ -382,6 +382,24 @@ def run_ours(args):
     # the host, pinned batch -> H2D, forward/backward/optimizer, loss read back for the log line.
     engine.max_steps = e2e_steps           # step 0 starts the loader; steps 1..K are timed
     engine.needs_dist_cleanup = False      # the process group is still needed for the reductions
+    # One more untimed warm-up step, on the longest batch the loop is going to see (a dry pass
+    # over the loader finds it: the order of an epoch depends on seed and epoch only, and train()
+    # re-seeds it). A batch longer than all before it makes the caching allocator ask the driver
+    # for new blocks, which on a shared host has stalled a step by several hundred milliseconds.
+    if engine.sampler is not None:
+        engine.sampler.set_epoch(engine.epoch)
+    if engine._data_gen is not None:
+        engine._data_gen.manual_seed(engine._data_seed + engine.epoch)
+    longest, longest_tokens = None, -1
+    for i, b in enumerate(engine.dataloader):
+        if i >= e2e_steps:
+            break
+        n_tok = sum(int(b[k]["input_ids"].numel()) for k in ("query", "doc", "neg") if k in b)
+        if n_tok > longest_tokens:
+            longest, longest_tokens = b, n_tok
+    if longest is not None:
+        engine.train_step(longest).item()
+        nv.check_status(device)
     timed.arm(1, K, device, sample_clocks=False)
     with contextlib.redirect_stdout(sys.stderr):   # the loop's own log lines
         last = engine.train()
@@ -391,7 +409,8 @@ def run_ours(args):
     e2e = {"value": pairs / (ms_e2e / 1e3), "unit": "pairs/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": int(timed.h2d / K), "d2h_bytes_per_step": 4, "last_loss": last,
            "api": "lset_b200.train.engine.TrainingEngine.train() (DataLoader + collator + pinned "
-                  "H2D + step + global loss read back and logged every step)"}
+                  "H2D + step + global loss read back and logged every step); one untimed warm-up "
+                  "step on the longest batch of the loop before it"}
     if rank == 0:
         line = result_line("ours", world, K, W, ms_dev, pairs, tok_dev, clocks, e2e, launches,
                            {"host_enqueue_ms_per_step": round(host_ms, 2),

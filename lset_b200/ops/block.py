@@ -104,12 +104,25 @@ def _library():
 _arenas = {}
 
 
+def _arena_size(nbytes: int) -> int:
+    """``nbytes`` rounded up to the next size of a geometric series (eight sizes per octave, at
+    most 12.5 % more). Packed batches differ in token count from step to step; with exact sizes
+    every batch longer than all before it makes the caching allocator ask the driver for one new
+    block per decoder block (a stall of up to several hundred milliseconds on a busy host), with
+    rounded sizes that happens a few times at the start of a run and then no more."""
+    if nbytes <= (1 << 20):
+        return max(nbytes, 1)
+    top = 1 << (nbytes.bit_length() - 1)       # largest power of two <= nbytes
+    step = top >> 3
+    return (nbytes + step - 1) // step * step
+
+
 def _work_arena(nbytes: int, device) -> torch.Tensor:
     """Temporary storage of the block backward: one buffer per device, grown on demand. Blocks run
     their backward one after the other on the same stream, so they share it."""
     t = _arenas.get(device)
     if t is None or t.numel() < nbytes:
-        t = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        t = torch.empty(_arena_size(nbytes), dtype=torch.uint8, device=device)
         _arenas[device] = t
     return t
 
@@ -392,7 +405,7 @@ class _BlockFn(torch.autograd.Function):
         tp, tp_state = _tp_struct(plan.sp, T, H) if plan.sp is not None else (None, None)
         tp_ptr = ctypes.addressof(tp) if tp is not None else None
         nbytes = lib.lb_block_saved_bytes(ctypes.addressof(d), T, int(has_res), tp_ptr)
-        saved = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        saved = torch.empty(_arena_size(nbytes), dtype=torch.uint8, device=dev)
         out = torch.empty(T, H, dtype=branch.dtype, device=dev)
         res_out = torch.empty(T, H, dtype=branch.dtype, device=dev)
         io = LbBlockIO()
