@@ -339,3 +339,22 @@ def test_gemma_post_pooling_projection_is_applied_between_pooling_and_normalisat
     toks = lambda ts: [[5, 6, 7, 8][: 2 + i] for i, _ in enumerate(ts)]
     out = encode_chunked(model, toks, None, texts, device="cpu", pooling="mean", post_pooling=proj)
     assert out.shape == (2, 24) and abs(float((out[0] ** 2).sum()) - 1.0) < 1e-4
+
+
+def test_block_runner_arena_sizes_form_a_geometric_series():
+    """Arena sizes are rounded up to eight sizes per octave: never smaller than asked for, at most
+    12.5 % larger, and token counts a few percent apart share a size (so the caching allocator
+    sees a handful of distinct sizes over a run instead of one per batch length)."""
+    import random
+
+    from lset_b200.ops.block import _arena_size
+
+    rng = random.Random(0)
+    for _ in range(20000):
+        n = rng.randint(1, 1 << 40)
+        r = _arena_size(n)
+        assert n <= r <= n * 1.125 + 1
+    assert _arena_size(1000) == 1000                      # small requests stay exact
+    sizes = {_arena_size(t * 40960) for t in range(20000, 27000, 50)}   # bytes per token x tokens
+    assert len(sizes) <= 5, sorted(sizes)
+    assert _arena_size(_arena_size(123456789)) == _arena_size(123456789)
