@@ -439,11 +439,11 @@ def run_ours(args):
 def run_reference(args):
     preset = PRESETS[args.config]
     if preset["tp"] > 1:
-        # The reference's tensor-parallel step was run once on this pool (2 x B200, TP2 x DP1, the
+        # The reference's tensor-parallel step was run once on these machines (2 x B200, TP2 x DP1, the
         # command below with --impl reference) and its own Triton code raised "an illegal memory
         # access was encountered" on rank 1. A GPU fault in the reference is not run a second time.
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference's tensor-parallel step faulted on this pool (Triton Error "
+                          "the reference's tensor-parallel step faulted on these B200 machines (Triton Error "
                           "[CUDA]: an illegal memory access was encountered, TP2 x DP1 on 2 x B200); "
                           "its GPU code is not run again"}))
         return
