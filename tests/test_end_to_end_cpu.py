@@ -469,3 +469,40 @@ def test_parameter_sharded_mode_combines_with_other_options(tmp_path, tag, optio
         logged[mode] = [float(tok.split("=")[1]) for line in r.stdout.splitlines()
                         if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
     assert len(logged["true"]) >= 2 and logged["true"] == pytest.approx(logged["false"], abs=2e-3), logged
+
+
+def test_parameter_sharded_mode_checkpoints_resume_and_interchange(tmp_path):
+    """A run in the parameter-sharded mode saves full tensors like the resident mode: it resumes
+    to the losses of the uninterrupted run, and a checkpoint written in the resident mode
+    continues in the parameter-sharded mode with the same losses."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positives": [" ".join(WORDS[(i + j) % 16] for j in range(12))],
+                                 "negatives": [" ".join(WORDS[(i + 3 * j) % 16] for j in range(9))]}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+
+    def run(out, steps, sharded, *extra):
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--data.num_hard_negatives", "1",
+                  "--training.batch_size", "4", "--training.max_steps", str(steps),
+                  "--training.lr", "1e-3", "--training.scheduler", "constant",
+                  "--packing.enabled", "true", "--checkpoint.save_steps", "2",
+                  "--checkpoint.output_dir", str(out), "--logging.log_interval", "1",
+                  "--distributed.dp_size", "2", "--distributed.reshard_after_forward", sharded,
+                  *extra])
+        assert r.returncode == 0, r.stderr[-2000:]
+        return [float(tok.split("=")[1]) for line in r.stdout.splitlines()
+                if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
+
+    whole = run(tmp_path / "whole", 4, "true")
+    assert len(whole) == 4
+    assert run(tmp_path / "split", 2, "true") == pytest.approx(whole[:2], abs=1e-4)
+    rest = run(tmp_path / "split", 4, "true", "--checkpoint.resume_from", "auto")
+    assert rest == pytest.approx(whole[2:], abs=1e-3), (rest, whole)
+    assert run(tmp_path / "resident", 2, "false") == pytest.approx(whole[:2], abs=1e-4)
+    crossed = run(tmp_path / "resident", 4, "true", "--checkpoint.resume_from", "auto")
+    assert crossed == pytest.approx(whole[2:], abs=1e-3), (crossed, whole)
