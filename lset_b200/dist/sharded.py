@@ -353,8 +353,14 @@ class ParamStore:
         # batches): a resident group is reduced when the last of those passes has been through
         # backward, not at the first hook that fires.
         self._pending = {}
+        # Layers that ran a pass none of whose inputs requires a gradient (the first block behind
+        # frozen embeddings: LoRA, QLoRA): torch then fires the module's backward hook when the
+        # gradients of its *outputs* are ready, before the layer's own parameters have received
+        # theirs. Such a layer is not reduced from the hook; `finish_backward` does it.
+        self._fires_early = {}
         for layer, gs in self._groups_of_layer:
             self._pending[id(layer)] = 0
+            self._fires_early[id(layer)] = False
 
             def after_backward(_mod, _gin, _gout, gs=gs, key=id(layer)):
                 left = self._pending[key] = max(0, self._pending[key] - 1)
@@ -362,7 +368,8 @@ class ParamStore:
                     # sharded groups reduce on every pass and micro-step (their full gradient
                     # buffer is handed on to the next layer); resident ones only on the boundary
                     # step, after the last pass
-                    if g.sharded or (self.requires_gradient_sync and left == 0):
+                    if g.sharded or (self.requires_gradient_sync and left == 0
+                                     and not self._fires_early[key]):
                         self._reduce_group(g)
                     if g.sharded:
                         self._release_params(g)
@@ -370,6 +377,8 @@ class ParamStore:
             def before_forward(_mod, _args, gs=gs, key=id(layer)):
                 if torch.is_grad_enabled():
                     self._pending[key] += 1
+                    if not any(torch.is_tensor(a) and a.requires_grad for a in _args):
+                        self._fires_early[key] = True
                 for g in gs:
                     if g.sharded:
                         self._materialize(g)
@@ -527,6 +536,8 @@ class ParamStore:
                 continue
             if not g.reduced:
                 self._reduce_group(g)
+        for key in getattr(self, "_fires_early", ()):
+            self._fires_early[key] = False
 
     def wait_reductions(self) -> None:
         for g in self.groups:

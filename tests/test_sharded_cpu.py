@@ -182,3 +182,39 @@ def test_layers_run_twice_per_step_reduce_after_the_last_pass():
         # seen embedding row), so a handful of elements may differ; a missed reduction moves all
         off = ((t - res[False]["masters"][n]).abs() > 1e-4).float().mean()
         assert off < 1e-3, (n, float(off))
+
+
+def _lora_worker(rank, world, port, out_dir, grad_cache):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = _engine(world, lora=True, lora_r=4, use_grad_cache=grad_cache, gc_chunk_size=2)
+    loss = eng.forward_backward(_batch(rank * 4, rank * 4 + 4), True)
+    total = loss.clone()
+    dist.all_reduce(total)
+    grads = [eng.store._gather_fp32(g, g.grad_shard) for g in eng.store.groups]
+    if rank == 0:
+        torch.save({"loss": total, "grads": grads},
+                   os.path.join(out_dir, f"lora_{int(grad_cache)}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("grad_cache", [False, True])
+def test_first_block_behind_frozen_embeddings_is_reduced_after_its_backward(grad_cache):
+    """With adapters the embeddings are frozen, so no input of the first block requires a gradient
+    and torch fires that block's backward hook *before* its parameters have their gradients. The
+    block's gradients must still be averaged over the ranks: two ranks agree with a single process
+    on the union batch, with and without GradCache."""
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_lora_worker, args=(2, _free_port(), out_dir, grad_cache), nprocs=2, join=True)
+    got = torch.load(os.path.join(out_dir, f"lora_{int(grad_cache)}.pt"), weights_only=False)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        os.environ.pop(k, None)
+    eng = _engine(1, lora=True, lora_r=4)
+    loss = eng.forward_backward(_batch(0, 8), True)
+    assert torch.allclose(loss, got["loss"], atol=1e-5), (loss, got["loss"])
+    assert len(eng.store.groups) == len(got["grads"]) and len(got["grads"]) >= 2
+    for g, ref in zip(eng.store.groups, got["grads"]):
+        assert float(g.flat_grad.abs().max()) > 0
+        assert torch.allclose(g.flat_grad / 2, ref, atol=2e-5), (g.flat_grad / 2 - ref).abs().max()
