@@ -178,7 +178,12 @@ def apply_tp(model: nn.Module, tp_group, plan: Dict[str, str],
         # lora_A of a colwise target / lora_B of a rowwise target stay replicated and un-hooked;
         # the hooks go on the layers that actually change the activation layout.
         if leaf == "lora_B" and kind == "colwise":
-            continue  # its input (rank-r activations) is replicated already
+            # Its input (the rank-r activations) is replicated, but every rank back-propagates only
+            # its own output columns into it: the gradient of that input is a partial sum, and so
+            # would be lora_A's weight gradient and the adapter's share of dx. Identity forward,
+            # all-reduce of the input gradient in backward, as for the base layer.
+            _wrap_forward(module, "colwise", tp_group)
+            continue
         if leaf == "lora_A" and kind == "rowwise":
             _wrap_forward(module, "rowwise", tp_group)
             continue

@@ -143,3 +143,51 @@ def test_plans():
     assert decoder_tp_plan(None, use_sequence_parallel=True, use_lora=True).get("norm") is None
     pb = bert_tp_plan(None)
     assert pb["layers.*.attention.query"] == "colwise" and pb["layers.*.mlp.dense_out"] == "rowwise"
+
+
+def _lora_traj(tp):
+    from lset_b200.tasks.bi_encoder import global_loss_value
+    from lset_b200.train.data.collator import PackedCollator
+    from lset_b200.train.data.dataset import SyntheticPairDataset
+    from lset_b200.train.engine import TrainingEngine
+
+    torch.manual_seed(0)
+    cfg = Qwen3Config(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+    eng = TrainingEngine("qwen3", None, None, dp_size=1, tp_size=tp, batch_size=8, lr=3e-3,
+                         packed=True, model_config=cfg, log_interval=0, device="cpu", grad_clip=1.0,
+                         scheduler_type="constant", lora=True, lora_r=4)
+    ds = SyntheticPairDataset(16, 300, (3, 6), (5, 12), seed=5)
+    coll = PackedCollator()
+    out = []
+    for s in range(3):
+        lo = (s % 2) * 8
+        loss = eng.train_step(coll([ds[i] for i in range(lo, lo + 8)]))
+        out.append(float(global_loss_value(loss, eng.dp_group)))
+    return out
+
+
+def _lora_worker(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    losses = _lora_traj(world)
+    if rank == 0:
+        torch.save(losses, os.path.join(out_dir, "lora_tp.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_lora_under_tensor_parallelism_trains_like_one_process():
+    """Adapters on column-parallel layers: ``lora_B`` is column-sharded and its rank-r input is
+    replicated, so the gradient flowing back into that input (and with it ``lora_A``'s weight
+    gradient and the adapter's share of dx) is a partial sum per rank until it is all-reduced.
+    The third loss depends on ``lora_A``'s second gradient (its first one is zero because
+    ``lora_B`` starts at zero)."""
+    out_dir = tempfile.mkdtemp()
+    mp.spawn(_lora_worker, args=(2, _port(), out_dir), nprocs=2, join=True)
+    got = torch.load(os.path.join(out_dir, "lora_tp.pt"), weights_only=False)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        os.environ.pop(k, None)
+    ref = _lora_traj(1)
+    assert got == pytest.approx(ref, abs=1e-4), (got, ref)
