@@ -39,7 +39,9 @@ def pad_batch(sequences: Sequence[dict], pad_token_id: int, side: str = "left",
 
 
 class _TripleCollator:
-    """query / positive / optional negative -> ``{"query", "doc"[, "neg"]}``."""
+    """query / positive / optional negative(s) -> ``{"query", "doc"[, "neg"]}``. A sample may carry
+    one hard negative (``"negative"``) or a list of them (``"negatives"``, flattened sample by
+    sample: negative j of sample i is row ``i * n + j``)."""
 
     def _batch(self, seqs: List[dict]) -> dict:  # pragma: no cover - overridden
         raise NotImplementedError
@@ -49,6 +51,8 @@ class _TripleCollator:
                "doc": self._batch([s["positive"] for s in batch])}
         if "negative" in batch[0]:
             out["neg"] = self._batch([s["negative"] for s in batch])
+        elif batch[0].get("negatives"):
+            out["neg"] = self._batch([n for s in batch for n in s["negatives"]])
         return out
 
 

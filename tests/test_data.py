@@ -43,6 +43,21 @@ def test_pad_collators():
     assert fb["query"]["input_ids"].numel() == 8 and fb["query"]["num_sequences"] == 2
 
 
+def test_collators_flatten_a_list_of_hard_negatives():
+    """``"negatives"`` (a list per sample) lands in ``"neg"`` sample by sample, as one
+    ``"negative"`` per sample does."""
+    batch = [{"query": _tok([1]), "positive": _tok([2]), "negatives": [_tok([3, 4]), _tok([5])]},
+             {"query": _tok([6]), "positive": _tok([7]), "negatives": [_tok([8]), _tok([9, 10, 11])]}]
+    packed = PackedCollator()(batch)
+    assert packed["neg"]["input_ids"].tolist() == [3, 4, 5, 8, 9, 10, 11]
+    assert packed["neg"]["cu_seqlens"].tolist() == [0, 2, 3, 4, 7]
+    right = RightPadCollator(0)(batch)
+    assert right["neg"]["input_ids"].tolist() == [[3, 4, 0], [5, 0, 0], [8, 0, 0], [9, 10, 11]]
+    ds = SyntheticPairDataset(4, 50, (2, 3), (3, 5), num_negatives=3, seed=1)
+    out = PackedCollator()([ds[i] for i in range(4)])
+    assert out["neg"]["cu_seqlens"].numel() == 4 * 3 + 1
+
+
 class _FakeTok:
     class _E:
         def __init__(self, ids):
