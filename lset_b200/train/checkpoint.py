@@ -10,6 +10,12 @@ readers that do not know it can ignore it.
 
 With the sharded runtime the model entry holds the fp32 master weights (what the reference keeps
 in its FSDP2 parameters); frozen parameters and buffers are stored as they are.
+
+Fused projections (``model.fused_projections``: one ``qkv_proj`` / ``gate_up_proj`` weight) are
+written under the reference's names, split into ``q_proj`` / ``k_proj`` / ``v_proj`` (``query`` /
+``key`` / ``value`` for BERT) and ``gate_proj`` / ``up_proj``, weights, biases and both AdamW moments,
+and fused again on the way in: a checkpoint does not depend on the flag, and the reference, which
+has no fused modules, can read it.
 """
 from __future__ import annotations
 
@@ -40,6 +46,150 @@ def _tp_metas(model) -> dict:
     return {n: p._tp_meta for n, p in model.named_parameters() if hasattr(p, "_tp_meta")}
 
 
+# ---------------------------------------------------------------------- fused projections
+def _fusions(model) -> list:
+    """``[(fused module FQN, [(part module FQN, share), ...])]`` for every fused projection that is
+    a plain linear layer (an adapter wrapped around a fused projection has no unfused twin and
+    keeps its names). Shares are the parts' relative numbers of output rows."""
+    from torch import nn
+
+    out = []
+    for mname, m in model.named_modules():
+        pre = mname + "." if mname else ""
+        if getattr(m, "fused_qkv", False) and isinstance(getattr(m, "qkv_proj", None), nn.Linear):
+            if hasattr(m, "num_kv_heads"):
+                parts = [("q_proj", m.num_heads), ("k_proj", m.num_kv_heads), ("v_proj", m.num_kv_heads)]
+            else:
+                parts = [("query", 1), ("key", 1), ("value", 1)]
+            out.append((pre + "qkv_proj", [(pre + n, w) for n, w in parts]))
+        if getattr(m, "fused_gate_up", False) and isinstance(getattr(m, "gate_up_proj", None), nn.Linear):
+            out.append((pre + "gate_up_proj", [(pre + "gate_proj", 1), (pre + "up_proj", 1)]))
+    return out
+
+
+def _split_rows(t: torch.Tensor, shares) -> list:
+    total = sum(shares)
+    rows = [t.shape[0] * w // total for w in shares]
+    assert sum(rows) == t.shape[0], (t.shape, shares)
+    return list(torch.split(t, rows, dim=0))
+
+
+def _unfuse_state(sd: dict, fusions) -> dict:
+    for fused, parts in fusions:
+        for suffix in ("weight", "bias"):
+            t = sd.pop(f"{fused}.{suffix}", None)
+            if t is not None:
+                for (name, _), piece in zip(parts, _split_rows(t, [w for _, w in parts])):
+                    sd[f"{name}.{suffix}"] = piece.contiguous()
+    return sd
+
+
+def _fuse_state(sd: dict, fusions) -> dict:
+    for fused, parts in fusions:
+        for suffix in ("weight", "bias"):
+            keys = [f"{name}.{suffix}" for name, _ in parts]
+            if f"{fused}.{suffix}" not in sd and all(k in sd for k in keys):
+                sd[f"{fused}.{suffix}"] = torch.cat([sd.pop(k) for k in keys], dim=0)
+    return sd
+
+
+def _optim_layout(model, fusions) -> Optional[list]:
+    """The model's trainable parameters in optimizer order as ``("plain", index)`` or
+    ``("fused", {suffix: index}, parts)`` entries (the weight and bias of one fused projection form
+    one entry); None when nothing is fused."""
+    by_prefix = {fused: parts for fused, parts in fusions}
+    if not by_prefix:
+        return None
+    layout, seen, idx = [], {}, 0
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        prefix, _, suffix = name.rpartition(".")
+        if prefix in by_prefix and suffix in ("weight", "bias"):
+            if prefix not in seen:
+                seen[prefix] = ("fused", {}, by_prefix[prefix])
+                layout.append(seen[prefix])
+            seen[prefix][1][suffix] = idx
+        else:
+            layout.append(("plain", idx))
+        idx += 1
+    return layout
+
+
+def _entry(state: dict, idx):
+    return state.get(idx, state.get(str(idx)))
+
+
+def _unfuse_optim(osd: dict, layout) -> dict:
+    """Optimizer state renumbered for the unfused module order: per part its weight, then its
+    bias, the moments split by rows."""
+    state, out = osd["state"], {}
+    for item in layout:
+        if item[0] == "plain":
+            ent = _entry(state, item[1])
+            if ent is not None:
+                out[len(out)] = ent
+            else:
+                out[len(out)] = None
+            continue
+        _, idxs, parts = item
+        shares = [w for _, w in parts]
+        pieces = {}
+        for suffix, i in idxs.items():
+            ent = _entry(state, i)
+            pieces[suffix] = None if ent is None else {
+                "step": ent["step"],
+                "exp_avg": _split_rows(ent["exp_avg"], shares),
+                "exp_avg_sq": _split_rows(ent["exp_avg_sq"], shares)}
+        for j in range(len(parts)):
+            for suffix in ("weight", "bias"):
+                if suffix not in idxs:
+                    continue
+                e = pieces[suffix]
+                out[len(out)] = None if e is None else {
+                    "step": e["step"].clone() if torch.is_tensor(e["step"]) else e["step"],
+                    "exp_avg": e["exp_avg"][j].contiguous(),
+                    "exp_avg_sq": e["exp_avg_sq"][j].contiguous()}
+    n = len(out)
+    groups = [dict(g, params=list(range(n))) for g in (osd.get("param_groups") or [])][:1]
+    return {"state": {k: v for k, v in out.items() if v is not None}, "param_groups": groups}
+
+
+def _fuse_optim(osd: dict, layout) -> dict:
+    """Inverse of ``_unfuse_optim`` for a state dict written in the unfused numbering."""
+    state, out, src = osd["state"], {}, 0
+    own = sum(1 if it[0] == "plain" else len(it[1]) for it in layout)
+    for item in layout:
+        if item[0] == "plain":
+            ent = _entry(state, src)
+            if ent is not None:
+                out[item[1]] = ent
+            src += 1
+            continue
+        _, idxs, parts = item
+        got = {suffix: [] for suffix in idxs}
+        for _ in parts:
+            for suffix in ("weight", "bias"):
+                if suffix in idxs:
+                    got[suffix].append(_entry(state, src))
+                    src += 1
+        for suffix, i in idxs.items():
+            ents = got[suffix]
+            if all(e is not None for e in ents):
+                out[i] = {"step": ents[0]["step"],
+                          "exp_avg": torch.cat([e["exp_avg"] for e in ents], dim=0),
+                          "exp_avg_sq": torch.cat([e["exp_avg_sq"] for e in ents], dim=0)}
+    groups = [dict(g, params=list(range(own))) for g in (osd.get("param_groups") or [])][:1]
+    return {"state": out, "param_groups": groups}
+
+
+def _optim_entries(osd: dict) -> int:
+    groups = osd.get("param_groups") or []
+    if groups and "params" in groups[0]:
+        return sum(len(g["params"]) for g in groups)
+    return len(osd["state"])
+
+
 def model_state(model, store=None) -> dict:
     """Full (unsharded) model tensors by FQN. Data-parallel shards are gathered by the store;
     tensor-parallel shards are re-assembled over the tensor-parallel group, so a checkpoint holds
@@ -54,15 +204,15 @@ def model_state(model, store=None) -> dict:
 
         for name, meta in _tp_metas(model).items():
             sd[name] = unshard(sd[name], meta, group)
-    return sd
+    return _unfuse_state(sd, _fusions(model))
 
 
 def load_model_state(model, sd: dict, store=None, strict: bool = True) -> None:
+    sd = _fuse_state(dict(sd), _fusions(model))
     _, tpr, tpw = _tp_of(store)
     if tpw > 1:
         from ..dist.tp import reshard
 
-        sd = dict(sd)
         for name, meta in _tp_metas(model).items():
             if name in sd:
                 sd[name] = reshard(sd[name], meta, tpr, tpw)
@@ -85,10 +235,16 @@ def optimizer_state(optimizer, model=None, store=None) -> dict:
                 ent = osd["state"][idx]
                 for k in ("exp_avg", "exp_avg_sq"):
                     ent[k] = unshard(ent[k], meta, group)
-    return osd
+    layout = _optim_layout(model, _fusions(model)) if model is not None else None
+    return _unfuse_optim(osd, layout) if layout is not None else osd
 
 
-def load_optimizer_state(optimizer, osd: dict, store=None) -> None:
+def load_optimizer_state(optimizer, osd: dict, store=None, model=None) -> None:
+    layout = _optim_layout(model, _fusions(model)) if model is not None else None
+    if layout is not None:
+        own = sum(1 if it[0] == "plain" else len(it[1]) for it in layout)
+        if _optim_entries(osd) != own:      # written in the unfused numbering
+            osd = _fuse_optim(osd, layout)
     _, tpr, tpw = _tp_of(store)
     if tpw > 1:
         from ..dist.tp import reshard
@@ -138,7 +294,7 @@ def load_checkpoint(model, optimizer, ckpt_dir: str, store=None) -> int:
     if os.path.exists(single):
         blob = torch.load(single, map_location="cpu", weights_only=False)
         load_model_state(model, blob["model"], store)
-        load_optimizer_state(optimizer, blob["optimizer"], store)
+        load_optimizer_state(optimizer, blob["optimizer"], store, model)
     else:
         import torch.distributed.checkpoint as dcp
 
@@ -147,7 +303,7 @@ def load_checkpoint(model, optimizer, ckpt_dir: str, store=None) -> int:
         target = {"model": msd, "optimizer": osd}
         dcp.load(target, checkpoint_id=ckpt_dir)
         load_model_state(model, target["model"], store)
-        load_optimizer_state(optimizer, _unflatten_optim(target["optimizer"]), store)
+        load_optimizer_state(optimizer, _unflatten_optim(target["optimizer"]), store, model)
     meta = os.path.join(ckpt_dir, "meta.pt")
     if os.path.exists(meta):
         return int(torch.load(meta, map_location="cpu", weights_only=False)["step"])

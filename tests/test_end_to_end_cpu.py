@@ -506,3 +506,46 @@ def test_parameter_sharded_mode_checkpoints_resume_and_interchange(tmp_path):
     assert run(tmp_path / "resident", 2, "false") == pytest.approx(whole[:2], abs=1e-4)
     crossed = run(tmp_path / "resident", 4, "true", "--checkpoint.resume_from", "auto")
     assert crossed == pytest.approx(whole[2:], abs=1e-3), (crossed, whole)
+
+
+@pytest.mark.parametrize("layout", [[], ["--distributed.dp_size", "2"]], ids=["single", "dp2"])
+def test_checkpoints_do_not_depend_on_fused_projections(tmp_path, layout):
+    """A model with fused QKV / gate-up weights writes them under the unfused (reference) names,
+    moments included: a run that starts unfused and resumes fused, or the other way round, logs
+    the losses of the uninterrupted run, in the single-file and the distributed format."""
+    model = _model_dir(tmp_path / "model")
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as fh:
+        for i in range(64):
+            fh.write(json.dumps({"query": f"what is {WORDS[i % 16]} {i}",
+                                 "positives": [" ".join(WORDS[(i + j) % 16] for j in range(12))],
+                                 "negatives": [" ".join(WORDS[(i + 3 * j) % 16] for j in range(9))]}) + "\n")
+    (tmp_path / "empty.yaml").write_text("{}\n")
+
+    def run(out, steps, fused, *extra):
+        r = _run(["-m", "lset_b200.cli", "train", "--config", str(tmp_path / "empty.yaml"),
+                  "--model.path", str(model), "--data.train_path", str(data),
+                  "--data.max_seq_length", "48", "--data.num_hard_negatives", "1",
+                  "--training.batch_size", "4", "--training.max_steps", str(steps),
+                  "--training.lr", "1e-3", "--training.scheduler", "constant",
+                  "--packing.enabled", "true", "--checkpoint.save_steps", "2",
+                  "--checkpoint.output_dir", str(out), "--logging.log_interval", "1",
+                  "--model.fused_projections", fused, *layout, *extra])
+        assert r.returncode == 0, r.stderr[-2000:]
+        return [float(tok.split("=")[1]) for line in r.stdout.splitlines()
+                if line.startswith("step=") for tok in line.split() if tok.startswith("loss=")]
+
+    whole = run(tmp_path / "whole", 4, "true")
+    assert len(whole) == 4
+    assert run(tmp_path / "a", 2, "false") == pytest.approx(whole[:2], abs=1e-4)
+    rest = run(tmp_path / "a", 4, "true", "--checkpoint.resume_from", "auto")
+    assert rest == pytest.approx(whole[2:], abs=1e-3), (rest, whole)
+    assert run(tmp_path / "b", 2, "true") == pytest.approx(whole[:2], abs=1e-4)
+    rest = run(tmp_path / "b", 4, "false", "--checkpoint.resume_from", "auto")
+    assert rest == pytest.approx(whole[2:], abs=1e-3), (rest, whole)
+    if not layout:
+        blob = torch.load(tmp_path / "b" / "step_2" / "checkpoint.pt", map_location="cpu",
+                          weights_only=False)
+        keys = set(blob["model"])
+        assert "layers.0.self_attn.q_proj.weight" in keys and "layers.0.mlp.up_proj.weight" in keys
+        assert not any("qkv_proj" in k or "gate_up_proj" in k for k in keys)
