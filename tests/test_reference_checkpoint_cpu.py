@@ -30,13 +30,22 @@ def _reference():
     return model, opt, ref_ckpt
 
 
-def _engine(tmp_path):
+def _engine(tmp_path, fused=False):
     from lset_b200.models import Qwen3Config
     from lset_b200.train.engine import TrainingEngine
 
     return TrainingEngine("qwen3", None, None, batch_size=4, lr=1e-3, packed=True,
                           model_config=Qwen3Config(**DIMS), log_interval=0, device="cpu",
-                          scheduler_type="constant", output_dir=str(tmp_path / "ours"))
+                          scheduler_type="constant", output_dir=str(tmp_path / "ours"),
+                          fused_projections=fused)
+
+
+def _saved_view(eng):
+    """Weights and optimizer state as this engine writes them (the reference's names and
+    numbering, whether its projections are fused or not)."""
+    from lset_b200.train.checkpoint import model_state, optimizer_state
+
+    return model_state(eng.model, eng.store), optimizer_state(eng.optimizer, eng.model, eng.store)["state"]
 
 
 def _step_with_random_grads(model, opt, seed):
@@ -47,19 +56,19 @@ def _step_with_random_grads(model, opt, seed):
     opt.zero_grad()
 
 
-def test_reference_checkpoint_loads_into_this_engine(tmp_path):
+@pytest.mark.parametrize("fused", [False, True], ids=["unfused", "fused-projections"])
+def test_reference_checkpoint_loads_into_this_engine(tmp_path, fused):
     from lset_b200.train.checkpoint import load_checkpoint
 
     ref_model, ref_opt, ref_ckpt = _reference()
     _step_with_random_grads(ref_model, ref_opt, 1)
     ref_ckpt.save_checkpoint(ref_model, ref_opt, 3, str(tmp_path / "ref"))
-    eng = _engine(tmp_path)
+    eng = _engine(tmp_path, fused)
     step = load_checkpoint(eng.model, eng.optimizer, str(tmp_path / "ref" / "step_3"), store=eng.store)
     assert step == 3
-    ours = dict(eng.store.named_master_tensors())
+    ours, sd = _saved_view(eng)
     for name, p in ref_model.named_parameters():
         assert torch.equal(ours[name], p.detach()), name
-    sd = eng.optimizer.state_dict()["state"]
     ref_sd = ref_opt.state_dict()["state"]
     assert len(sd) == len(ref_sd)
     for idx, ent in ref_sd.items():
@@ -68,11 +77,12 @@ def test_reference_checkpoint_loads_into_this_engine(tmp_path):
     assert eng.optimizer.step_count == 1
 
 
-def test_checkpoint_written_here_loads_through_the_reference(tmp_path):
+@pytest.mark.parametrize("fused", [False, True], ids=["unfused", "fused-projections"])
+def test_checkpoint_written_here_loads_through_the_reference(tmp_path, fused):
     from lset_b200.train.data.collator import PackedCollator
     from lset_b200.train.data.dataset import SyntheticPairDataset
 
-    eng = _engine(tmp_path)
+    eng = _engine(tmp_path, fused)
     ds = SyntheticPairDataset(8, 64, (4, 8), (8, 16), seed=0)
     eng.train_step(PackedCollator()([ds[i] for i in range(4)]))
     path = eng.save(1)
@@ -80,10 +90,9 @@ def test_checkpoint_written_here_loads_through_the_reference(tmp_path):
     _step_with_random_grads(ref_model, ref_opt, 2)     # gives the optimizer a state to overwrite
     step = ref_ckpt.load_checkpoint(ref_model, ref_opt, path)
     assert step == 1
-    ours = dict(eng.store.named_master_tensors())
+    ours, ours_opt = _saved_view(eng)
     for name, p in ref_model.named_parameters():
         assert torch.equal(p.detach(), ours[name]), name
-    ours_opt = eng.optimizer.state_dict()["state"]
     for idx, ent in ref_opt.state_dict()["state"].items():
         assert torch.equal(ent["exp_avg"], ours_opt[idx]["exp_avg"]), idx
         assert float(ent["step"]) == 1.0
