@@ -43,6 +43,14 @@ VARIANTS = {
                         dict(packed=True, matryoshka_dims=[8, 16, 32]), 0),
     "full-recompute": ("qwen3", Qwen3Config(**_DEC),
                        dict(packed=True, activation_checkpoint=True, ac_mode="full"), 0),
+    # parameter-sharded mode (layers hold 1/W of parameters and gradients) with other options
+    "sharded-padded-recompute": ("qwen3", Qwen3Config(**_DEC),
+                                 dict(packed=False, reshard_after_forward=True,
+                                      activation_checkpoint=True, ac_mode="full"), 1),
+    "sharded-gradcache-accumulation": ("qwen3", Qwen3Config(**_DEC),
+                                       dict(packed=True, reshard_after_forward=True,
+                                            use_grad_cache=True, gc_chunk_size=2,
+                                            gradient_accumulation_steps=2), 0),
 }
 
 
@@ -90,6 +98,8 @@ def _worker(rank, world, port, out_path):
         total = loss.clone()
         dist.all_reduce(total)
         stores = [eng.store] + ([eng.task_store] if eng.task_store is not None else [])
+        if opts.get("reshard_after_forward"):
+            assert eng.store.zero3
         res[name] = (float(total), [[st._gather_fp32(g, g.grad_shard) for g in st.groups]
                                     for st in stores])
     if rank == 0:
